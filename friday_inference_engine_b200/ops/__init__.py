@@ -1,0 +1,225 @@
+"""The operations that parts are made of, as functions on torch tensors.
+
+Every function launches this library's own CUDA kernels on the current stream of the
+tensors' device.  Tensors must live on a CUDA device: there is no CPU path, and a
+kernel library that cannot be built or loaded is an error.
+
+`set_backend` swaps the implementation object; the package itself never calls it.  It
+exists so that tests of the code *around* the kernels (cache, step function, loop) can
+run where there is no GPU, with a stand-in defined in the tests.
+"""
+import torch
+
+from . import lib
+from .lib import KernelError
+
+F32, BF16 = 0, 1
+_CODES = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+def code_of(dtype):
+    try:
+        return _CODES[dtype]
+    except KeyError:
+        raise KernelError("no kernel for dtype %s (float32 and bfloat16 only)" % dtype) from None
+
+
+def _ptr(t):
+    return 0 if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("tensor on %s: this library runs on CUDA devices only, it has no CPU path" % t.device)
+
+
+def _rowmajor(t, what):
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise KernelError("%s must be a 2-d tensor with unit inner stride, got shape %s strides %s"
+                          % (what, tuple(t.shape), t.stride()))
+
+
+class CudaOps:
+    """The product's implementation: ctypes calls into the libraries built from csrc/."""
+
+    name = "cuda"
+
+    # -- row-wise ---------------------------------------------------------
+    def embedding(self, tokens, table):
+        _need_cuda(tokens, table)
+        assert tokens.dtype == torch.int32 and tokens.is_contiguous() and table.is_contiguous()
+        out = torch.empty((tokens.numel(), table.shape[1]), dtype=table.dtype, device=table.device)
+        lib.family("rowwise").call("rowwise_embedding", _ptr(tokens), _ptr(table), _ptr(out), tokens.numel(),
+                                   table.shape[1], code_of(table.dtype), _stream())
+        return out
+
+    def gather_rows(self, rows, src):
+        _need_cuda(rows, src)
+        assert rows.dtype == torch.int32 and src.is_contiguous()
+        out = torch.empty((rows.numel(), src.shape[1]), dtype=src.dtype, device=src.device)
+        lib.family("rowwise").call("rowwise_gather_rows", _ptr(rows), _ptr(src), _ptr(out), rows.numel(),
+                                   src.shape[1], code_of(src.dtype), _stream())
+        return out
+
+    def rmsnorm(self, x, weight, eps, out=None):
+        _need_cuda(x, weight)
+        assert x.is_contiguous() and weight.is_contiguous() and weight.numel() == x.shape[-1]
+        if out is None:
+            out = torch.empty_like(x)
+        rows = x.numel() // x.shape[-1]
+        lib.family("rowwise").call("rowwise_rmsnorm", _ptr(x), _ptr(weight), code_of(weight.dtype), _ptr(out), rows,
+                                   x.shape[-1], float(eps), code_of(x.dtype), _stream())
+        return out
+
+    def swiglu(self, gate_up):
+        _need_cuda(gate_up)
+        assert gate_up.is_contiguous() and gate_up.shape[1] % 2 == 0
+        inner = gate_up.shape[1] // 2
+        out = torch.empty((gate_up.shape[0], inner), dtype=gate_up.dtype, device=gate_up.device)
+        lib.family("rowwise").call("rowwise_swiglu", _ptr(gate_up), _ptr(out), gate_up.shape[0], inner,
+                                   code_of(gate_up.dtype), _stream())
+        return out
+
+    def rope_kv_write(self, qkv, row_seq, row_pos, denom, rotary_dim, n_heads, n_kv_heads, head_dim,
+                      k_pool=None, v_pool=None, block_table=None, page_size=0):
+        """Rotates q and k inside `qkv` [rows, (nq + 2 nkv) * hd] (denom None: no rotation) and, if
+        pools are given, writes k and v to the cache rows of (row_seq, row_pos)."""
+        _need_cuda(qkv, row_seq, row_pos)
+        assert qkv.is_contiguous() and qkv.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim
+        write = k_pool is not None
+        if write:
+            assert k_pool.dtype == qkv.dtype and v_pool.dtype == qkv.dtype
+            assert k_pool.is_contiguous() and v_pool.is_contiguous() and block_table.dim() == 2
+        if denom is not None:
+            assert denom.dtype == torch.float32 and denom.numel() == rotary_dim // 2
+        lib.family("rowwise").call(
+            "rowwise_rope_kv_write", _ptr(qkv), _ptr(row_seq), _ptr(row_pos), _ptr(denom), rotary_dim, n_heads,
+            n_kv_heads, head_dim, _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
+            block_table.shape[1] if write else 0, page_size, 1 if write else 0, qkv.shape[0], code_of(qkv.dtype),
+            _stream())
+
+    def advance(self, tokens, sampled, row_pos, kv_len, row_seq):
+        lib.family("rowwise").call("rowwise_advance", _ptr(tokens), _ptr(sampled), _ptr(row_pos), _ptr(kv_len),
+                                   _ptr(row_seq), tokens.numel(), _stream())
+
+    # -- matrix products --------------------------------------------------
+    def linear(self, x, weight, bias=None, residual=None, out_dtype=None, out=None):
+        """x [rows, k] @ weight [n, k]^T (+ bias [n]) (+ residual [rows, n])."""
+        _need_cuda(x, weight, bias, residual)
+        _rowmajor(x, "linear input")
+        _rowmajor(weight, "linear weight")
+        rows, k = x.shape
+        n = weight.shape[0]
+        if weight.shape[1] != k:
+            raise KernelError("linear: input has %d columns, weight %s" % (k, tuple(weight.shape)))
+        out_dtype = out_dtype or x.dtype
+        if out is None:
+            out = torch.empty((rows, n), dtype=out_dtype, device=x.device)
+        if residual is not None:
+            assert residual.shape == out.shape and residual.dtype == out.dtype and residual.stride() == out.stride()
+        self._linear(x, weight, bias, residual, out)
+        return out
+
+    def _linear(self, x, weight, bias, residual, out):
+        rows, k = x.shape
+        n = weight.shape[0]
+        lib.family("gemm_simt").call(
+            "gemm_simt", _ptr(x), code_of(x.dtype), _ptr(weight), code_of(weight.dtype), _ptr(out),
+            code_of(out.dtype), _ptr(bias), code_of(bias.dtype) if bias is not None else 0, _ptr(residual), rows, n,
+            k, x.stride(0), weight.stride(0), out.stride(0), _stream())
+
+    # -- attention --------------------------------------------------------
+    def attention(self, q, q_stride, out, k_pool, v_pool, block_table, page_size, row_seq, row_pos, n_heads,
+                  n_kv_heads, head_dim, window, scale, geometry):
+        """Causal attention of the step's rows over the paged cache.
+
+        q: the buffer that holds the queries, row stride q_stride (elements), head h at h * head_dim.
+        geometry: StepGeometry-like object with rows, n_seqs, max_q_len, max_kv_len (host numbers
+        used to size the launch only).
+        """
+        _need_cuda(q, out, k_pool, v_pool, block_table, row_seq, row_pos)
+        rows = out.shape[0]
+        splits = self.attention_splits(rows, n_heads, geometry.max_kv_len)
+        scratch = None
+        if splits > 1:
+            scratch = geometry.scratch(rows * n_heads * splits * (head_dim + 2), q.device)
+        lib.family("attention_simt").call(
+            "attention_simt", _ptr(q), q_stride, _ptr(out), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
+            block_table.shape[1], page_size, _ptr(row_seq), _ptr(row_pos), rows, n_heads, n_kv_heads, head_dim,
+            window or 0, float(scale), splits, _ptr(scratch), code_of(out.dtype), _stream())
+
+    @staticmethod
+    def attention_splits(rows, n_heads, max_kv_len):
+        """Few rows facing long contexts are cut along the keys so that the device fills."""
+        warps = rows * n_heads
+        want = 148 * 16
+        if warps >= want or max_kv_len <= 128:
+            return 1
+        return int(max(1, min(want // max(warps, 1), (max_kv_len + 63) // 64, 64)))
+
+    # -- sampling ---------------------------------------------------------
+    def sample(self, logits, temperature, streams, steps, seed, row_live=None, out=None):
+        _need_cuda(logits, temperature, streams, steps)
+        assert logits.dtype == torch.float32 and logits.stride(1) == 1
+        assert temperature.dtype == torch.float32 and streams.dtype == torch.int32 and steps.dtype == torch.int32
+        if out is None:
+            out = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
+        lib.family("sampling").call("sampling_sample", _ptr(logits), logits.shape[0], logits.shape[1],
+                                    logits.stride(0), _ptr(temperature), _ptr(streams), _ptr(steps),
+                                    int(seed) & 0xFFFFFFFFFFFFFFFF, _ptr(row_live), _ptr(out), _stream())
+        return out
+
+
+_backend = CudaOps()
+
+
+def set_backend(obj):
+    """Replaces the implementation object and returns the previous one."""
+    global _backend
+    prev, _backend = _backend, obj
+    return prev
+
+
+def backend():
+    return _backend
+
+
+def embedding(*a, **k):
+    return _backend.embedding(*a, **k)
+
+
+def gather_rows(*a, **k):
+    return _backend.gather_rows(*a, **k)
+
+
+def rmsnorm(*a, **k):
+    return _backend.rmsnorm(*a, **k)
+
+
+def swiglu(*a, **k):
+    return _backend.swiglu(*a, **k)
+
+
+def rope_kv_write(*a, **k):
+    return _backend.rope_kv_write(*a, **k)
+
+
+def advance(*a, **k):
+    return _backend.advance(*a, **k)
+
+
+def linear(*a, **k):
+    return _backend.linear(*a, **k)
+
+
+def attention(*a, **k):
+    return _backend.attention(*a, **k)
+
+
+def sample(*a, **k):
+    return _backend.sample(*a, **k)

@@ -1,0 +1,35 @@
+"""Gated feed-forward: x + Wd (silu(Wg h) * (Wu h)).
+
+Gate and up are one product over the stacked matrices, as the reference runs the two
+in one launch (transformer.cpp:1064-1066); silu(z) = z / (1 + e^-z) times up
+(cpu_ops.cpp:85-101, without its shortcuts for |z| > 20); the residual is added in the
+down product's epilogue (transformer.cpp:1072).
+"""
+import torch
+
+from .. import ops
+from .base import Part, register_part
+
+
+@register_part("feed_forward", "swiglu")
+class SwiGLU(Part):
+    category = "feed_forward"
+
+    def __init__(self, env, inner):
+        super().__init__(env)
+        self.inner = int(inner)
+        self.declare("gate_proj.weight", (self.inner, env.width))
+        self.declare("up_proj.weight", (self.inner, env.width))
+        self.declare("down_proj.weight", (env.width, self.inner))
+
+    def finalize(self):
+        super().finalize()
+        t = self.tensors
+        ws = [t.pop("gate_proj.weight"), t.pop("up_proj.weight")]
+        wdt = torch.float32 if any(w.dtype == torch.float32 for w in ws) else ws[0].dtype
+        self.w_gate_up = torch.cat([w.to(wdt) for w in ws], dim=0).contiguous()
+        self.w_down = t["down_proj.weight"]
+
+    def forward(self, h, residual, ctx):
+        gate_up = ops.linear(h, self.w_gate_up)
+        return ops.linear(ops.swiglu(gate_up), self.w_down, residual=residual)
