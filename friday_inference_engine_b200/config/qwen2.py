@@ -65,6 +65,9 @@ class Qwen2Config:
                               % v["head_dim"])
         if v["use_sliding_window"] and v["sliding_window"] is None:
             raise ConfigError("config.json: 'use_sliding_window' is true but 'sliding_window' is missing")
+        archs = d.get("architectures")
+        if isinstance(archs, list) and archs and isinstance(archs[0], str):
+            v["architecture"] = archs[0]          # another registered name may reuse these keys
         return cls(**v)
 
     def to_dict(self) -> dict:

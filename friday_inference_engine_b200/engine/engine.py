@@ -48,6 +48,7 @@ class EngineOptions:
     max_tokens: Optional[int] = None       # cache capacity in tokens; default max_batch * max_ctx (in pages)
     device: str = "cuda:0"
     prefill_chunk: int = 2048              # tokens of one sequence per pass
+    cuda_graphs: bool = True               # decode steps of generate() are captured once and replayed
     random_on_device: bool = True          # random weights are drawn on the device (fast); False: on the CPU
 
 
@@ -138,7 +139,33 @@ class Engine:
                  on_step=None):
         """prompts: lists of token ids.  Returns one Generation (tokens, finish_reason) per prompt."""
         sampler = Sampler(SamplingParams(float(temperature), int(seed)), self.device)
+
+        class Rows:
+            """The decoder behind the loop's interface: tokens in from the host, chosen ids out to the host."""
+
+            def __init__(rows, slots, first_tokens, streams, steps_done):
+                rows.dec = self.decoder(slots, first_tokens, temperature=temperature, seed=seed, streams=streams,
+                                        steps_done=steps_done)
+
+            def step(rows, tokens):
+                rows.dec.step(tokens)
+                return rows.dec.read_sampled()
+
+            def retire(rows, index):
+                rows.dec.retire(index)
+
+            def close(rows):
+                rows.dec.close()
+
         return _generate.generate(
             prompts, step=self.step, sample=sampler.sample, alloc_slot=self.alloc_slot, free_slot=self.free_slot,
             max_batch=self.max_batch, max_context=self.max_ctx, vocab_size=self.vocab_size,
-            max_new_tokens=max_new_tokens, stop_token_ids=stop_token_ids, ignore_eos=ignore_eos, on_step=on_step)
+            max_new_tokens=max_new_tokens, stop_token_ids=stop_token_ids, ignore_eos=ignore_eos, on_step=on_step,
+            decoder=Rows)
+
+    def decoder(self, slots, first_tokens, temperature=0.0, seed=0, streams=None, steps_done=None):
+        """Decoding of the sequences in `slots`, one token each per step(), from buffers that stay on the
+        device (engine/decode.py); the step is captured in a CUDA graph unless cuda_graphs is off."""
+        from .decode import DeviceDecoder
+        return DeviceDecoder(self, slots, first_tokens, temperature=temperature, seed=seed, streams=streams,
+                             steps_done=steps_done, use_graph=self.options.cuda_graphs)

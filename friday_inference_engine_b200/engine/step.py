@@ -59,6 +59,7 @@ class Stepper:
         self._scratch = None
         self._staging = []            # pinned host buffers with the event of their last copy
         self._next_staging = 0
+        self.last_upload_bytes = 0
 
     def scratch(self, n_floats, device):
         if self._scratch is None or self._scratch.numel() < n_floats:
@@ -69,6 +70,7 @@ class Stepper:
     def _upload(self, host):
         """One copy of a packed int32 array to the device, through pinned memory."""
         n = host.size
+        self.last_upload_bytes = 4 * n
         if self.device.type != "cuda":
             return torch.from_numpy(host.copy())
         if len(self._staging) < 4:

@@ -122,16 +122,18 @@ class CudaOps:
             out = torch.empty((rows, n), dtype=out_dtype, device=x.device)
         if residual is not None:
             assert residual.shape == out.shape and residual.dtype == out.dtype and residual.stride() == out.stride()
-        self._linear(x, weight, bias, residual, out)
+        self._linear_simt(x, weight, bias, residual, out)
         return out
 
-    def _linear(self, x, weight, bias, residual, out):
+    def _linear_simt(self, x, weight, bias, residual, out):
+        """The CUDA-core product: true fp32, and the fallback of bf16 for sizes the tensor-core kernel refuses."""
         rows, k = x.shape
         n = weight.shape[0]
         lib.family("gemm_simt").call(
             "gemm_simt", _ptr(x), code_of(x.dtype), _ptr(weight), code_of(weight.dtype), _ptr(out),
             code_of(out.dtype), _ptr(bias), code_of(bias.dtype) if bias is not None else 0, _ptr(residual), rows, n,
             k, x.stride(0), weight.stride(0), out.stride(0), _stream())
+        return out
 
     # -- attention --------------------------------------------------------
     def attention(self, q, q_stride, out, k_pool, v_pool, block_table, page_size, row_seq, row_pos, n_heads,

@@ -32,6 +32,20 @@ _SIGNATURES = {
 }
 
 
+_launches = 0
+
+
+def launch_count():
+    """Calls into the kernel libraries so far (each launches at least one kernel); graph replays add the
+    number of calls that were captured."""
+    return _launches
+
+
+def add_launches(n):
+    global _launches
+    _launches += n
+
+
 class KernelError(RuntimeError):
     """A kernel refused its arguments or the CUDA runtime reported an error."""
 
@@ -54,6 +68,8 @@ class Family:
             f.restype = c_int
 
     def call(self, fn, *args):
+        global _launches
+        _launches += 1
         rc = getattr(self.cdll, fn)(*args)
         if rc != 0:
             raise KernelError("%s: %s" % (fn, self._last_error().decode("utf-8", "replace")))

@@ -3,8 +3,9 @@ a JSON header (name -> dtype, shape, byte range), then the raw bytes.
 
 The reference reads GGUF (gguf_file.h:53-91) through a table name -> offset, size, shape,
 dtype (model_layout.h:17-23); this is the same idea for the format that model folders
-with a config.json use.  The file is memory-mapped; a tensor's bytes are touched only
-when it is asked for.
+with a config.json use.  The file is memory-mapped (privately: torch wants writable
+memory, the file itself is never written); a tensor's bytes are touched only when it is
+asked for.
 """
 import json
 import mmap
@@ -56,7 +57,7 @@ class SafetensorsFile:
             if hi - lo != count * torch.empty((), dtype=dtype).element_size() or self._base + hi > size:
                 raise SafetensorsError("%s: tensor '%s' has a byte range that does not match its shape" % (path, name))
             self.entries[name] = (dtype, shape, lo, hi)
-        self._mm = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_READ) if size > 0 else None
+        self._mm = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_COPY) if size > 0 else None
 
     def names(self):
         return list(self.entries)

@@ -1,0 +1,195 @@
+"""The engine against the plain implementation, however the work is cut.
+
+Every test runs twice: on the GPU with the library's kernels (marked gpu), and, where
+there is no GPU, with the kernel layer replaced by tests/ops_double.py, which checks the
+code around the kernels (pages, step function, passes, loop) and nothing of the kernels.
+"""
+import numpy as np
+import pytest
+import torch
+
+import harness
+import plain_model
+import tiny_configs
+from friday_inference_engine_b200 import Engine, ops
+
+BACKENDS = [pytest.param(("cuda:0", "float32"), marks=pytest.mark.gpu, id="gpu-f32"),
+            pytest.param(("cuda:0", "bfloat16"), marks=pytest.mark.gpu, id="gpu-bf16"),
+            pytest.param(("cpu", "float32"), id="double-f32")]
+
+
+@pytest.fixture(scope="module")
+def root(tmp_path_factory):
+    return tmp_path_factory.mktemp("models")
+
+
+@pytest.fixture(params=BACKENDS)
+def where(request):
+    device, dtype = request.param
+    prev = None
+    if device == "cpu":
+        import ops_double
+        prev = ops.set_backend(ops_double.TorchOps())
+    yield device, dtype
+    if prev is not None:
+        ops.set_backend(prev)
+
+
+def engine(root, name, where, **kw):
+    d, pm = harness.model_dir(root, name)
+    device, dtype = where
+    kw.setdefault("max_ctx", 512)
+    kw.setdefault("max_batch", 6)
+    return Engine(model_path=d, dtype=dtype, device=device, **kw), pm
+
+
+LENGTHS = {"A": [5, 11, 17, 70], "B": [1, 19, 40, 64, 97], "C": [33, 130, 200]}
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_each_request_alone_and_whole(root, where, name):
+    eng, pm = engine(root, name, where)
+    for n, p in zip(LENGTHS[name], tiny_configs.random_prompts(LENGTHS[name], eng.vocab_size, 11)):
+        s = eng.alloc_slot()
+        got = eng.step([s], [p], [list(range(n))])
+        eng.free_slot(s)
+        harness.check_logits(harness.to_np(got), plain_model.logits(pm, p), where[1], "%s whole %d" % (name, n))
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_last_32_tokens_one_by_one(root, where, name):
+    eng, pm = engine(root, name, where)
+    n = 100 if name != "C" else 180
+    (p,) = tiny_configs.random_prompts([n], eng.vocab_size, 12)
+    ref = plain_model.logits(pm, p)
+    s = eng.alloc_slot()
+    head = eng.step([s], [p[:n - 32]], [[n - 33]])
+    harness.check_logits(harness.to_np(head), ref[n - 33:n - 32], where[1], "%s prompt's end" % name)
+    for t in range(n - 32, n):
+        got = eng.step([s], [[p[t]]], [[0]])
+        harness.check_logits(harness.to_np(got), ref[t:t + 1], where[1], "%s decoded token at %d" % (name, t))
+    eng.free_slot(s)
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_unequal_batches_one_after_another_reuse_slots(root, where, name):
+    eng, pm = engine(root, name, where, max_batch=3, max_tokens=3 * 192 + 64, max_ctx=192)
+    rounds = [[9, 70, 33], [64, 2, 65], [1, 110, 40]]
+    for ri, lens in enumerate(rounds):
+        extra = [3 + 2 * i + ri for i in range(len(lens))]          # tokens decoded after the prompt: unequal
+        prompts = tiny_configs.random_prompts([a + b for a, b in zip(lens, extra)], eng.vocab_size, 20 + ri)
+        refs = [plain_model.logits(pm, p) for p in prompts]
+        slots = [eng.alloc_slot() for _ in prompts]
+        got = eng.step(slots, [p[:n] for p, n in zip(prompts, lens)], [[n - 1] for n in lens])
+        for i, n in enumerate(lens):
+            harness.check_logits(harness.to_np(got[i:i + 1]), refs[i][n - 1:n], where[1],
+                                 "%s round %d prompt %d" % (name, ri, i))
+        live = list(range(len(prompts)))
+        t = 0
+        while live:
+            got = eng.step([slots[i] for i in live], [[prompts[i][lens[i] + t]] for i in live], [[0]] * len(live))
+            for k, i in enumerate(live):
+                at = lens[i] + t
+                harness.check_logits(harness.to_np(got[k:k + 1]), refs[i][at:at + 1], where[1],
+                                     "%s round %d request %d token %d" % (name, ri, i, at))
+            t += 1
+            for i in [i for i in live if t >= extra[i]]:       # the shorter requests end earlier
+                eng.free_slot(slots[i])
+                live.remove(i)
+        assert eng.cache.slots.held_count == 0 and all(g.pages.held_count == 0 for g in eng.cache.groups)
+
+
+@pytest.mark.parametrize("name", ["B", "C"])
+def test_cut_into_passes_and_continued(root, where, name):
+    """A prompt longer than one pass, and a prompt given in two steps, equal the whole."""
+    eng, pm = engine(root, name, where, prefill_chunk=48)
+    (p,) = tiny_configs.random_prompts([150], eng.vocab_size, 13)
+    ref = plain_model.logits(pm, p)
+    s = eng.alloc_slot()
+    got = eng.step([s], [p], [[149, 0, 47, 48, 100]])
+    harness.check_logits(harness.to_np(got), ref[[149, 0, 47, 48, 100]], where[1], "in passes of 48")
+    eng.free_slot(s)
+    s = eng.alloc_slot()
+    eng.step([s], [p[:82]], [[]])
+    got = eng.step([s], [p[82:]], [[0, 67]])
+    harness.check_logits(harness.to_np(got), ref[[82, 149]], where[1], "continued at 82")
+    eng.free_slot(s)
+
+
+def test_first_tokens_of_a_sequence(root, where):
+    eng, pm = engine(root, "B", where)
+    (p,) = tiny_configs.random_prompts([6], eng.vocab_size, 14)
+    ref = plain_model.logits(pm, p)
+    s = eng.alloc_slot()
+    for t in range(6):                                       # from the very first token, one by one
+        got = eng.step([s], [[p[t]]], [[0]])
+        harness.check_logits(harness.to_np(got), ref[t:t + 1], where[1], "token %d from empty" % t)
+    eng.free_slot(s)
+
+
+def test_long_decoding(root, where):
+    eng, pm = engine(root, "C", where, max_ctx=512)
+    n = 420
+    (p,) = tiny_configs.random_prompts([n], eng.vocab_size, 15)
+    ref = plain_model.logits(pm, p)
+    s = eng.alloc_slot()
+    eng.step([s], [p[:20]], [[]])
+    for t in range(20, n):
+        got = eng.step([s], [[p[t]]], [[0]])
+        if t % 7 == 0 or t > n - 5 or t in (63, 64, 65, 127, 128, 129, 191, 192):
+            harness.check_logits(harness.to_np(got), ref[t:t + 1], where[1], "decoded token %d" % t)
+    eng.free_slot(s)
+
+
+@pytest.mark.parametrize("name, temperature", [("A", 0.0), ("B", 0.8)])
+def test_generation_through_the_entry_point(root, where, name, temperature):
+    eng, pm = engine(root, name, where, max_batch=2, max_ctx=128)
+    lens = [5, 11, 17] if name == "A" else [1, 19, 40, 64]
+    prompts = tiny_configs.random_prompts(lens, eng.vocab_size, 16)
+    steps = 8 if name == "A" else 16
+    out = eng.generate(prompts, max_new_tokens=steps, temperature=temperature, seed=7)
+    for i, (p, g) in enumerate(zip(prompts, out)):
+        assert g.finish_reason == "length" and len(g.tokens) == steps
+        # teacher forcing on the engine's own tokens: every choice must be the plain model's choice, or a
+        # near-tie of it (bfloat16 only)
+        seq = list(p)
+        for k, tok in enumerate(g.tokens):
+            row = plain_model.logits(pm, seq, at=[len(seq) - 1])[0]
+            want = plain_model.sample(row, temperature, 7, i, k)
+            if tok != want:
+                assert where[1] == "bfloat16", "request %d token %d: %d, plain chose %d" % (i, k, tok, want)
+                if temperature == 0:
+                    assert row[want] - row[tok] < 0.05 * row.std(), "not a near-tie"
+                else:
+                    _, cdf = plain_model.temperature_cdf(row, temperature)
+                    u = plain_model.uniform_for(7, i, k)
+                    edge = min(abs(cdf[min(tok, want)] - u), abs(cdf[max(tok, want) - 1] - u))
+                    assert abs(tok - want) == 1 and edge < 0.02, "not at the edge of the chosen interval"
+            seq.append(tok)
+
+
+def test_stop_tokens_end_sequences_early(root, where):
+    eng, pm = engine(root, "A", where, max_batch=3, max_ctx=128)
+    prompts = tiny_configs.random_prompts([5, 11, 17], eng.vocab_size, 17)
+    free = eng.generate(prompts, max_new_tokens=12)
+    stop = free[1].tokens[4]
+    cut = eng.generate(prompts, max_new_tokens=12, stop_token_ids=[stop])
+    for f, c in zip(free, cut):
+        if stop in f.tokens:
+            assert c.finish_reason == "stop" and c.tokens == f.tokens[:f.tokens.index(stop)]
+        else:
+            assert c.finish_reason == "length" and c.tokens == f.tokens
+    assert eng.cache.slots.held_count == 0
+
+
+def test_refusals(root, where):
+    eng, _ = engine(root, "A", where, max_ctx=64, max_batch=2)
+    from friday_inference_engine_b200.engine import StepError
+    s = eng.alloc_slot()
+    with pytest.raises(StepError):
+        eng.step([s], [[512]], [[0]])                        # outside the vocabulary: an error, never remapped
+    with pytest.raises(StepError):
+        eng.step([s], [[1] * 65], [[0]])                     # longer than the context
+    with pytest.raises(StepError):
+        eng.step([s, s], [[1], [2]], [[0], [0]])
+    eng.free_slot(s)

@@ -1,0 +1,228 @@
+"""Each kernel alone against the plain implementation's function for the same step, at
+sizes other than the test models': widths and vocabularies that are no power of two,
+head sizes in steps of 16 up to 256, odd head counts and groups, long contexts."""
+import numpy as np
+import pytest
+import torch
+
+import plain_model as pm
+from friday_inference_engine_b200 import ops
+from friday_inference_engine_b200.cache import PAGE
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def rnd(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+def f64(t):
+    return t.detach().double().cpu().numpy()
+
+
+def close(got, ref, dtype, what, fp32_tol=2e-5, bf16_rel=0.02):
+    got, ref = f64(got) if torch.is_tensor(got) else got, np.asarray(ref)
+    scale = np.abs(ref).max() + 1e-12
+    err = np.abs(got - ref).max() / scale
+    tol = fp32_tol if dtype == torch.float32 else bf16_rel
+    assert err <= tol, "%s: relative error %.3g > %.3g" % (what, err, tol)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding_and_gather(dtype):
+    table = rnd((777, 100), dtype, 0)
+    toks = torch.tensor([0, 776, 5, 5, 300], dtype=torch.int32, device=DEV)
+    assert torch.equal(ops.embedding(toks, table), table[toks.long()])
+    assert torch.equal(ops.gather_rows(toks, table), table[toks.long()])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width", [100, 3584, 5000])
+def test_rmsnorm(dtype, width):
+    x, w = rnd((7, width), dtype, 1, 3.0), rnd((width,), dtype, 2)
+    close(ops.rmsnorm(x, w, 1e-5), pm.rms_norm(f64(x), f64(w), 1e-5), dtype, "rmsnorm %d" % width)
+    w32 = w.float()                     # a weight stored in 32-bit stays so beside bf16 activations
+    close(ops.rmsnorm(x, w32, 1e-6), pm.rms_norm(f64(x), f64(w32), 1e-6), dtype, "rmsnorm fp32 weight")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu(dtype):
+    gu = rnd((9, 2 * 177), dtype, 3, 4.0)
+    ref = pm.swiglu(f64(gu)[:, :177], f64(gu)[:, 177:])
+    close(ops.swiglu(gu), ref, dtype, "swiglu")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m,n,k", [(1, 64, 64), (37, 200, 1024), (130, 96, 768), (5, 1001, 333), (64, 177, 3584)])
+def test_gemm_simt(dtype, m, n, k):
+    a, w = rnd((m, k), dtype, 4), rnd((n, k), dtype, 5, 0.05)
+    bias, res = rnd((n,), dtype, 6), rnd((m, n), dtype, 7)
+    close(ops.backend()._linear_simt(a, w, None, None, torch.empty((m, n), dtype=dtype, device=DEV)),
+          pm.linear(f64(a), f64(w)), dtype, "product")
+    ref = pm.linear(f64(a), f64(w), f64(bias)) + f64(res)
+    out = res.clone()                                     # the residual in place, as the blocks use it
+    close(ops.backend()._linear_simt(a, w, bias, out, out), ref, dtype, "product + bias + residual in place")
+    lg = ops.backend()._linear_simt(a, w, None, None, torch.empty((m, n), dtype=torch.float32, device=DEV))
+    assert lg.dtype == torch.float32
+    close(lg, pm.linear(f64(a), f64(w)), torch.float32 if dtype == torch.float32 else dtype, "fp32 output",
+          bf16_rel=1e-4)                                  # bf16 inputs are exact; only the sum is rounded (fp32)
+
+
+def test_gemm_simt_mixed_storage():
+    a, w = rnd((9, 96), torch.bfloat16, 8), rnd((50, 96), torch.float32, 9)
+    bias = rnd((50,), torch.float32, 10)
+    out = torch.empty((9, 50), dtype=torch.bfloat16, device=DEV)
+    ops.backend()._linear_simt(a, w, bias, None, out)
+    close(out, pm.linear(f64(a), f64(w), f64(bias)), torch.bfloat16, "bf16 rows, fp32 matrix")
+
+
+def paged(k, v, dtype, extra_pages=3, seed=0):
+    """Scatters [n, nkv, hd] keys and values over shuffled pages; returns pools and table."""
+    n = k.shape[0]
+    n_pages = (n + PAGE - 1) // PAGE
+    perm = torch.randperm(n_pages + extra_pages, generator=torch.Generator().manual_seed(seed))[:n_pages]
+    kp = torch.full((n_pages + extra_pages, PAGE) + tuple(k.shape[1:]), float("nan"), dtype=dtype, device=DEV)
+    vp = kp.clone()
+    for lp in range(n_pages):
+        rows = slice(lp * PAGE, min((lp + 1) * PAGE, n))
+        kp[perm[lp], : rows.stop - rows.start] = k[rows]
+        vp[perm[lp], : rows.stop - rows.start] = v[rows]
+    return kp, vp, perm.to(torch.int32).to(DEV).view(1, -1)
+
+
+class Geo:
+    def __init__(self, max_kv_len):
+        self.max_kv_len = max_kv_len
+        self._s = None
+
+    def scratch(self, n, device):
+        self._s = torch.empty((max(n, 1),), dtype=torch.float32, device=device)
+        return self._s
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,hd,n,window", [
+    (4, 2, 16, 37, None), (3, 1, 32, 130, 24), (28, 4, 128, 300, None), (6, 2, 48, 257, 80), (5, 5, 256, 70, None),
+    (8, 1, 112, 64, 64), (14, 2, 64, 1000, None)])
+def test_attention_rows_of_a_whole_sequence(dtype, nq, nkv, hd, n, window):
+    q, k, v = rnd((n, nq, hd), dtype, 11), rnd((n, nkv, hd), dtype, 12), rnd((n, nkv, hd), dtype, 13)
+    q = q * 2                                            # sharper softmax, as the reference's test does
+    ref = pm.attention(f64(q), f64(k), f64(v), window).reshape(n, nq * hd)
+    kp, vp, table = paged(k, v, dtype)
+    row_seq = torch.zeros(n, dtype=torch.int32, device=DEV)
+    row_pos = torch.arange(n, dtype=torch.int32, device=DEV)
+    out = torch.empty((n, nq * hd), dtype=dtype, device=DEV)
+    qf = q.reshape(n, nq * hd).contiguous()
+    ops.attention(qf, nq * hd, out, kp, vp, table, PAGE, row_seq, row_pos, nq, nkv, hd, window, hd ** -0.5, Geo(n))
+    close(out, ref, dtype, "whole sequence")
+    # the last row alone, as decoding sees it (few rows, long context: the keys are split)
+    out1 = torch.empty((1, nq * hd), dtype=dtype, device=DEV)
+    ops.attention(qf[n - 1:], nq * hd, out1, kp, vp, table, PAGE, row_seq[:1], row_pos[n - 1:], nq, nkv, hd, window,
+                  hd ** -0.5, Geo(n))
+    close(out1, ref[n - 1:], dtype, "last row alone")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_one_far_key(dtype):
+    """One key among a thousand matches the query; its value must come out."""
+    nq, nkv, hd, n = 4, 2, 64, 1000
+    k = rnd((n, nkv, hd), dtype, 14, 0.1)
+    v = rnd((n, nkv, hd), dtype, 15)
+    q = rnd((1, nq, hd), dtype, 16, 0.1)
+    far = 3
+    k[far, :, :] = 0
+    k[far, :, 0] = 8.0
+    q[0, :, 0] = 8.0 * (hd ** 0.5)                        # score 64 for the far key, about 0 elsewhere
+    kp, vp, table = paged(k, v, dtype)
+    out = torch.empty((1, nq * hd), dtype=dtype, device=DEV)
+    pos = torch.tensor([n - 1], dtype=torch.int32, device=DEV)
+    ops.attention(q.reshape(1, -1).contiguous(), nq * hd, out, kp, vp, table, PAGE, torch.zeros(1, dtype=torch.int32, device=DEV),
+                  pos, nq, nkv, hd, None, hd ** -0.5, Geo(n))
+    want = f64(v)[far].repeat(nq // nkv, axis=0).reshape(-1)
+    close(out[0], want, dtype, "the far key's value", fp32_tol=1e-4)
+    # with a window that ends one short of it, it must NOT be seen
+    ops.attention(q.reshape(1, -1).contiguous(), nq * hd, out, kp, vp, table, PAGE, torch.zeros(1, dtype=torch.int32, device=DEV),
+                  pos, nq, nkv, hd, n - 1 - far, hd ** -0.5, Geo(n))
+    assert np.abs(f64(out[0]) - want).max() > 0.5
+    ops.attention(q.reshape(1, -1).contiguous(), nq * hd, out, kp, vp, table, PAGE, torch.zeros(1, dtype=torch.int32, device=DEV),
+                  pos, nq, nkv, hd, n - far, hd ** -0.5, Geo(n))
+    close(out[0], want, dtype, "the window's first key", fp32_tol=1e-4)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_rope_and_cache_write(dtype):
+    nq, nkv, hd = 5, 2, 48
+    rows = 10
+    qkv = rnd((rows, (nq + 2 * nkv) * hd), dtype, 17)
+    before = f64(qkv).reshape(rows, nq + 2 * nkv, hd)
+    row_seq = torch.tensor([0, 0, 0, 1, 1, -1, 1, 0, 0, 0], dtype=torch.int32, device=DEV)
+    row_pos = torch.tensor([62, 63, 64, 0, 1, 0, 2, 65, 66, 200], dtype=torch.int32, device=DEV)
+    table = torch.tensor([[3, 1, 7, 5], [2, 0, -1, -1]], dtype=torch.int32, device=DEV)
+    kp = torch.zeros((8, PAGE, nkv, hd), dtype=dtype, device=DEV)
+    vp = torch.zeros_like(kp)
+    denom = torch.from_numpy(np.power(np.float32(50000.0), np.float32(2.0) * np.arange(hd // 2, dtype=np.float32)
+                                      / np.float32(hd)).astype(np.float32)).to(DEV)
+    ops.rope_kv_write(qkv, row_seq, row_pos, denom, hd, nq, nkv, hd, kp, vp, table, PAGE)
+    after = f64(qkv).reshape(rows, nq + 2 * nkv, hd)
+    tbl = table.cpu().numpy()
+    for r in range(rows):
+        if int(row_seq[r]) < 0:
+            assert np.array_equal(after[r], before[r])      # a padding row is left alone
+            continue
+        p = int(row_pos[r])
+        ref = pm.rope_neox(before[r:r + 1, : nq + nkv], [p], 50000.0)[0]
+        close(after[r, : nq + nkv], ref, dtype, "rotated q and k, row %d" % r)
+        assert np.array_equal(after[r, nq + nkv:], before[r, nq + nkv:])          # v is untouched
+        page = tbl[int(row_seq[r]), p // PAGE]
+        assert np.array_equal(f64(kp[page, p % PAGE]), after[r, nq:nq + nkv])
+        assert np.array_equal(f64(vp[page, p % PAGE]), after[r, nq + nkv:])
+    assert int((kp != 0).any(dim=-1).any(dim=-1).sum()) == rows - 1                # nothing else was written
+
+
+def test_sampling_greedy_rule():
+    x = torch.tensor([[1.0, 3.0, 3.0, 2.0], [float("nan"), float("inf"), 1.0, -float("inf")],
+                      [-5.0, -5.0, -5.0, -5.0]], device=DEV)
+    t = torch.zeros(3, device=DEV)
+    z = torch.zeros(3, dtype=torch.int32, device=DEV)
+    assert ops.sample(x, t, z, z, 0).tolist() == [1, 2, 0]
+
+
+@pytest.mark.parametrize("vocab", [50, 1000, 152064])
+def test_sampling_matches_plain_draws(vocab):
+    rows = 24
+    logits = rnd((rows, vocab), torch.float32, 18, 3.0)
+    temp = torch.full((rows,), 0.8, device=DEV)
+    streams = torch.arange(rows, dtype=torch.int32, device=DEV) % 5
+    steps = torch.arange(rows, dtype=torch.int32, device=DEV) * 3
+    got = ops.sample(logits, temp, streams, steps, 7).tolist()
+    host = logits.cpu().numpy()
+    exact = 0
+    for r in range(rows):
+        want = pm.sample(host[r], 0.8, 7, int(streams[r]), int(steps[r]))
+        if got[r] == want:
+            exact += 1
+            continue
+        # fp32 running sums may move an interval's edge by a rounding: then u must sit on that edge
+        _, cdf = pm.temperature_cdf(host[r], 0.8)
+        u = pm.uniform_for(7, int(streams[r]), int(steps[r]))
+        lo, hi = min(got[r], want), max(got[r], want)
+        assert abs(cdf[lo] - u) < 1e-5 and cdf[hi - 1] - cdf[lo] < 1e-5, "row %d: %d, plain %d" % (r, got[r], want)
+    assert exact >= rows - 2
+    # greedy on the same rows
+    g = ops.sample(logits, torch.zeros(rows, device=DEV), streams, steps, 7).tolist()
+    assert g == [pm.greedy(host[r]) for r in range(rows)]
+
+
+def test_sampling_draws_do_not_depend_on_the_batch():
+    logits = rnd((6, 300), torch.float32, 19, 2.0)
+    temp = torch.full((6,), 1.3, device=DEV)
+    streams = torch.tensor([4, 9, 1, 0, 7, 2], dtype=torch.int32, device=DEV)
+    steps = torch.tensor([0, 5, 2, 2, 9, 1], dtype=torch.int32, device=DEV)
+    whole = ops.sample(logits, temp, streams, steps, 3).tolist()
+    for r in (0, 3, 5):
+        alone = ops.sample(logits[r:r + 1].contiguous(), temp[:1], streams[r:r + 1].contiguous(),
+                           steps[r:r + 1].contiguous(), 3).tolist()
+        assert alone == [whole[r]]
