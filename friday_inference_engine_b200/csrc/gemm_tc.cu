@@ -1,0 +1,501 @@
+// bf16 matrix product on the 5th-generation tensor cores (sm_100a):
+//
+//     out[m][n] = sum_k x[m][k] * w[n][k]  (+ bias[n]) (+ residual[m][n]),  fp32 sums
+//
+// x: activations [rows][k], w: projection weights [out][in]; both are row-major with k
+// innermost ("K-major"), which is the layout tcgen05.mma takes for both operands, so
+// nothing is transposed or copied.  One persistent kernel per launch:
+//
+//   warp 0      TMA producer: cp.async.bulk.tensor.2d loads of 64-element (128-byte) wide
+//               k-slices of both operands into a ring of shared-memory stages, 128-byte
+//               swizzle, completion on an mbarrier per stage.  No cluster multicast.
+//   warp 1      allocates tensor memory, then one lane issues tcgen05.mma
+//               (cta_group::1, kind::f16, M=128, N=BN, K=16) from shared-memory
+//               descriptors; tcgen05.commit hands stages back to the producer and
+//               accumulators on to the epilogue.
+//   warps 2-5   epilogue: tcgen05.ld of the fp32 accumulators (TMEM lanes = rows of the
+//               tile), bias, residual, rounding, stores.  Two accumulator buffers in
+//               TMEM let the epilogue of one tile overlap the products of the next.
+//
+// The operand that feeds the M side of the instruction ("P", tiles of 128 rows) and the
+// one that feeds its N side ("Q", tiles of BN rows) are chosen by the launcher:
+//   many rows (prompts):   P = x, Q = w, BN = 128 or 256;
+//   few rows (decoding):   P = w, Q = x, BN = 16/32/64 >= rows: every weight is streamed
+//                          once at full width, the handful of activations ride along, and
+//                          the epilogue writes the tile transposed.
+// When a shape has fewer tiles than the GPU has SMs (decoding against a [4608 x 3584]
+// matrix is 36 tiles), k is cut into `splits` ranges; each CTA writes its partial tile to
+// a scratch buffer, and the CTA that arrives last for a tile (a counter per tile) sums
+// the partials in split order and runs the epilogue.  The sum order is fixed, so results
+// do not depend on which CTA came last.
+//
+// Replaces the reference's int8 mma.sync GEMM (prefill_kernels.cu:173-327) and its dp4a
+// GEMVs (hpc_k_quants.cu:445-681), with the same epilogue contract (bias, then
+// residual, in place allowed: prefill_kernels.cu:156-171, hpc_k_quants.cu:404-437).
+//
+// Every wait on an mbarrier is bounded: after about two seconds the waiting thread
+// records a code in `status` and all roles leave their loops, free TMEM and return.
+#include <cuda.h>
+
+#include "common.cuh"
+
+FR_EXPORT const char* gemm_tc_last_error() { return fr_error_text; }
+
+namespace {
+
+constexpr int TILE_P = 128;          // rows of P per tile = M of the instruction
+constexpr int TILE_K = 64;           // bf16 elements per stage along k = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int P_BYTES = TILE_P * TILE_K * 2;
+constexpr int THREADS = 192;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // a wait gives up after two seconds
+
+struct GemmParams {
+    void* out;
+    const void* bias;
+    const void* residual;
+    float* ws;          // [tiles][splits][128][BN] partial tiles when splits > 1
+    int* counters;      // [tiles], zero between launches
+    int* status;        // 0, or a code when a wait gave up
+    int p_rows, q_rows, ldo, out_dtype, bias_dtype, swapped;
+    int tiles_p, tiles_q, splits, kb_total, kb_per;
+};
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait; false (and a code in *status) if the barrier did not complete in time.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
+    if (mbar_try(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_try(bar, parity)) return true;
+        if ((it & 63u) == 0 && global_ns() - t0 > WAIT_LIMIT_NS) break;
+    }
+    atomicCAS(status, 0, code);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                       uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows of 128 bytes,
+// groups of 8 rows 1024 bytes apart.  Bits: [0,14) address >> 4; [16,30) leading byte
+// offset >> 4 (unused with this swizzle); [32,46) stride byte offset >> 4; [46,48) = 1
+// (descriptor version of sm_100); [61,64) = 2 (128-byte swizzle).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// Instruction descriptor of kind::f16: fp32 accumulate (bit 4), bf16 A (bit 7) and B (bit 10), both
+// K-major (bits 15, 16 clear), N >> 3 at bit 17, M >> 4 at bit 24.
+__host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ float bias_at(const GemmParams& p, int i) {
+    return p.bias_dtype == FR_F32 ? ((const float*)p.bias)[i] : __bfloat162float(((const __nv_bfloat16*)p.bias)[i]);
+}
+
+// Bias, residual, rounding and store of 16 consecutive q-columns of P-row gi.
+__device__ __forceinline__ void finish16(const GemmParams& p, int gi, int gj0, float (&v)[16]) {
+    if (gi >= p.p_rows) return;
+    if (!p.swapped) {
+        // out[gi][gj0 .. gj0+15]
+        const size_t base = (size_t)gi * p.ldo + gj0;
+        const bool whole = gj0 + 16 <= p.q_rows;
+        if (p.out_dtype == FR_BF16) {
+            __nv_bfloat16* o = (__nv_bfloat16*)p.out + base;
+            const __nv_bfloat16* r = p.residual ? (const __nv_bfloat16*)p.residual + base : nullptr;
+            if (whole && (p.ldo % 8 == 0) && (((uintptr_t)p.out & 15) == 0) &&
+                (r == nullptr || ((uintptr_t)p.residual & 15) == 0)) {
+                if (p.bias)
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] += bias_at(p, gj0 + j);
+                if (r) {
+                    uint4 rr[2] = {((const uint4*)r)[0], ((const uint4*)r)[1]};
+                    const __nv_bfloat16* rb = (const __nv_bfloat16*)rr;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] += __bfloat162float(rb[j]);
+                }
+                uint4 pk[2];
+                __nv_bfloat162* ph = (__nv_bfloat162*)pk;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) ph[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                ((uint4*)o)[0] = pk[0];
+                ((uint4*)o)[1] = pk[1];
+            } else {
+                for (int j = 0; j < 16 && gj0 + j < p.q_rows; ++j) {
+                    float x = v[j];
+                    if (p.bias) x += bias_at(p, gj0 + j);
+                    if (r) x += __bfloat162float(r[j]);
+                    o[j] = __float2bfloat16_rn(x);
+                }
+            }
+        } else {
+            float* o = (float*)p.out + base;
+            const float* r = p.residual ? (const float*)p.residual + base : nullptr;
+            if (whole && (p.ldo % 4 == 0) && (((uintptr_t)p.out & 15) == 0) && r == nullptr) {
+                if (p.bias)
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] += bias_at(p, gj0 + j);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) ((float4*)o)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            } else {
+                for (int j = 0; j < 16 && gj0 + j < p.q_rows; ++j) {
+                    float x = v[j];
+                    if (p.bias) x += bias_at(p, gj0 + j);
+                    if (r) x += r[j];
+                    o[j] = x;
+                }
+            }
+        }
+    } else {
+        // transposed: out[gj][gi]; bias goes with gi
+        const float b = p.bias ? bias_at(p, gi) : 0.f;
+        for (int j = 0; j < 16 && gj0 + j < p.q_rows; ++j) {
+            const size_t at = (size_t)(gj0 + j) * p.ldo + gi;
+            float x = v[j] + b;
+            if (p.out_dtype == FR_BF16) {
+                if (p.residual) x += __bfloat162float(((const __nv_bfloat16*)p.residual)[at]);
+                ((__nv_bfloat16*)p.out)[at] = __float2bfloat16_rn(x);
+            } else {
+                if (p.residual) x += ((const float*)p.residual)[at];
+                ((float*)p.out)[at] = x;
+            }
+        }
+    }
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
+               const GemmParams p) {
+    constexpr int Q_BYTES = BN * TILE_K * 2;
+    constexpr int STAGE_BYTES = P_BYTES + Q_BYTES;
+    constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);
+    // bars: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
+    int* flags = (int*)(tmem_slot + 1);      // flags[0]: this CTA came last for the tile (split-k)
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
+    const uint32_t accf0 = smem_u32(bars + 2 * STAGES), acce0 = smem_u32(bars + 2 * STAGES + 2);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(accf0 + 8 * a, 1);
+            mbar_init(acce0 + 8 * a, 4);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"((uint32_t)TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int n_tiles = p.tiles_p * p.tiles_q;
+    const int n_items = n_tiles * p.splits;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_p) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
+                const int tile = w / p.splits, split = w - tile * p.splits;
+                const int q_blk = tile / p.tiles_p, p_blk = tile - q_blk * p.tiles_p;
+                const int kb0 = split * p.kb_per, kb1 = min(kb0 + p.kb_per, p.kb_total);
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!(ok = mbar_wait(empty0 + 8 * stage, phase ^ 1, p.status, 1))) break;
+                    const uint32_t dst = smem_u32(smem + stage * STAGE_BYTES);
+                    mbar_expect_tx(full0 + 8 * stage, STAGE_BYTES);
+                    tma_load_2d(dst, &map_p, kb * TILE_K, p_blk * TILE_P, full0 + 8 * stage);
+                    tma_load_2d(dst + P_BYTES, &map_q, kb * TILE_K, q_blk * BN, full0 + 8 * stage);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc(TILE_P, BN);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            int it = 0;
+            for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x, ++it) {
+                const int tile = w / p.splits, split = w - tile * p.splits;
+                const int kb0 = split * p.kb_per, kb1 = min(kb0 + p.kb_per, p.kb_total);
+                const int a = it & 1;
+                const uint32_t acc_phase = (it >> 1) & 1;
+                if (!(ok = mbar_wait(acce0 + 8 * a, acc_phase ^ 1, p.status, 2))) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + a * BN;
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!(ok = mbar_wait(full0 + 8 * stage, phase, p.status, 3))) break;
+                    tc_fence_after();
+                    const uint32_t pa = smem_u32(smem + stage * STAGE_BYTES);
+                    const uint64_t da = smem_desc(pa), db = smem_desc(pa + P_BYTES);
+#pragma unroll
+                    for (int k = 0; k < TILE_K / UMMA_K; ++k)
+                        tc_mma(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                    tc_commit(empty0 + 8 * stage);        // the stage is free once these products are done
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (ok) tc_commit(accf0 + 8 * a);         // the accumulator is complete
+            }
+        }
+    } else {
+        const int quarter = warp & 3;                      // TMEM lanes this warp may read: 32*quarter ..
+        const int i_local = quarter * 32 + lane;
+        const int et = threadIdx.x - 64;                   // 0..127 among the epilogue threads
+        bool ok = true;
+        int it = 0;
+        for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x, ++it) {
+            const int tile = w / p.splits, split = w - tile * p.splits;
+            const int q_blk = tile / p.tiles_p, p_blk = tile - q_blk * p.tiles_p;
+            const int a = it & 1;
+            const uint32_t acc_phase = (it >> 1) & 1;
+            if (!(ok = mbar_wait(accf0 + 8 * a, acc_phase, p.status, 4))) break;
+            tc_fence_after();
+            const int gi = p_blk * TILE_P + i_local;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + a * BN;
+            float* part = p.splits > 1 ? p.ws + ((size_t)w * TILE_P + i_local) * BN : nullptr;
+#pragma unroll 1
+            for (int c = 0; c < BN / 16; ++c) {
+                uint32_t r[16];
+                tc_ld16(taddr + c * 16, r);
+                tc_ld_wait();
+                float v[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+                if (part == nullptr) {
+                    finish16(p, gi, q_blk * BN + c * 16, v);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        ((float4*)(part + c * 16))[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acce0 + 8 * a);     // the accumulator may be overwritten
+            if (p.splits > 1) {
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (et == 0) flags[0] = atomicAdd(p.counters + tile, 1) == p.splits - 1;
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (flags[0]) {
+                    __threadfence();
+                    const float* first = p.ws + ((size_t)tile * p.splits * TILE_P + i_local) * BN;
+#pragma unroll 1
+                    for (int c = 0; c < BN / 16; ++c) {
+                        float v[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] = 0.f;
+                        for (int s = 0; s < p.splits; ++s) {
+                            const float4* src = (const float4*)(first + (size_t)s * TILE_P * BN + c * 16);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const float4 x = __ldcg(src + j);
+                                v[4 * j] += x.x; v[4 * j + 1] += x.y; v[4 * j + 2] += x.z; v[4 * j + 3] += x.w;
+                            }
+                        }
+                        finish16(p, gi, q_blk * BN + c * 16, v);
+                    }
+                    if (et == 0) p.counters[tile] = 0;     // ready for the next launch
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
+                     : "memory");
+    }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+    static EncodeTiled fn = nullptr;
+    if (fn == nullptr) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)ptr;
+    }
+    return fn;
+}
+
+// [rows][k] bf16, row stride ld elements; box = 64 elements of k by box_rows rows.
+int make_map(CUtensorMap* map, const void* base, int rows, int k, int ld, int box_rows) {
+    EncodeTiled enc = encode_fn();
+    if (enc == nullptr) FR_REFUSE("gemm_tc: the driver does not offer cuTensorMapEncodeTiled");
+    cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)TILE_K, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) FR_REFUSE("gemm_tc: cuTensorMapEncodeTiled failed with %d (rows %d, k %d, ld %d)", (int)r, rows, k, ld);
+    return FR_OK;
+}
+
+template <int BN, int STAGES>
+int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmParams& p, int grid, cudaStream_t stream) {
+    constexpr int smem = STAGES * (P_BYTES + BN * TILE_K * 2) + 1024 + 256;
+    static bool configured = false;
+    if (!configured) {
+        FR_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        configured = true;
+    }
+    gemm_tc_kernel<BN, STAGES><<<grid, THREADS, smem, stream>>>(mp, mq, p);
+    FR_CHECK_LAUNCH("gemm_tc");
+    return FR_OK;
+}
+
+}  // namespace
+
+// What the launcher would choose for a shape: fills plan[0..3] = {swapped, BN, splits, scratch floats needed}
+// and plan[4] = counters needed.  bn / splits / swap < 0 let the heuristics decide.
+FR_EXPORT int gemm_tc_plan(int m, int n, int k, int sm_count, int swap, int bn, int splits, long long* plan) {
+    if (swap < 0) swap = m <= 64 ? 1 : 0;
+    const int q_rows = swap ? m : n, p_rows = swap ? n : m;
+    if (bn <= 0) {
+        if (swap) bn = q_rows <= 16 ? 16 : q_rows <= 32 ? 32 : 64;
+        else bn = q_rows >= 256 ? 256 : q_rows > 64 ? 128 : 64;
+    }
+    const int tiles = ((p_rows + TILE_P - 1) / TILE_P) * ((q_rows + bn - 1) / bn);
+    const int kb_total = (k + TILE_K - 1) / TILE_K;
+    if (splits <= 0) {
+        splits = 1;
+        if (tiles * 2 <= sm_count) {
+            splits = sm_count / tiles;
+            if (splits > kb_total / 4) splits = kb_total / 4;      // at least four k-slices per split
+            if (splits < 1) splits = 1;
+        }
+    }
+    if (splits > kb_total) splits = kb_total;
+    const int kb_per = (kb_total + splits - 1) / splits;
+    splits = (kb_total + kb_per - 1) / kb_per;                     // no empty split
+    plan[0] = swap; plan[1] = bn; plan[2] = splits;
+    plan[3] = splits > 1 ? (long long)tiles * splits * TILE_P * bn : 0;
+    plan[4] = splits > 1 ? tiles : 0;
+    return FR_OK;
+}
+
+// x [m][k] (row stride lda), w [n][k] (ldw): bf16.  out, residual [m][n] (ldo), bf16 or fp32 (out_dtype).
+// scratch/counters/status: device buffers of the caller; counters must be zero on entry and are zero on return.
+FR_EXPORT int gemm_tc(const void* x, const void* w, void* out, int out_dtype, const void* bias, int bias_dtype,
+                      const void* residual, int m, int n, int k, int lda, int ldw, int ldo, float* scratch,
+                      long long scratch_floats, int* counters, int n_counters, int* status, int sm_count, int swap,
+                      int bn, int splits, cudaStream_t stream) {
+    if (m <= 0 || n <= 0) return FR_OK;
+    if (k <= 0 || k % 8 || lda % 8 || ldw % 8)
+        FR_REFUSE("gemm_tc: k = %d and the row strides (%d, %d) must be multiples of 8 (16-byte rows for TMA)", k, lda, ldw);
+    if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) FR_REFUSE("gemm_tc: operands must be 16-byte aligned");
+    if (status == nullptr) FR_REFUSE("gemm_tc: a status word is needed");
+    long long plan[5];
+    gemm_tc_plan(m, n, k, sm_count, swap, bn, splits, plan);
+    swap = (int)plan[0]; bn = (int)plan[1]; splits = (int)plan[2];
+    if (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256) FR_REFUSE("gemm_tc: tile width %d", bn);
+    if (plan[3] > scratch_floats || plan[4] > n_counters)
+        FR_REFUSE("gemm_tc: split-k needs %lld scratch floats and %lld counters, given %lld and %d", plan[3], plan[4],
+                  scratch_floats, n_counters);
+    GemmParams p;
+    p.out = out; p.bias = bias; p.residual = residual; p.ws = scratch; p.counters = counters; p.status = status;
+    p.p_rows = swap ? n : m; p.q_rows = swap ? m : n; p.ldo = ldo; p.out_dtype = out_dtype; p.bias_dtype = bias_dtype;
+    p.swapped = swap;
+    p.tiles_p = (p.p_rows + TILE_P - 1) / TILE_P; p.tiles_q = (p.q_rows + bn - 1) / bn;
+    p.splits = splits; p.kb_total = (k + TILE_K - 1) / TILE_K; p.kb_per = (p.kb_total + splits - 1) / splits;
+    CUtensorMap mp, mq;
+    int rc = swap ? make_map(&mp, w, n, k, ldw, TILE_P) : make_map(&mp, x, m, k, lda, TILE_P);
+    if (rc) return rc;
+    rc = swap ? make_map(&mq, x, m, k, lda, bn) : make_map(&mq, w, n, k, ldw, bn);
+    if (rc) return rc;
+    const int items = p.tiles_p * p.tiles_q * splits;
+    const int grid = items < sm_count ? items : sm_count;
+    switch (bn) {
+        case 16: return launch<16, 10>(mp, mq, p, grid, stream);
+        case 32: return launch<32, 10>(mp, mq, p, grid, stream);
+        case 64: return launch<64, 8>(mp, mq, p, grid, stream);
+        case 128: return launch<128, 6>(mp, mq, p, grid, stream);
+        default: return launch<256, 4>(mp, mq, p, grid, stream);
+    }
+}

@@ -127,12 +127,16 @@ class Engine:
 
     def step_token(self, token, pos):
         """One token at position `pos`; returns its logits as a host fp32 tensor [vocab]."""
-        return self.step([self._single_at(pos)], [[int(token)]], [[0]])[0].cpu()
+        out = self.step([self._single_at(pos)], [[int(token)]], [[0]])[0].cpu()
+        self.check()
+        return out
 
     def prefill(self, tokens, pos=0):
         """tokens at positions pos .. pos+n-1; returns the logits of the last one (host)."""
         tokens = [int(t) for t in tokens]
-        return self.step([self._single_at(pos)], [tokens], [[len(tokens) - 1]])[0].cpu()
+        out = self.step([self._single_at(pos)], [tokens], [[len(tokens) - 1]])[0].cpu()
+        self.check()
+        return out
 
     # -- generation ------------------------------------------------------------
     def generate(self, prompts, max_new_tokens=100, temperature=0.0, seed=0, stop_token_ids=(), ignore_eos=False,
@@ -157,11 +161,20 @@ class Engine:
             def close(rows):
                 rows.dec.close()
 
-        return _generate.generate(
+        out = _generate.generate(
             prompts, step=self.step, sample=sampler.sample, alloc_slot=self.alloc_slot, free_slot=self.free_slot,
             max_batch=self.max_batch, max_context=self.max_ctx, vocab_size=self.vocab_size,
             max_new_tokens=max_new_tokens, stop_token_ids=stop_token_ids, ignore_eos=ignore_eos, on_step=on_step,
             decoder=Rows)
+        self.check()
+        return out
+
+    def check(self):
+        """Raises if a kernel reported that it gave up on a wait (its results would be invalid)."""
+        from .. import ops
+        be = ops.backend()
+        if hasattr(be, "check_status"):
+            be.check_status()
 
     def decoder(self, slots, first_tokens, temperature=0.0, seed=0, streams=None, steps_done=None):
         """Decoding of the sequences in `slots`, one token each per step(), from buffers that stay on the

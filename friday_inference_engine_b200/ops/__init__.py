@@ -49,6 +49,9 @@ class CudaOps:
 
     name = "cuda"
 
+    def __init__(self):
+        self._tc = {}
+
     # -- row-wise ---------------------------------------------------------
     def embedding(self, tokens, table):
         _need_cuda(tokens, table)
@@ -122,8 +125,55 @@ class CudaOps:
             out = torch.empty((rows, n), dtype=out_dtype, device=x.device)
         if residual is not None:
             assert residual.shape == out.shape and residual.dtype == out.dtype and residual.stride() == out.stride()
+        if self.tensor_core_ok(x, weight, out, residual):
+            return self._linear_tc(x, weight, bias, residual, out)
         self._linear_simt(x, weight, bias, residual, out)
         return out
+
+    # Scratch of the tensor-core product (partial tiles of split-k), its tile counters and the word in which
+    # a kernel records a wait that gave up: one set per device, made once, so that captured graphs keep
+    # their addresses.  At most one CTA per SM holds a partial tile of 128 x 256 floats.
+    _TC_SCRATCH_FLOATS = 148 * 128 * 256
+    _TC_COUNTERS = 4096
+
+    def _tc_buffers(self, device):
+        bufs = self._tc.get(device)
+        if bufs is None:
+            props = torch.cuda.get_device_properties(device)
+            bufs = self._tc[device] = (
+                torch.empty((self._TC_SCRATCH_FLOATS,), dtype=torch.float32, device=device),
+                torch.zeros((self._TC_COUNTERS,), dtype=torch.int32, device=device),
+                torch.zeros((4,), dtype=torch.int32, device=device),
+                props.multi_processor_count)
+        return bufs
+
+    @staticmethod
+    def tensor_core_ok(x, weight, out, residual):
+        """The tensor-core kernel takes bf16 operands whose rows start on 16-byte boundaries."""
+        return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+                and out.dtype in (torch.bfloat16, torch.float32)
+                and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0
+                and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+    def _linear_tc(self, x, weight, bias, residual, out, swap=-1, bn=-1, splits=-1):
+        scratch, counters, status, sms = self._tc_buffers(x.device)
+        rows, k = x.shape
+        lib.family("gemm_tc").call(
+            "gemm_tc", _ptr(x), _ptr(weight), _ptr(out), code_of(out.dtype), _ptr(bias),
+            code_of(bias.dtype) if bias is not None else 0, _ptr(residual), rows, weight.shape[0], k, x.stride(0),
+            weight.stride(0), out.stride(0), _ptr(scratch), scratch.numel(), _ptr(counters), counters.numel(),
+            _ptr(status), sms, swap, bn, splits, _stream())
+        return out
+
+    def check_status(self):
+        """Raises if a kernel recorded that one of its waits gave up (reads one word per device; call it
+        where the host waits for the device anyway)."""
+        for device, bufs in self._tc.items():
+            code = int(bufs[2][0].item())
+            if code:
+                bufs[2].zero_()
+                raise KernelError("a tensor-core kernel on %s gave up waiting (code %d: 1 producer, 2 accumulator, "
+                                  "3 operands, 4 epilogue); its results are not valid" % (device, code))
 
     def _linear_simt(self, x, weight, bias, residual, out):
         """The CUDA-core product: true fp32, and the fallback of bf16 for sizes the tensor-core kernel refuses."""

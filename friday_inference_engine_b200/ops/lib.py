@@ -23,6 +23,10 @@ _SIGNATURES = {
     "gemm_simt": {
         "gemm_simt": [P, I, P, I, P, I, P, I, P, I, I, I, I, I, I, P],
     },
+    "gemm_tc": {
+        "gemm_tc": [P, P, P, I, P, I, P, I, I, I, I, I, I, P, c_longlong, P, I, P, I, I, I, I, P],
+        "gemm_tc_plan": [I, I, I, I, I, I, I, P],
+    },
     "attention_simt": {
         "attention_simt": [P, I, P, P, P, P, I, I, P, P, I, I, I, I, I, F, I, P, I, P],
     },

@@ -226,3 +226,61 @@ def test_sampling_draws_do_not_depend_on_the_batch():
         alone = ops.sample(logits[r:r + 1].contiguous(), temp[:1], streams[r:r + 1].contiguous(),
                            steps[r:r + 1].contiguous(), 3).tolist()
         assert alone == [whole[r]]
+
+
+# ------------------------------------------------------------------ tensor-core product
+TC_SHAPES = [
+    # m, n, k: rows of activations, out features, in features
+    (1, 128, 64), (1, 4608, 3584), (8, 3584, 3584), (7, 1001, 328), (16, 777, 96), (17, 256, 512), (33, 200, 1024),
+    (64, 3584, 18944), (64, 130, 72), (65, 96, 768), (130, 96, 768), (200, 1001, 328), (257, 300, 64),
+    (512, 4608, 3584), (2048, 512, 1024),
+]
+
+
+@pytest.mark.parametrize("m,n,k", TC_SHAPES)
+def test_gemm_tensor_core(m, n, k):
+    dt = torch.bfloat16
+    a, w = rnd((m, k), dt, 20), rnd((n, k), dt, 21, 0.05)
+    bias, res = rnd((n,), dt, 22), rnd((m, n), dt, 23)
+    ref0 = pm.linear(f64(a), f64(w))
+    be = ops.backend()
+    assert be.tensor_core_ok(a, w, res, res)
+    # fp32 output shows the sums themselves: inputs are exact in bf16, only the order of the fp32 sum differs
+    lg = be._linear_tc(a, w, None, None, torch.empty((m, n), dtype=torch.float32, device=DEV))
+    close(lg, ref0, torch.float32, "tensor-core product, fp32 out", fp32_tol=3e-5)
+    out = be._linear_tc(a, w, None, None, torch.empty((m, n), dtype=dt, device=DEV))
+    close(out, ref0, dt, "tensor-core product", bf16_rel=0.01)
+    ref = pm.linear(f64(a), f64(w), f64(bias)) + f64(res)
+    io = res.clone()
+    close(be._linear_tc(a, w, bias, io, io), ref, dt, "bias + residual in place", bf16_rel=0.01)
+    io = res.clone()
+    close(be._linear_tc(a, w, bias.float(), io, io), ref, dt, "fp32 bias", bf16_rel=0.01)
+    be.check_status()
+
+
+@pytest.mark.parametrize("m,n,k,swap,bn,splits", [
+    (8, 512, 1024, 1, 16, 1), (8, 512, 1024, 1, 16, 4), (8, 512, 1024, 1, 64, 16), (40, 300, 2048, 1, 64, 3),
+    (40, 300, 2048, 0, 64, 1), (300, 300, 2048, 0, 128, 2), (300, 700, 2048, 0, 256, 5), (128, 256, 4096, 0, 256, 64),
+    (100, 100, 64, 0, 128, 1), (5, 130, 72, 0, 256, 1), (300, 40, 2048, 1, 32, 1)])
+def test_gemm_tensor_core_every_tiling(m, n, k, swap, bn, splits):
+    """Orientation, tile width and split-k are choices of the launcher; each must give the same product."""
+    dt = torch.bfloat16
+    a, w = rnd((m, k), dt, 24), rnd((n, k), dt, 25, 0.05)
+    bias, res = rnd((n,), dt, 26), rnd((m, n), torch.float32, 27)
+    ref = pm.linear(f64(a), f64(w), f64(bias)) + f64(res)
+    be = ops.backend()
+    for _ in range(2):                                       # twice: the tile counters must be back at zero
+        io = res.clone()
+        got = be._linear_tc(a, w, bias, io, io, swap=swap, bn=bn, splits=splits)
+        close(got, ref, torch.float32, "swap %d bn %d splits %d" % (swap, bn, splits), fp32_tol=3e-5)
+    be.check_status()
+
+
+def test_linear_chooses_a_kernel_that_can_do_the_shape():
+    dt = torch.bfloat16
+    a, w = rnd((9, 100), dt, 28), rnd((50, 100), dt, 29)     # k = 100: rows are not 16-byte multiples
+    assert not ops.backend().tensor_core_ok(a, w, a, None)
+    close(ops.linear(a, w), pm.linear(f64(a), f64(w)), dt, "falls back to CUDA cores")
+    a, w = rnd((9, 104), dt, 28), rnd((50, 104), dt, 29)
+    assert ops.backend().tensor_core_ok(a, w, a, None)
+    close(ops.linear(a, w), pm.linear(f64(a), f64(w)), dt, "tensor cores")

@@ -81,9 +81,9 @@ def test_attention_part(dtype, window):
     spec = PartSpec("gqa_attention", {"n_heads": nq, "n_kv_heads": nkv, "head_dim": hd, "window": window,
                                       "position": PartSpec("rotary_neox", {"theta": 5e4, "head_dim": hd})})
     part = build_part("mixer", spec, env(width, dtype))
-    w = fill(part, 1)
+    w = fill(part, 1, scale=0.08)                     # scores of a few units: peaked, but not beyond what bf16 resolves
     one = OneSeq(part.cache_request(), n, dtype)
-    h = (torch.randn(n, width) * 2).to(dtype).to(DEV)
+    h = torch.randn(n, width).to(dtype).to(DEV)
     res = torch.randn(n, width).to(dtype).to(DEV)
     got = part.forward(h, res, one.ctx, one.view).double().cpu().numpy()
     hn = h.double().cpu().numpy()
