@@ -188,6 +188,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64, prefill and e2e")
+    ap.add_argument("--prefill-only", action="store_true", help="time the 2,048-token prompt only (for profiling)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -209,6 +210,10 @@ def main():
     print("[bench] %s (%.0f s)" % (eng.summary(), time.time() - t0), file=sys.stderr, flush=True)
     nums = model_numbers(cfg, layers)
 
+    if args.prefill_only:
+        ms_pre = time_prefill(eng, max(1, args.warmup - 2), max(1, args.steps))
+        print(json.dumps({"prefill_ms": round(ms_pre, 3), "layers_run": layers}))
+        return 0
     clocks = Clocks()
     clocks.start()
     ms_step, launches, mean_len = time_decode(eng, args.batch, args.steps, args.warmup, seed=1)
