@@ -499,3 +499,70 @@ FR_EXPORT int gemm_tc(const void* x, const void* w, void* out, int out_dtype, co
         default: return launch<256, 4>(mp, mq, p, grid, stream);
     }
 }
+
+// ------------------------------------------------------------------ the entry point that allocates nothing
+#include "gemm_tc_noalloc.h"
+
+namespace {
+
+// Tile counters first (they must start at zero), partial tiles after them.  In host code this name is only
+// a stand-in for the symbol: the device address comes from cudaGetSymbolAddress below.
+static __device__ __align__(256) unsigned char noalloc_area[GEMM_TC_NOALLOC_BYTES];
+
+struct NoAllocDevice {
+    bool ready = false;
+    unsigned char* base = nullptr;     // device address of noalloc_area on this device
+    int sm_count = 0;
+};
+NoAllocDevice noalloc_devices[64];
+
+template <int BN, int STAGES>
+cudaError_t allow_smem() {
+    return cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                STAGES * (P_BYTES + BN * TILE_K * 2) + 1024 + 256);
+}
+
+// Once per device, with that device current.
+int noalloc_setup(int device) {
+    NoAllocDevice& d = noalloc_devices[device];
+    void* ptr = nullptr;
+    FR_CUDA(cudaGetSymbolAddress(&ptr, noalloc_area));
+    FR_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, device));
+    FR_CUDA((allow_smem<16, 10>()));
+    FR_CUDA((allow_smem<32, 10>()));
+    FR_CUDA((allow_smem<64, 8>()));
+    FR_CUDA((allow_smem<128, 6>()));
+    FR_CUDA((allow_smem<256, 4>()));
+    d.base = (unsigned char*)ptr;
+    d.ready = true;
+    return FR_OK;
+}
+
+}  // namespace
+
+FR_EXPORT int gemm_tc_noalloc(const void* x, const void* w, void* out, int out_dtype, const void* bias,
+                              int bias_dtype, const void* residual, int m, int n, int k, int lda, int ldw, int ldo,
+                              int* status, cudaStream_t stream) {
+    int device = 0;
+    FR_CUDA(cudaGetDevice(&device));
+    if (device < 0 || device >= 64) FR_REFUSE("gemm_tc_noalloc: device %d is outside the table of 64", device);
+    if (!noalloc_devices[device].ready) {
+        const int rc = noalloc_setup(device);
+        if (rc) return rc;
+    }
+    const NoAllocDevice& d = noalloc_devices[device];
+    if (m <= 0 || n <= 0) return FR_OK;
+    long long plan[5];
+    gemm_tc_plan(m, n, k > 0 ? k : 1, d.sm_count, -1, -1, -1, plan);
+    if (plan[3] > GEMM_TC_NOALLOC_SCRATCH_FLOATS || plan[4] > GEMM_TC_NOALLOC_COUNTERS)
+        FR_REFUSE("gemm_tc_noalloc: a product of %d x %d x %d splits k %lld ways over %lld tiles and needs %lld scratch "
+                  "floats; the built-in area holds %d floats and %d tiles. Use gemm_tc() with a buffer of your own.",
+                  m, n, k, plan[2], plan[4], plan[3], GEMM_TC_NOALLOC_SCRATCH_FLOATS, GEMM_TC_NOALLOC_COUNTERS);
+    int* counters = (int*)d.base;
+    float* scratch = (float*)(d.base + GEMM_TC_NOALLOC_COUNTERS * 4);
+    // The area keeps what the last call left; counters must start at zero whatever happened before.
+    FR_CUDA(cudaMemsetAsync(counters, 0, GEMM_TC_NOALLOC_COUNTERS * 4, stream));
+    return gemm_tc(x, w, out, out_dtype, bias, bias_dtype, residual, m, n, k, lda, ldw, ldo, scratch,
+                   GEMM_TC_NOALLOC_SCRATCH_FLOATS, counters, GEMM_TC_NOALLOC_COUNTERS, status, d.sm_count, (int)plan[0],
+                   (int)plan[1], (int)plan[2], stream);
+}
