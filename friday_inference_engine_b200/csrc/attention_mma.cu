@@ -1,0 +1,426 @@
+// Causal grouped-query attention over the paged cache on tensor cores (bf16 operands,
+// fp32 scores, softmax and sums), for prompts and for decoding.
+//
+// The query heads that share one key/value head are packed into the rows of one tile:
+// for a sequence and a kv head, row r stands for (token r / G, group head r % G), G =
+// heads / kv heads.  A key/value block is then read once for all G heads, which is what
+// makes decoding with grouped heads memory-bound instead of compute-bound (the reference
+// does the same with CUDA cores: decodeAttentionGqaKernel, attention_kernels.cu:267-411,
+// and its R = tq*G + g rows for prompts, :493-499).
+//
+// Blocks of 64 keys are exactly the cache's pages, so a block is one page lookup.  K and
+// V blocks go global -> shared with cp.async (two buffers: the next block loads while this
+// one is used; rows past a sequence's last needed key are zero-filled, so stale pages
+// never reach the arithmetic), fragments come from ldmatrix, products are
+// mma.sync.m16n8k16 with the online softmax of flash attention between them.
+//
+// Two shapes of the same kernel:
+//   rows mode (prompts): a CTA owns 64 rows; each of its 4 warps owns 16 rows and walks
+//       all 64 keys of a block;
+//   keys mode (decoding): a CTA owns 16 rows (one token's G heads, padded) and a range of
+//       blocks (`splits` CTAs share a sequence's keys); each warp takes 16 of a block's 64
+//       keys; warps merge through shared memory, splits through the scratch buffer and
+//       the merge kernel.
+// Head sizes: multiples of 16 up to 128.  Others are served by the CUDA-core kernel.
+#include <math.h>
+
+#include "attention_merge.cuh"
+#include "common.cuh"
+
+FR_EXPORT const char* attention_mma_last_error() { return fr_error_text; }
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+constexpr int BLOCK_N = 64;     // keys per block = tokens per cache page
+constexpr int WARPS = 4;
+constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
+
+struct MmaArgs {
+    const bf16* q;            // rows of q_stride elements; head h at h * hd
+    bf16* out;                // [rows][nq * hd]
+    const bf16* k_pool;       // [pages][64][nkv][hd]
+    const bf16* v_pool;
+    const int* block_table;   // [seqs][table_width]
+    const int* seq_start;     // first row of each sequence
+    const int* seq_qlen;      // rows (tokens) of each sequence in this step
+    const int* seq_pos0;      // position of its first row
+    const int* seq_live;      // may be null; < 0 at seq_start[s]: the sequence has ended (row marker)
+    float* part;              // [rows * nq][splits][hd + 2] when splits > 1
+    int q_stride, table_width, nq, nkv, window, splits;
+    float scale_log2;         // softmax scale times log2(e)
+};
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldsm4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm4_t(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int HD, bool KEYS_MODE>
+__global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs p) {
+    constexpr int ROW_BYTES = HD * 2 + 16;            // padded: 8 consecutive rows hit 8 different bank groups
+    constexpr int CHUNKS = HD / 8;                    // 16-byte pieces per row
+    constexpr int ROWS_CTA = KEYS_MODE ? 16 : 64;
+    constexpr int KPW = KEYS_MODE ? 16 : 64;          // keys of a block per warp
+    constexpr int NT = KPW / 8;                       // score tiles (8 keys each) per warp
+    constexpr int DT = HD / 8;                        // output tiles (8 dims each)
+    constexpr int KV_BYTES = BLOCK_N * ROW_BYTES;
+    extern __shared__ __align__(16) uint8_t smem[];
+    uint8_t* s_q = smem;                              // [ROWS_CTA][ROW_BYTES]
+    uint8_t* s_k = s_q + ROWS_CTA * ROW_BYTES;        // [2][64][ROW_BYTES]
+    uint8_t* s_v = s_k + 2 * KV_BYTES;                // [2][64][ROW_BYTES]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int seq = blockIdx.z, kvh = blockIdx.y;
+    const int split = blockIdx.x % p.splits, tile = blockIdx.x / p.splits;
+    const int G = p.nq / p.nkv;
+    const int q_len = p.seq_qlen[seq], q_start = p.seq_start[seq], pos0 = p.seq_pos0[seq];
+    const int n_rows = q_len * G;
+    const int r0 = tile * ROWS_CTA;
+    if (r0 >= n_rows) return;
+    const bool live = p.seq_live == nullptr || p.seq_live[q_start] >= 0;
+
+    // Range of key blocks for this CTA.
+    const int t_first = r0 / G, t_last = min((r0 + ROWS_CTA - 1) / G, q_len - 1);
+    const int pos_hi = pos0 + t_last;                 // the farthest key any row of the CTA may see
+    const int lo_min = p.window > 0 ? max(0, pos0 + t_first - p.window + 1) : 0;
+    int kb_begin = lo_min / BLOCK_N, kb_end = pos_hi / BLOCK_N;     // inclusive
+    if (p.splits > 1) {
+        const int n = kb_end - kb_begin + 1, per = (n + p.splits - 1) / p.splits;
+        kb_begin += split * per;
+        kb_end = min(kb_begin + per - 1, kb_end);
+    }
+    if (!live) kb_end = kb_begin - 1;                 // nothing to read: the output is zero
+
+    const int* table = p.block_table + (size_t)seq * p.table_width;
+    const size_t kv_row = (size_t)p.nkv * HD;         // elements between consecutive keys of a page
+
+    auto load_q = [&]() {
+        for (int c = tid; c < ROWS_CTA * CHUNKS; c += WARPS * 32) {
+            const int r = c / CHUNKS, ch = c - r * CHUNKS;
+            const int rr = r0 + r;
+            const bool ok = rr < n_rows;
+            const int t = ok ? rr / G : 0, g = ok ? rr - t * G : 0;
+            const bf16* src = p.q + (size_t)(q_start + t) * p.q_stride + (size_t)(kvh * G + g) * HD + ch * 8;
+            cp_async16((uint32_t)__cvta_generic_to_shared(s_q + r * ROW_BYTES + ch * 16), src, ok ? 16 : 0);
+        }
+    };
+    auto load_kv = [&](int kb, int buf) {
+        const int page = table[kb];
+        const bf16* kbase = p.k_pool + ((size_t)page * BLOCK_N) * kv_row + (size_t)kvh * HD;
+        const bf16* vbase = p.v_pool + ((size_t)page * BLOCK_N) * kv_row + (size_t)kvh * HD;
+        for (int c = tid; c < BLOCK_N * CHUNKS; c += WARPS * 32) {
+            const int r = c / CHUNKS, ch = c - r * CHUNKS;
+            const int bytes = (kb * BLOCK_N + r <= pos_hi) ? 16 : 0;        // beyond the last needed key: zeros
+            const size_t off = (size_t)r * kv_row + ch * 8;
+            cp_async16((uint32_t)__cvta_generic_to_shared(s_k + buf * KV_BYTES + r * ROW_BYTES + ch * 16),
+                       bytes ? (const void*)(kbase + off) : (const void*)p.k_pool, bytes);
+            cp_async16((uint32_t)__cvta_generic_to_shared(s_v + buf * KV_BYTES + r * ROW_BYTES + ch * 16),
+                       bytes ? (const void*)(vbase + off) : (const void*)p.v_pool, bytes);
+        }
+    };
+
+    // This thread's two rows (fragment layout of mma: rows lane/4 and lane/4 + 8 of the warp's 16).
+    const int row_base = KEYS_MODE ? 0 : warp * 16;
+    const int key_base = KEYS_MODE ? warp * 16 : 0;
+    int pos_r[2], lo_r[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int rr = r0 + row_base + (lane >> 2) + 8 * i;
+        const bool ok = rr < n_rows;
+        pos_r[i] = ok ? pos0 + rr / G : -1;           // -1: every key is masked
+        lo_r[i] = (ok && p.window > 0) ? max(0, pos_r[i] - p.window + 1) : 0;
+    }
+    // Warp-wide bounds that decide whether a block needs the mask at all.
+    const int w_first = (r0 + row_base) / G;
+    const int w_last = min((r0 + row_base + 15) / G, q_len - 1);
+    const int w_pos_min = pos0 + w_first;
+    const int w_lo_max = p.window > 0 ? max(0, pos0 + w_last - p.window + 1) : 0;
+
+    float o[DT][4];
+#pragma unroll
+    for (int d = 0; d < DT; ++d)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[d][e] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+    load_q();
+    if (kb_begin <= kb_end) load_kv(kb_begin, 0);
+    cp_commit();
+
+    const uint32_t q_addr = (uint32_t)__cvta_generic_to_shared(s_q);
+    int buf = 0;
+    for (int kb = kb_begin; kb <= kb_end; ++kb, buf ^= 1) {
+        if (kb < kb_end) {
+            load_kv(kb + 1, buf ^ 1);
+            cp_commit();
+            cp_wait<1>();
+        } else {
+            cp_wait<0>();
+        }
+        __syncthreads();
+        const uint32_t k_addr = (uint32_t)__cvta_generic_to_shared(s_k + buf * KV_BYTES);
+        const uint32_t v_addr = (uint32_t)__cvta_generic_to_shared(s_v + buf * KV_BYTES);
+
+        // scores = Q K^T for this warp's 16 rows and KPW keys
+        float s[NT][4];
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[n][e] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+            uint32_t a[4];
+            ldsm4(a, q_addr + (row_base + (lane & 7) + 8 * ((lane >> 3) & 1)) * ROW_BYTES + (ks * 16 + 8 * (lane >> 4)) * 2);
+#pragma unroll
+            for (int np = 0; np < NT / 2; ++np) {
+                uint32_t b[4];
+                ldsm4(b, k_addr + (key_base + np * 16 + (lane & 7) + 8 * (lane >> 4)) * ROW_BYTES +
+                             (ks * 16 + 8 * ((lane >> 3) & 1)) * 2);
+                mma16816(s[2 * np], a, b[0], b[1]);
+                mma16816(s[2 * np + 1], a, b[2], b[3]);
+            }
+        }
+
+        // scale, mask, online softmax
+        const int j0 = kb * BLOCK_N + key_base;
+        const bool need_mask = (j0 + KPW - 1 > w_pos_min) || (p.window > 0 && j0 < w_lo_max);
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float v = s[n][e] * p.scale_log2;
+                if (need_mask) {
+                    const int j = j0 + n * 8 + 2 * (lane & 3) + (e & 1);
+                    if (j > pos_r[e >> 1] || j < lo_r[e >> 1]) v = -INFINITY;
+                } else if (pos_r[e >> 1] < 0) {
+                    v = -INFINITY;
+                }
+                s[n][e] = v;
+                mx[e >> 1] = fmaxf(mx[e >> 1], v);
+            }
+        float alpha[2], m_use[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+            const float m_new = fmaxf(m_run[i], mx[i]);
+            m_use[i] = m_new == -INFINITY ? 0.f : m_new;
+            alpha[i] = exp2f(m_run[i] - m_use[i]);     // 0 while the row has seen no key
+            m_run[i] = m_new;
+        }
+        float sum[2] = {0.f, 0.f};
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float pe = exp2f(s[n][e] - m_use[e >> 1]);
+                s[n][e] = pe;
+                sum[e >> 1] += pe;
+            }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) l_run[i] = l_run[i] * alpha[i] + sum[i];
+#pragma unroll
+        for (int d = 0; d < DT; ++d) {
+            o[d][0] *= alpha[0]; o[d][1] *= alpha[0];
+            o[d][2] *= alpha[1]; o[d][3] *= alpha[1];
+        }
+
+        // o += P V
+#pragma unroll
+        for (int kk = 0; kk < KPW / 16; ++kk) {
+            uint32_t a[4];
+            a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+            a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+            a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+            a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+            for (int dp = 0; dp < DT / 2; ++dp) {
+                uint32_t b[4];
+                ldsm4_t(b, v_addr + (key_base + kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * ROW_BYTES +
+                               (dp * 16 + 8 * (lane >> 4)) * 2);
+                mma16816(o[2 * dp], a, b[0], b[1]);
+                mma16816(o[2 * dp + 1], a, b[2], b[3]);
+            }
+        }
+        __syncthreads();          // every warp is done with this buffer before it is loaded again
+    }
+    if (kb_begin > kb_end) cp_wait<0>();
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
+    }
+
+    if (!KEYS_MODE) {
+        // Each warp owns its rows outright.
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int rr = r0 + row_base + (lane >> 2) + 8 * i;
+            if (rr >= n_rows) continue;
+            const int t = rr / G, h = kvh * G + (rr - t * G);
+            const size_t item = (size_t)(q_start + t) * p.nq + h;
+            if (p.splits == 1) {
+                const float inv = l_run[i] > 0.f ? 1.f / l_run[i] : 0.f;
+                bf16* dst = p.out + item * HD;
+#pragma unroll
+                for (int d = 0; d < DT; ++d)
+                    *reinterpret_cast<uint32_t*>(dst + d * 8 + 2 * (lane & 3)) =
+                        pack_bf16(o[d][2 * i] * inv, o[d][2 * i + 1] * inv);
+            } else {
+                float* dst = p.part + (item * p.splits + split) * (HD + 2);
+#pragma unroll
+                for (int d = 0; d < DT; ++d) {
+                    dst[d * 8 + 2 * (lane & 3)] = o[d][2 * i];
+                    dst[d * 8 + 2 * (lane & 3) + 1] = o[d][2 * i + 1];
+                }
+                if ((lane & 3) == 0) {
+                    dst[HD] = m_run[i] * LN2;
+                    dst[HD + 1] = l_run[i];
+                }
+            }
+        }
+    } else {
+        // The four warps saw different keys of the same 16 rows: merge through shared memory
+        // (the K/V buffers are free now).
+        float* c_o = reinterpret_cast<float*>(s_k);                 // [WARPS][16][HD]
+        float* c_m = c_o + WARPS * 16 * HD;                         // [WARPS][16]
+        float* c_l = c_m + WARPS * 16;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int r = (lane >> 2) + 8 * i;
+#pragma unroll
+            for (int d = 0; d < DT; ++d) {
+                c_o[(warp * 16 + r) * HD + d * 8 + 2 * (lane & 3)] = o[d][2 * i];
+                c_o[(warp * 16 + r) * HD + d * 8 + 2 * (lane & 3) + 1] = o[d][2 * i + 1];
+            }
+            if ((lane & 3) == 0) {
+                c_m[warp * 16 + r] = m_run[i];
+                c_l[warp * 16 + r] = l_run[i];
+            }
+        }
+        __syncthreads();
+        const int r = tid >> 3;                       // 16 rows x 8 threads
+        const int rr = r0 + r;
+        if (rr < n_rows) {
+            float big = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) big = fmaxf(big, c_m[w * 16 + r]);
+            float f[WARPS], l = 0.f;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) {
+                f[w] = c_m[w * 16 + r] == -INFINITY ? 0.f : exp2f(c_m[w * 16 + r] - big);
+                l += c_l[w * 16 + r] * f[w];
+            }
+            const int t = rr / G, h = kvh * G + (rr - t * G);
+            const size_t item = (size_t)(q_start + t) * p.nq + h;
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            for (int d = (tid & 7); d < HD; d += 8) {
+                float acc = 0.f;
+#pragma unroll
+                for (int w = 0; w < WARPS; ++w) acc += c_o[(w * 16 + r) * HD + d] * f[w];
+                if (p.splits == 1) p.out[item * HD + d] = __float2bfloat16_rn(acc * inv);
+                else p.part[(item * p.splits + split) * (HD + 2) + d] = acc;
+            }
+            if (p.splits > 1 && (tid & 7) == 0) {
+                float* dst = p.part + (item * p.splits + split) * (HD + 2);
+                dst[HD] = big * LN2;                  // natural-log units, as the merge kernel expects
+                dst[HD + 1] = l;
+            }
+        }
+    }
+}
+
+template <int HD, bool KEYS_MODE>
+int launch(const MmaArgs& p, dim3 grid, cudaStream_t stream) {
+    constexpr int ROW_BYTES = HD * 2 + 16;
+    constexpr int ROWS_CTA = KEYS_MODE ? 16 : 64;
+    constexpr int kv = 4 * BLOCK_N * ROW_BYTES;
+    constexpr int merge = KEYS_MODE ? (WARPS * 16 * HD + 2 * WARPS * 16) * 4 : 0;
+    constexpr int smem = ROWS_CTA * ROW_BYTES + (kv > merge ? kv : merge);
+    static bool configured = false;
+    if (!configured) {
+        FR_CUDA(cudaFuncSetAttribute(attention_mma_kernel<HD, KEYS_MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        configured = true;
+    }
+    attention_mma_kernel<HD, KEYS_MODE><<<grid, WARPS * 32, smem, stream>>>(p);
+    FR_CHECK_LAUNCH("attention_mma");
+    return FR_OK;
+}
+
+template <bool KEYS_MODE>
+int launch_hd(int hd, const MmaArgs& p, dim3 grid, cudaStream_t stream) {
+    switch (hd) {
+        case 16: return launch<16, KEYS_MODE>(p, grid, stream);
+        case 32: return launch<32, KEYS_MODE>(p, grid, stream);
+        case 48: return launch<48, KEYS_MODE>(p, grid, stream);
+        case 64: return launch<64, KEYS_MODE>(p, grid, stream);
+        case 80: return launch<80, KEYS_MODE>(p, grid, stream);
+        case 96: return launch<96, KEYS_MODE>(p, grid, stream);
+        case 112: return launch<112, KEYS_MODE>(p, grid, stream);
+        case 128: return launch<128, KEYS_MODE>(p, grid, stream);
+        default: FR_REFUSE("attention_mma: head size %d is not built (multiples of 16 up to 128)", hd);
+    }
+}
+
+}  // namespace
+
+FR_EXPORT int attention_mma_supports(int hd, int page) { return hd % 16 == 0 && hd >= 16 && hd <= 128 && page == BLOCK_N; }
+
+// q: rows of q_stride bf16 (head h at h * hd); out [rows][nq * hd]; pools [pages][64][nkv][hd] bf16.
+// seq_start/seq_qlen/seq_pos0: per sequence, its first row, its rows in this step, the position of its first row.
+// seq_live (may be null): indexed by a sequence's first row; negative marks a sequence that has ended.
+// max_q_len: the longest seq_qlen (sizes the grid).  keys_mode: 1 for one-token steps.  splits > 1 needs
+// scratch of rows * nq * splits * (hd + 2) floats.
+FR_EXPORT int attention_mma(const void* q, int q_stride, void* out, const void* k_pool, const void* v_pool,
+                            const int* block_table, int table_width, int page, const int* seq_start,
+                            const int* seq_qlen, const int* seq_pos0, const int* seq_live, int n_seqs, int rows,
+                            int max_q_len, int nq, int nkv, int hd, int window, float scale, int keys_mode, int splits,
+                            float* scratch, cudaStream_t stream) {
+    if (n_seqs <= 0 || rows <= 0) return FR_OK;
+    if (!attention_mma_supports(hd, page)) FR_REFUSE("attention_mma: head size %d / page %d is not built", hd, page);
+    if (nkv <= 0 || nq % nkv != 0) FR_REFUSE("attention: %d heads cannot share %d key/value heads", nq, nkv);
+    if (splits < 1 || splits > 4096) FR_REFUSE("attention_mma: %d splits", splits);
+    if (splits > 1 && scratch == nullptr) FR_REFUSE("attention_mma: splits need a scratch buffer");
+    if (n_seqs > 65535 || nkv > 65535) FR_REFUSE("attention_mma: %d sequences x %d kv heads exceed the grid", n_seqs, nkv);
+    MmaArgs p;
+    p.q = (const bf16*)q; p.out = (bf16*)out; p.k_pool = (const bf16*)k_pool; p.v_pool = (const bf16*)v_pool;
+    p.block_table = block_table; p.seq_start = seq_start; p.seq_qlen = seq_qlen; p.seq_pos0 = seq_pos0;
+    p.seq_live = seq_live; p.part = scratch; p.q_stride = q_stride; p.table_width = table_width; p.nq = nq;
+    p.nkv = nkv; p.window = window; p.splits = splits; p.scale_log2 = scale * LOG2E;
+    const int G = nq / nkv;
+    const int rows_cta = keys_mode ? 16 : 64;
+    const int tiles = (max_q_len * G + rows_cta - 1) / rows_cta;
+    dim3 grid(tiles * splits, nkv, n_seqs);
+    int rc = keys_mode ? launch_hd<true>(hd, p, grid, stream) : launch_hd<false>(hd, p, grid, stream);
+    if (rc) return rc;
+    if (splits > 1) {
+        MergeArgs mp{scratch, out, rows, nq, hd, splits};
+        attention_merge_kernel<bf16><<<(rows * nq + 3) / 4, 128, 0, stream>>>(mp);
+        FR_CHECK_LAUNCH("attention merge");
+    }
+    return FR_OK;
+}

@@ -18,6 +18,7 @@
 // block_table[b][j / page], row j % page, of pools laid out [pages][page][nkv][hd].
 #include <math.h>
 
+#include "attention_merge.cuh"
 #include "common.cuh"
 
 FR_EXPORT const char* attention_simt_last_error() { return fr_error_text; }
@@ -113,40 +114,6 @@ __global__ void __launch_bounds__(128) attention_kernel(AttnArgs p) {
     }
 }
 
-// o = sum_s o_s exp(m_s - M) / sum_s l_s exp(m_s - M), M = max_s m_s; a split that saw
-// no key has l = 0 and m = -inf and drops out.
-template <typename T>
-__global__ void __launch_bounds__(128) attention_merge_kernel(AttnArgs p) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int item = blockIdx.x * 4 + warp;
-    if (item >= p.rows * p.nq) return;
-    const float* part = p.part + (size_t)item * p.splits * (p.hd + 2);
-    float big = -INFINITY;
-    for (int s = 0; s < p.splits; ++s) big = fmaxf(big, part[(size_t)s * (p.hd + 2) + p.hd]);
-    float l = 0.f, acc[MAX_PER_LANE];
-#pragma unroll
-    for (int i = 0; i < MAX_PER_LANE; ++i) acc[i] = 0.f;
-    for (int s = 0; s < p.splits; ++s) {
-        const float* ps = part + (size_t)s * (p.hd + 2);
-        const float ls = ps[p.hd + 1];
-        if (!(ls > 0.f)) continue;
-        const float f = expf(ps[p.hd] - big);
-        l += ls * f;
-#pragma unroll
-        for (int i = 0; i < MAX_PER_LANE; ++i) {
-            const int d = lane + 32 * i;
-            if (d < p.hd) acc[i] += ps[d] * f;
-        }
-    }
-    const float inv = l > 0.f ? 1.0f / l : 0.f;
-    T* o_row = (T*)p.out + (size_t)item * p.hd;
-#pragma unroll
-    for (int i = 0; i < MAX_PER_LANE; ++i) {
-        const int d = lane + 32 * i;
-        if (d < p.hd) fr_store(o_row + d, acc[i] * inv);
-    }
-}
-
 }  // namespace
 
 // Scratch floats needed for `splits` > 1.
@@ -166,15 +133,16 @@ FR_EXPORT int attention_simt(const void* q, int q_stride, void* out, const void*
     AttnArgs p{q, out, k_pool, v_pool, block_table, row_seq, row_pos, scratch, table_width, page, rows, nq, nkv, hd,
                q_stride, window, splits, scale};
     const int items = rows * nq;
+    MergeArgs mp{scratch, out, rows, nq, hd, splits};
     dim3 grid((items + 3) / 4, splits);
     if (dtype == FR_F32) {
         attention_kernel<float><<<grid, 128, 0, stream>>>(p);
         FR_CHECK_LAUNCH("attention");
-        if (splits > 1) attention_merge_kernel<float><<<(items + 3) / 4, 128, 0, stream>>>(p);
+        if (splits > 1) attention_merge_kernel<float><<<(items + 3) / 4, 128, 0, stream>>>(mp);
     } else if (dtype == FR_BF16) {
         attention_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(p);
         FR_CHECK_LAUNCH("attention");
-        if (splits > 1) attention_merge_kernel<__nv_bfloat16><<<(items + 3) / 4, 128, 0, stream>>>(p);
+        if (splits > 1) attention_merge_kernel<__nv_bfloat16><<<(items + 3) / 4, 128, 0, stream>>>(mp);
     } else {
         FR_REFUSE("attention: unknown dtype %d", dtype);
     }

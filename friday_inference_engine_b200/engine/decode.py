@@ -46,6 +46,9 @@ class DeviceDecoder:
         self.tables = [torch.from_numpy(t.copy()).to(dev) for t in self.tables_host]
         self.ctx = StepContext(self, self.slots, [1] * n, [self.cache.max_seq_tokens] * n)
         self.ctx.tokens, self.ctx.row_seq, self.ctx.row_pos = self.tokens, self.row_seq, self.row_pos
+        self.ctx.seq_start = torch.arange(n, **i32)              # one row per sequence
+        self.ctx.seq_qlen = torch.ones(n, **i32)
+        self.ctx.seq_pos0 = self.row_pos                          # the row's position is the sequence's
         self.ctx.tables = self.tables
         self.ctx.seq_slots = torch.as_tensor(self.slots, dtype=torch.int64, device=dev) if self.cache.states else None
         self._scratch = None

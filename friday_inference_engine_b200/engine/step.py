@@ -14,7 +14,8 @@ cuts prompts at 512: transformer.cpp:1369).  A pass runs all layers; the next pa
 the earlier tokens in the cache.  The cut changes no result beyond rounding.
 
 Host-side layout of a pass (int32, sent to the device in one copy):
-    tokens[rows] | row_seq[rows] | row_pos[rows] | want_rows[n] | per group: table[n_seqs][width]
+    tokens[rows] | row_seq[rows] | row_pos[rows] | want_rows[n] | seq_start[n_seqs] | seq_qlen[n_seqs] |
+    seq_pos0[n_seqs] | per group: table[n_seqs][width]
 """
 import numpy as np
 import torch
@@ -40,6 +41,7 @@ class StepContext:
         self.max_kv_len = max(self.kv_lens) if self.kv_lens else 0
         self.decode = self.max_q_len == 1
         self.tokens = self.row_seq = self.row_pos = self.want_rows = self.seq_slots = None
+        self.seq_start = self.seq_qlen = self.seq_pos0 = None    # int32 [n_seqs] on the device
         self.tables = []
 
     def scratch(self, n_floats, device):
@@ -97,7 +99,8 @@ class Stepper:
         ctx = StepContext(self, slots, q_lens, [a + q for a, q in zip(start, q_lens)])
         rows = ctx.rows
         tables = cache.tables_for(slots)
-        sizes = [rows, rows, rows, len(want_rows)] + [t.size for t in tables]
+        nseq = len(slots)
+        sizes = [rows, rows, rows, len(want_rows), nseq, nseq, nseq] + [t.size for t in tables]
         offs = np.concatenate([[0], np.cumsum([_pad4(s) for s in sizes])]).astype(np.int64)
         host = np.zeros((int(offs[-1]),), dtype=np.int32)
         host[offs[0]:offs[0] + rows] = np.concatenate([np.asarray(t, dtype=np.int32) for t in pass_tokens])
@@ -105,14 +108,20 @@ class Stepper:
         host[offs[2]:offs[2] + rows] = np.concatenate(
             [np.arange(a, a + q, dtype=np.int32) for a, q in zip(start, q_lens)])
         host[offs[3]:offs[3] + len(want_rows)] = np.asarray(want_rows, dtype=np.int32)
+        host[offs[4]:offs[4] + nseq] = np.concatenate([[0], np.cumsum(q_lens)[:-1]]).astype(np.int32)
+        host[offs[5]:offs[5] + nseq] = np.asarray(q_lens, dtype=np.int32)
+        host[offs[6]:offs[6] + nseq] = np.asarray(start, dtype=np.int32)
         for i, t in enumerate(tables):
-            host[offs[4 + i]:offs[4 + i] + t.size] = t.reshape(-1)
+            host[offs[7 + i]:offs[7 + i] + t.size] = t.reshape(-1)
         dev = self._upload(host)
         ctx.tokens = dev[offs[0]:offs[0] + rows]
         ctx.row_seq = dev[offs[1]:offs[1] + rows]
         ctx.row_pos = dev[offs[2]:offs[2] + rows]
         ctx.want_rows = dev[offs[3]:offs[3] + len(want_rows)]
-        ctx.tables = [dev[offs[4 + i]:offs[4 + i] + t.size].view(t.shape) for i, t in enumerate(tables)]
+        ctx.seq_start = dev[offs[4]:offs[4] + nseq]
+        ctx.seq_qlen = dev[offs[5]:offs[5] + nseq]
+        ctx.seq_pos0 = dev[offs[6]:offs[6] + nseq]
+        ctx.tables = [dev[offs[7 + i]:offs[7 + i] + t.size].view(t.shape) for i, t in enumerate(tables)]
         ctx.seq_slots = torch.as_tensor(slots, dtype=torch.int64, device=self.device) if cache.states else None
         return ctx
 

@@ -191,10 +191,22 @@ class CudaOps:
         """Causal attention of the step's rows over the paged cache.
 
         q: the buffer that holds the queries, row stride q_stride (elements), head h at h * head_dim.
-        geometry: StepGeometry-like object with rows, n_seqs, max_q_len, max_kv_len (host numbers
-        used to size the launch only).
+        geometry: the step's context: max_kv_len and scratch(); for the tensor-core kernel also n_seqs,
+        max_q_len, decode and the per-sequence arrays seq_start, seq_qlen, seq_pos0 (int32, device).
+        bf16 with a head size the tensor-core kernel is built for goes there; everything else (float32,
+        other head sizes, a caller without per-sequence arrays) goes to the CUDA-core kernel.
         """
         _need_cuda(q, out, k_pool, v_pool, block_table, row_seq, row_pos)
+        if (out.dtype == torch.bfloat16 and getattr(geometry, "seq_start", None) is not None
+                and self.attention_mma_supports(head_dim, page_size)):
+            keys_mode = bool(geometry.decode)
+            splits = 1
+            if keys_mode:
+                splits = self.decode_splits(geometry.n_seqs, n_heads, n_kv_heads, geometry.max_kv_len, q.device)
+            return self.attention_mma(q, q_stride, out, k_pool, v_pool, block_table, geometry.seq_start,
+                                      geometry.seq_qlen, geometry.seq_pos0, row_seq, geometry.n_seqs,
+                                      geometry.max_q_len, n_heads, n_kv_heads, head_dim, window, scale, keys_mode,
+                                      splits, geometry)
         rows = out.shape[0]
         splits = self.attention_splits(rows, n_heads, geometry.max_kv_len)
         scratch = None
@@ -205,9 +217,35 @@ class CudaOps:
             block_table.shape[1], page_size, _ptr(row_seq), _ptr(row_pos), rows, n_heads, n_kv_heads, head_dim,
             window or 0, float(scale), splits, _ptr(scratch), code_of(out.dtype), _stream())
 
+    def attention_mma_supports(self, head_dim, page_size):
+        return head_dim % 16 == 0 and 16 <= head_dim <= 128 and page_size == 64
+
+    def attention_mma(self, q, q_stride, out, k_pool, v_pool, block_table, seq_start, seq_qlen, seq_pos0, seq_live,
+                      n_seqs, max_q_len, n_heads, n_kv_heads, head_dim, window, scale, keys_mode, splits, geometry):
+        """The tensor-core kernel; keys_mode: one-token steps (rows of a CTA share a token, warps and `splits`
+        CTAs share the keys); otherwise CTAs own 64 rows of (token, group head) pairs."""
+        rows = out.shape[0]
+        scratch = None
+        if splits > 1:
+            scratch = geometry.scratch(rows * n_heads * splits * (head_dim + 2), q.device)
+        lib.family("attention_mma").call(
+            "attention_mma", _ptr(q), q_stride, _ptr(out), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
+            block_table.shape[1], 64, _ptr(seq_start), _ptr(seq_qlen), _ptr(seq_pos0), _ptr(seq_live), n_seqs, rows,
+            max_q_len, n_heads, n_kv_heads, head_dim, window or 0, float(scale), 1 if keys_mode else 0, splits,
+            _ptr(scratch), _stream())
+
+    def decode_splits(self, n_seqs, n_heads, n_kv_heads, max_kv_len, device):
+        """CTAs that share one sequence's keys in a one-token step: enough to put about four small CTAs on
+        every SM, never more than there are key blocks."""
+        sms = self._tc_buffers(device)[3]
+        group = n_heads // n_kv_heads
+        base = n_seqs * n_kv_heads * ((group + 15) // 16)
+        blocks = (max_kv_len + 63) // 64
+        return int(max(1, min((4 * sms + base - 1) // base, blocks, 256)))
+
     @staticmethod
     def attention_splits(rows, n_heads, max_kv_len):
-        """Few rows facing long contexts are cut along the keys so that the device fills."""
+        """CUDA-core kernel: few rows facing long contexts are cut along the keys so that the device fills."""
         warps = rows * n_heads
         want = 148 * 16
         if warps >= want or max_kv_len <= 128:

@@ -284,3 +284,80 @@ def test_linear_chooses_a_kernel_that_can_do_the_shape():
     a, w = rnd((9, 104), dt, 28), rnd((50, 104), dt, 29)
     assert ops.backend().tensor_core_ok(a, w, a, None)
     close(ops.linear(a, w), pm.linear(f64(a), f64(w)), dt, "tensor cores")
+
+
+# ------------------------------------------------------------------ tensor-core attention
+class SeqGeo(Geo):
+    pass
+
+
+def mma_case(seqs, nq, nkv, hd, window, keys_mode, splits, seed=30):
+    """seqs: list of (tokens held before the step, tokens in the step).  Builds a paged cache that holds
+    every sequence's keys and values (shuffled pages, NaN elsewhere), runs the tensor-core kernel on the
+    step's rows and compares with the plain attention of each whole sequence."""
+    dt = torch.bfloat16
+    n_pages_each = [(a + q + PAGE - 1) // PAGE for a, q in seqs]
+    total_pages = sum(n_pages_each) + 3
+    perm = torch.randperm(total_pages, generator=torch.Generator().manual_seed(seed)).tolist()
+    kp = torch.full((total_pages, PAGE, nkv, hd), float("nan"), dtype=dt, device=DEV)
+    vp = kp.clone()
+    width = max(n_pages_each) + 1
+    table = torch.full((len(seqs), width), -1, dtype=torch.int32)
+    rows = sum(q for _, q in seqs)
+    qbuf = torch.empty((rows, (nq + 2 * nkv) * hd), dtype=dt, device=DEV)     # q sits inside a wider row, as in qkv
+    refs, starts, row = [], [], 0
+    for s, (a, q) in enumerate(seqs):
+        n = a + q
+        qs, ks, vs = rnd((n, nq, hd), dt, seed + 3 * s + 1) * 2, rnd((n, nkv, hd), dt, seed + 3 * s + 2), \
+            rnd((n, nkv, hd), dt, seed + 3 * s + 3)
+        refs.append(pm.attention(f64(qs), f64(ks), f64(vs), window).reshape(n, nq * hd)[a:])
+        for lp in range(n_pages_each[s]):
+            page = perm.pop()
+            table[s, lp] = page
+            lo, hi = lp * PAGE, min((lp + 1) * PAGE, n)
+            kp[page, : hi - lo] = ks[lo:hi]
+            vp[page, : hi - lo] = vs[lo:hi]
+        qbuf[row:row + q, : nq * hd] = qs[a:].reshape(q, nq * hd)
+        starts.append(row)
+        row += q
+    i32 = dict(dtype=torch.int32, device=DEV)
+    geo = Geo(max(a + q for a, q in seqs))
+    out = torch.full((rows, nq * hd), float("nan"), dtype=dt, device=DEV)
+    ops.backend().attention_mma(
+        qbuf, qbuf.stride(0), out, kp, vp, table.to(DEV), torch.tensor(starts, **i32),
+        torch.tensor([q for _, q in seqs], **i32), torch.tensor([a for a, _ in seqs], **i32), None, len(seqs),
+        max(q for _, q in seqs), nq, nkv, hd, window, hd ** -0.5, keys_mode, splits, geo)
+    close(out, np.concatenate(refs, axis=0), dt, "tensor-core attention", bf16_rel=0.02)
+
+
+@pytest.mark.parametrize("nq,nkv,hd,window", [
+    (4, 2, 16, None), (3, 1, 32, 24), (28, 4, 128, None), (6, 2, 48, 80), (8, 1, 112, 64), (14, 2, 64, None),
+    (5, 5, 80, None), (9, 3, 96, 100), (32, 1, 64, None)])
+def test_attention_mma_prompts_of_unequal_lengths(nq, nkv, hd, window):
+    # whole prompts, a continued one, one token, lengths around the 64-key blocks
+    mma_case([(0, 37), (0, 130), (70, 65), (0, 1), (63, 2), (0, 64)], nq, nkv, hd, window, False, 1)
+
+
+@pytest.mark.parametrize("nq,nkv,hd,window,splits", [
+    (4, 2, 16, None, 1), (3, 1, 32, 24, 2), (28, 4, 128, None, 5), (28, 4, 128, None, 1), (6, 2, 48, 80, 3),
+    (8, 1, 112, 64, 4), (40, 8, 128, None, 7), (32, 1, 64, None, 2), (5, 5, 80, 130, 16)])
+def test_attention_mma_one_token_steps(nq, nkv, hd, window, splits):
+    mma_case([(0, 1), (63, 1), (64, 1), (65, 1), (299, 1), (1000, 1), (127, 1)], nq, nkv, hd, window, True, splits)
+
+
+def test_attention_mma_long_prompt_sizes_of_the_7b_shape():
+    mma_case([(0, 700), (300, 500)], 28, 4, 128, None, False, 1)
+
+
+def test_attention_mma_dead_rows_give_zero():
+    dt = torch.bfloat16
+    nq, nkv, hd = 4, 2, 32
+    kp = torch.full((2, PAGE, nkv, hd), float("nan"), dtype=dt, device=DEV)
+    q = rnd((2, (nq + 2 * nkv) * hd), dt, 40)
+    out = torch.full((2, nq * hd), float("nan"), dtype=dt, device=DEV)
+    i32 = dict(dtype=torch.int32, device=DEV)
+    live = torch.tensor([-1, -1], **i32)
+    ops.backend().attention_mma(q, q.stride(0), out, kp, kp, torch.zeros((2, 1), **i32), torch.tensor([0, 1], **i32),
+                                torch.ones(2, **i32), torch.tensor([5, 9], **i32), live, 2, 1, nq, nkv, hd, None, 1.0,
+                                True, 2, Geo(10))
+    assert float(out.float().abs().max()) == 0.0

@@ -49,6 +49,9 @@ class OneSeq:
         ctx.row_pos = torch.arange(n, dtype=torch.int32, device=DEV)
         ctx.tables = [torch.from_numpy(t).to(DEV) for t in self.cache.tables_for([self.slot])]
         ctx.seq_slots = torch.tensor([self.slot], dtype=torch.int64, device=DEV)
+        ctx.seq_start = torch.zeros(1, dtype=torch.int32, device=DEV)
+        ctx.seq_qlen = torch.full((1,), n, dtype=torch.int32, device=DEV)
+        ctx.seq_pos0 = torch.zeros(1, dtype=torch.int32, device=DEV)
         self.ctx = ctx
         self.view = self.cache.view(0, True, ctx.tables, ctx.seq_slots, [self.slot])
 
