@@ -18,6 +18,8 @@ constexpr int FR_MERGE_PER_LANE = 8;   // head sizes up to 256
 // no key has l = 0 and m = -inf and drops out.
 template <typename T>
 __global__ void __launch_bounds__(128) attention_merge_kernel(MergeArgs p) {
+    fr_pdl_wait();
+    fr_pdl_launch();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int item = blockIdx.x * 4 + warp;
     if (item >= p.rows * p.nq) return;

@@ -92,6 +92,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
     uint8_t* s_k = s_q + ROWS_CTA * ROW_BYTES;        // [2][64][ROW_BYTES]
     uint8_t* s_v = s_k + 2 * KV_BYTES;                // [2][64][ROW_BYTES]
 
+    fr_pdl_wait();
+    fr_pdl_launch();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int seq = blockIdx.z, kvh = blockIdx.y;
     const int split = blockIdx.x % p.splits, tile = blockIdx.x / p.splits;
@@ -366,7 +368,7 @@ int launch(const MmaArgs& p, dim3 grid, cudaStream_t stream) {
         FR_CUDA(cudaFuncSetAttribute(attention_mma_kernel<HD, KEYS_MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         configured = true;
     }
-    attention_mma_kernel<HD, KEYS_MODE><<<grid, WARPS * 32, smem, stream>>>(p);
+    FR_CUDA(fr_launch(attention_mma_kernel<HD, KEYS_MODE>, grid, dim3(WARPS * 32), smem, stream, p));
     FR_CHECK_LAUNCH("attention_mma");
     return FR_OK;
 }
@@ -419,7 +421,7 @@ FR_EXPORT int attention_mma(const void* q, int q_stride, void* out, const void* 
     if (rc) return rc;
     if (splits > 1) {
         MergeArgs mp{scratch, out, rows, nq, hd, splits};
-        attention_merge_kernel<bf16><<<(rows * nq + 3) / 4, 128, 0, stream>>>(mp);
+        FR_CUDA(fr_launch(attention_merge_kernel<bf16>, dim3((rows * nq + 3) / 4), dim3(128), 0, stream, mp));
         FR_CHECK_LAUNCH("attention merge");
     }
     return FR_OK;

@@ -12,10 +12,10 @@
 // decodeAttentionKernel and the split/combine pair (attention_kernels.cu:29-111,
 // 131-235), prefillAttentionKernel (:513-645); mask by range as there (j <= position).
 //
-// Geometry of a step: sequence b owns query rows cu_q[b] .. cu_q[b+1]-1; after the
-// step it holds kv_len[b] tokens, so its i-th query row stands at position
-// kv_len[b] - q_len + i.  Keys and values of position j are in page
-// block_table[b][j / page], row j % page, of pools laid out [pages][page][nkv][hd].
+// Geometry of a step: every row carries its sequence (row_seq, an index into the step's
+// block table) and its position (row_pos); it sees the keys of its sequence up to that
+// position.  Keys and values of position j are in page block_table[seq][j / page], row
+// j % page, of pools laid out [pages][page][nkv][hd].
 #include <math.h>
 
 #include "attention_merge.cuh"

@@ -10,6 +10,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 enum FrDtype { FR_F32 = 0, FR_BF16 = 1 };
 
@@ -69,4 +70,40 @@ __device__ __forceinline__ float fr_warp_max(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
     return v;
+}
+
+// ------------------------------------------------------------------ programmatic dependent launch
+// Every kernel of this library is launched so that it may start while its predecessor in
+// the stream is still draining (the launch itself, block scheduling and any prologue that
+// reads nothing the predecessor writes overlap with the predecessor's tail).  The contract
+// inside a kernel: fr_pdl_wait() before the first access to memory that an earlier kernel
+// may write or read; fr_pdl_launch() once the next kernel may be scheduled.  A kernel that
+// follows one of these in a stream but was launched the ordinary way is fully serialised,
+// as always.  FRIDAY_PDL=0 in the environment switches the launch attribute off.
+__device__ __forceinline__ void fr_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void fr_pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+static inline bool fr_pdl_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("FRIDAY_PDL");
+        v = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return v != 0;
+}
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t fr_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = fr_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }

@@ -58,6 +58,7 @@ struct GemmParams {
     int* counters;      // [tiles], zero between launches
     int* status;        // 0, or a code when a wait gave up
     int p_rows, q_rows, ldo, out_dtype, bias_dtype, swapped;
+    int act;            // 1: the product's columns are (gate, up) pairs; out gets silu(gate) * up, half as wide
     int tiles_p, tiles_q, splits, kb_total, kb_per;
 };
 
@@ -148,8 +149,41 @@ __device__ __forceinline__ float bias_at(const GemmParams& p, int i) {
     return p.bias_dtype == FR_F32 ? ((const float*)p.bias)[i] : __bfloat162float(((const __nv_bfloat16*)p.bias)[i]);
 }
 
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
+
+// Gated epilogue: rows 2f and 2f+1 of the weight are gate f and up f.  Must be called by whole warps.
+__device__ __forceinline__ void finish16_gated(const GemmParams& p, int gi, int gj0, float (&v)[16]) {
+    if (!p.swapped) {
+        // the pair sits in one thread: columns gj0 + 2j, gj0 + 2j + 1 -> out[gi][gj0/2 + j]
+        if (gi >= p.p_rows) return;
+        float r[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) r[j] = silu_mul(v[2 * j], v[2 * j + 1]);
+        const int oj0 = gj0 >> 1, o_cols = p.q_rows >> 1;
+        __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)gi * p.ldo + oj0;
+        if (oj0 + 8 <= o_cols && (p.ldo % 8 == 0) && (((uintptr_t)p.out & 15) == 0)) {
+            uint4 pk;
+            __nv_bfloat162* ph = (__nv_bfloat162*)&pk;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) ph[j] = __floats2bfloat162_rn(r[2 * j], r[2 * j + 1]);
+            *(uint4*)o = pk;
+        } else {
+            for (int j = 0; j < 8 && oj0 + j < o_cols; ++j) o[j] = __float2bfloat16_rn(r[j]);
+        }
+    } else {
+        // the pair sits in neighbouring lanes (TMEM lanes are weight rows): out[gj][gi/2]
+        float up[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) up[j] = __shfl_xor_sync(0xffffffffu, v[j], 1);
+        if ((gi & 1) || gi >= p.p_rows) return;
+        for (int j = 0; j < 16 && gj0 + j < p.q_rows; ++j)
+            ((__nv_bfloat16*)p.out)[(size_t)(gj0 + j) * p.ldo + (gi >> 1)] = __float2bfloat16_rn(silu_mul(v[j], up[j]));
+    }
+}
+
 // Bias, residual, rounding and store of 16 consecutive q-columns of P-row gi.
 __device__ __forceinline__ void finish16(const GemmParams& p, int gi, int gj0, float (&v)[16]) {
+    if (p.act) return finish16_gated(p, gi, gj0, v);
     if (gi >= p.p_rows) return;
     if (!p.swapped) {
         // out[gi][gj0 .. gj0+15]
@@ -258,6 +292,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) fr_pdl_launch();     // the next kernel may be scheduled; it waits for this one itself
 
     const int n_tiles = p.tiles_p * p.tiles_q;
     const int n_items = n_tiles * p.splits;
@@ -266,25 +301,58 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_p) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+            // The k-slices this CTA will load, in order: (work item, k block).
+            struct Walk {
+                int w, kb, kb1, p_blk, q_blk;
+            };
+            auto open_item = [&](Walk& k, int w) {
+                k.w = w;
+                if (w >= n_items) return;
+                const int tile = w / p.splits, split = w - tile * p.splits;
+                k.q_blk = tile / p.tiles_p;
+                k.p_blk = tile - k.q_blk * p.tiles_p;
+                k.kb = split * p.kb_per;
+                k.kb1 = min(k.kb + p.kb_per, p.kb_total);
+            };
+            auto step = [&](Walk& k) {
+                if (++k.kb >= k.kb1) open_item(k, k.w + gridDim.x);
+            };
+            // The weights do not depend on the kernel before this one; the activations do.  Fill the ring with
+            // weight slices first, then wait for the predecessor, then add the activation slices.
+            const CUtensorMap* map_w = p.swapped ? &map_p : &map_q;
+            const CUtensorMap* map_x = p.swapped ? &map_q : &map_p;
+            const uint32_t off_w = p.swapped ? 0 : P_BYTES, off_x = p.swapped ? P_BYTES : 0;
+            Walk head;
+            open_item(head, blockIdx.x);
+            Walk ahead = head;
+            int early = 0;
+            for (; early < STAGES && ahead.w < n_items; ++early, step(ahead)) {
+                mbar_expect_tx(full0 + 8 * early, STAGE_BYTES);
+                tma_load_2d(smem_u32(smem + early * STAGE_BYTES) + off_w, map_w, ahead.kb * TILE_K,
+                            p.swapped ? ahead.p_blk * TILE_P : ahead.q_blk * BN, full0 + 8 * early);
+            }
+            fr_pdl_wait();
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
-                const int tile = w / p.splits, split = w - tile * p.splits;
-                const int q_blk = tile / p.tiles_p, p_blk = tile - q_blk * p.tiles_p;
-                const int kb0 = split * p.kb_per, kb1 = min(kb0 + p.kb_per, p.kb_total);
-                for (int kb = kb0; kb < kb1; ++kb) {
+            for (; head.w < n_items && ok; step(head)) {
+                const uint32_t dst = smem_u32(smem + stage * STAGE_BYTES);
+                if (early > 0) {
+                    --early;                                 // the weight slice of this stage is already on its way
+                } else {
                     if (!(ok = mbar_wait(empty0 + 8 * stage, phase ^ 1, p.status, 1))) break;
-                    const uint32_t dst = smem_u32(smem + stage * STAGE_BYTES);
                     mbar_expect_tx(full0 + 8 * stage, STAGE_BYTES);
-                    tma_load_2d(dst, &map_p, kb * TILE_K, p_blk * TILE_P, full0 + 8 * stage);
-                    tma_load_2d(dst + P_BYTES, &map_q, kb * TILE_K, q_blk * BN, full0 + 8 * stage);
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                    tma_load_2d(dst + off_w, map_w, head.kb * TILE_K, p.swapped ? head.p_blk * TILE_P : head.q_blk * BN,
+                                full0 + 8 * stage);
                 }
+                tma_load_2d(dst + off_x, map_x, head.kb * TILE_K, p.swapped ? head.q_blk * BN : head.p_blk * TILE_P,
+                            full0 + 8 * stage);
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
+            fr_pdl_wait();
             constexpr uint32_t idesc = instr_desc(TILE_P, BN);
             int stage = 0;
             uint32_t phase = 0;
@@ -316,6 +384,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         const int quarter = warp & 3;                      // TMEM lanes this warp may read: 32*quarter ..
         const int i_local = quarter * 32 + lane;
         const int et = threadIdx.x - 64;                   // 0..127 among the epilogue threads
+        fr_pdl_wait();
         bool ok = true;
         int it = 0;
         for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x, ++it) {
@@ -425,7 +494,7 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmParams& p, in
         FR_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         configured = true;
     }
-    gemm_tc_kernel<BN, STAGES><<<grid, THREADS, smem, stream>>>(mp, mq, p);
+    FR_CUDA(fr_launch(gemm_tc_kernel<BN, STAGES>, dim3(grid), dim3(THREADS), smem, stream, mp, mq, p));
     FR_CHECK_LAUNCH("gemm_tc");
     return FR_OK;
 }
@@ -460,13 +529,31 @@ FR_EXPORT int gemm_tc_plan(int m, int n, int k, int sm_count, int swap, int bn, 
     return FR_OK;
 }
 
+FR_EXPORT int gemm_tc_act(const void* x, const void* w, void* out, int out_dtype, const void* bias, int bias_dtype,
+                          const void* residual, int m, int n, int k, int lda, int ldw, int ldo, float* scratch,
+                          long long scratch_floats, int* counters, int n_counters, int* status, int sm_count, int swap,
+                          int bn, int splits, int act, cudaStream_t stream);
+
 // x [m][k] (row stride lda), w [n][k] (ldw): bf16.  out, residual [m][n] (ldo), bf16 or fp32 (out_dtype).
 // scratch/counters/status: device buffers of the caller; counters must be zero on entry and are zero on return.
 FR_EXPORT int gemm_tc(const void* x, const void* w, void* out, int out_dtype, const void* bias, int bias_dtype,
                       const void* residual, int m, int n, int k, int lda, int ldw, int ldo, float* scratch,
                       long long scratch_floats, int* counters, int n_counters, int* status, int sm_count, int swap,
                       int bn, int splits, cudaStream_t stream) {
+    return gemm_tc_act(x, w, out, out_dtype, bias, bias_dtype, residual, m, n, k, lda, ldw, ldo, scratch, scratch_floats,
+                       counters, n_counters, status, sm_count, swap, bn, splits, 0, stream);
+}
+
+// The same with an activation in the epilogue.  act = 1: the rows of w are (gate, up) pairs, n is even, and
+// out [m][n/2] (bf16) receives silu(gate) * up; bias and residual must be null.
+FR_EXPORT int gemm_tc_act(const void* x, const void* w, void* out, int out_dtype, const void* bias, int bias_dtype,
+                          const void* residual, int m, int n, int k, int lda, int ldw, int ldo, float* scratch,
+                          long long scratch_floats, int* counters, int n_counters, int* status, int sm_count, int swap,
+                          int bn, int splits, int act, cudaStream_t stream) {
     if (m <= 0 || n <= 0) return FR_OK;
+    if (act != 0 && act != 1) FR_REFUSE("gemm_tc: unknown activation %d", act);
+    if (act && (n % 2 || bias != nullptr || residual != nullptr || out_dtype != FR_BF16))
+        FR_REFUSE("gemm_tc: the gated epilogue needs an even n, bf16 output, no bias and no residual");
     if (k <= 0 || k % 8 || lda % 8 || ldw % 8)
         FR_REFUSE("gemm_tc: k = %d and the row strides (%d, %d) must be multiples of 8 (16-byte rows for TMA)", k, lda, ldw);
     if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) FR_REFUSE("gemm_tc: operands must be 16-byte aligned");
@@ -482,6 +569,7 @@ FR_EXPORT int gemm_tc(const void* x, const void* w, void* out, int out_dtype, co
     p.out = out; p.bias = bias; p.residual = residual; p.ws = scratch; p.counters = counters; p.status = status;
     p.p_rows = swap ? n : m; p.q_rows = swap ? m : n; p.ldo = ldo; p.out_dtype = out_dtype; p.bias_dtype = bias_dtype;
     p.swapped = swap;
+    p.act = act;
     p.tiles_p = (p.p_rows + TILE_P - 1) / TILE_P; p.tiles_q = (p.q_rows + bn - 1) / bn;
     p.splits = splits; p.kb_total = (k + TILE_K - 1) / TILE_K; p.kb_per = (p.kb_total + splits - 1) / splits;
     CUtensorMap mp, mq;

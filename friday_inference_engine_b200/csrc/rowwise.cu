@@ -15,13 +15,26 @@
 FR_EXPORT const char* rowwise_last_error() { return fr_error_text; }
 
 // ------------------------------------------------------------------ embedding
+// Copies one row of `width` elements; 16 bytes at a time when rows start on 16-byte boundaries.
+template <typename T>
+__device__ __forceinline__ void copy_row(const T* __restrict__ src, T* __restrict__ dst, int width) {
+    constexpr int PER = 16 / sizeof(T);
+    if (width % PER == 0 && (((uintptr_t)src | (uintptr_t)dst) & 15) == 0) {
+        const uint4* s4 = (const uint4*)src;
+        uint4* d4 = (uint4*)dst;
+        for (int i = threadIdx.x; i < width / PER; i += blockDim.x) d4[i] = s4[i];
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ tokens, const T* __restrict__ table, T* __restrict__ out,
                                  int width) {
+    fr_pdl_wait();
+    fr_pdl_launch();
     const int row = blockIdx.x;
-    const T* src = table + (size_t)tokens[row] * width;
-    T* dst = out + (size_t)row * width;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = src[i];
+    copy_row(table + (size_t)tokens[row] * width, out + (size_t)row * width, width);
 }
 
 FR_EXPORT int rowwise_embedding(const int* tokens, const void* table, void* out, int n_rows, int width, int dtype,
@@ -30,8 +43,8 @@ FR_EXPORT int rowwise_embedding(const int* tokens, const void* table, void* out,
     if (dtype == FR_F32)
         embedding_kernel<float><<<n_rows, 256, 0, stream>>>(tokens, (const float*)table, (float*)out, width);
     else if (dtype == FR_BF16)
-        embedding_kernel<__nv_bfloat16>
-            <<<n_rows, 256, 0, stream>>>(tokens, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, width);
+        FR_CUDA(fr_launch(embedding_kernel<__nv_bfloat16>, dim3(n_rows), dim3(256), 0, stream, tokens,
+                          (const __nv_bfloat16*)table, (__nv_bfloat16*)out, width));
     else
         FR_REFUSE("embedding: unknown dtype %d", dtype);
     FR_CHECK_LAUNCH("embedding");
@@ -42,9 +55,9 @@ FR_EXPORT int rowwise_embedding(const int* tokens, const void* table, void* out,
 template <typename T>
 __global__ void gather_rows_kernel(const int* __restrict__ rows, const T* __restrict__ src, T* __restrict__ out,
                                    int width) {
-    const T* s = src + (size_t)rows[blockIdx.x] * width;
-    T* d = out + (size_t)blockIdx.x * width;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) d[i] = s[i];
+    fr_pdl_wait();
+    fr_pdl_launch();
+    copy_row(src + (size_t)rows[blockIdx.x] * width, out + (size_t)blockIdx.x * width, width);
 }
 
 FR_EXPORT int rowwise_gather_rows(const int* rows, const void* src, void* out, int n_rows, int width, int dtype,
@@ -53,8 +66,8 @@ FR_EXPORT int rowwise_gather_rows(const int* rows, const void* src, void* out, i
     if (dtype == FR_F32)
         gather_rows_kernel<float><<<n_rows, 256, 0, stream>>>(rows, (const float*)src, (float*)out, width);
     else if (dtype == FR_BF16)
-        gather_rows_kernel<__nv_bfloat16>
-            <<<n_rows, 256, 0, stream>>>(rows, (const __nv_bfloat16*)src, (__nv_bfloat16*)out, width);
+        FR_CUDA(fr_launch(gather_rows_kernel<__nv_bfloat16>, dim3(n_rows), dim3(256), 0, stream, rows,
+                          (const __nv_bfloat16*)src, (__nv_bfloat16*)out, width));
     else
         FR_REFUSE("gather_rows: unknown dtype %d", dtype);
     FR_CHECK_LAUNCH("gather_rows");
@@ -66,6 +79,8 @@ FR_EXPORT int rowwise_gather_rows(const int* rows, const void* src, void* out, i
 template <typename T>
 __global__ void rmsnorm_kernel(const T* __restrict__ x, FrVec w, T* __restrict__ y, int width, float eps) {
     __shared__ float partial[32];
+    fr_pdl_wait();
+    fr_pdl_launch();
     const T* xr = x + (size_t)blockIdx.x * width;
     T* yr = y + (size_t)blockIdx.x * width;
     float ss = 0.f;
@@ -86,12 +101,62 @@ __global__ void rmsnorm_kernel(const T* __restrict__ x, FrVec w, T* __restrict__
     for (int i = threadIdx.x; i < width; i += blockDim.x) fr_store(yr + i, fr_load(xr + i) * inv * w.at(i));
 }
 
+// bf16 rows of up to 8 * 256 * RMS_CHUNKS elements, a multiple of 8: every thread keeps its 16-byte pieces in
+// registers between the sum of squares and the scaling, so the row is read once.
+constexpr int RMS_CHUNKS = 4;
+__global__ void __launch_bounds__(256)
+rmsnorm_bf16_kernel(const __nv_bfloat16* __restrict__ x, FrVec w, __nv_bfloat16* __restrict__ y, int width, float eps) {
+    __shared__ float partial[8];
+    fr_pdl_wait();
+    fr_pdl_launch();
+    const int n_chunks = width / 8;
+    const uint4* xr = (const uint4*)(x + (size_t)blockIdx.x * width);
+    uint4* yr = (uint4*)(y + (size_t)blockIdx.x * width);
+    uint4 v[RMS_CHUNKS];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < RMS_CHUNKS; ++i) {
+        const int c = threadIdx.x + 256 * i;
+        if (c < n_chunks) {
+            v[i] = xr[c];
+            const __nv_bfloat162* h = (const __nv_bfloat162*)&v[i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(h[j]);
+                ss += f.x * f.x + f.y * f.y;
+            }
+        }
+    }
+    ss = fr_warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) total += partial[i];
+    const float inv = 1.0f / sqrtf(total / (float)width + eps);
+#pragma unroll
+    for (int i = 0; i < RMS_CHUNKS; ++i) {
+        const int c = threadIdx.x + 256 * i;
+        if (c < n_chunks) {
+            const __nv_bfloat16* h = (const __nv_bfloat16*)&v[i];
+            uint4 o;
+            __nv_bfloat16* oh = (__nv_bfloat16*)&o;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) oh[j] = __float2bfloat16_rn(__bfloat162float(h[j]) * inv * w.at(c * 8 + j));
+            yr[c] = o;
+        }
+    }
+}
+
 FR_EXPORT int rowwise_rmsnorm(const void* x, const void* w, int w_dtype, void* y, int n_rows, int width, float eps,
                               int dtype, cudaStream_t stream) {
     if (n_rows <= 0) return FR_OK;
     FrVec wv{w, w_dtype};
     if (dtype == FR_F32)
         rmsnorm_kernel<float><<<n_rows, 256, 0, stream>>>((const float*)x, wv, (float*)y, width, eps);
+    else if (dtype == FR_BF16 && width % 8 == 0 && width <= 8 * 256 * RMS_CHUNKS && (((uintptr_t)x | (uintptr_t)y) & 15) == 0)
+        FR_CUDA(fr_launch(rmsnorm_bf16_kernel, dim3(n_rows), dim3(256), 0, stream, (const __nv_bfloat16*)x, wv,
+                          (__nv_bfloat16*)y, width, eps));
     else if (dtype == FR_BF16)
         rmsnorm_kernel<__nv_bfloat16>
             <<<n_rows, 256, 0, stream>>>((const __nv_bfloat16*)x, wv, (__nv_bfloat16*)y, width, eps);
@@ -102,15 +167,16 @@ FR_EXPORT int rowwise_rmsnorm(const void* x, const void* w, int w_dtype, void* y
 }
 
 // ------------------------------------------------------------------ SwiGLU
-// gu is [rows][2*inner]: gate in the first `inner` columns, up in the last.
+// gu is [rows][2*inner] with gate and up interleaved: column 2f is gate f, column 2f+1 is up f (the rows of
+// the two projection matrices are stacked alternately, so that a product's tile holds both).
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inner, size_t total) {
+    fr_pdl_wait();
+    fr_pdl_launch();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
-        const size_t row = idx / inner;
-        const int col = (int)(idx - row * inner);
-        const float g = fr_load(gu + row * 2 * inner + col);
-        const float u = fr_load(gu + row * 2 * inner + inner + col);
+        const float g = fr_load(gu + 2 * idx);
+        const float u = fr_load(gu + 2 * idx + 1);
         fr_store(out + idx, g / (1.0f + expf(-g)) * u);
     }
 }
@@ -122,8 +188,8 @@ FR_EXPORT int rowwise_swiglu(const void* gu, void* out, int n_rows, int inner, i
     if (dtype == FR_F32)
         swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, inner, total);
     else if (dtype == FR_BF16)
-        swiglu_kernel<__nv_bfloat16>
-            <<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inner, total);
+        FR_CUDA(fr_launch(swiglu_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)gu,
+                          (__nv_bfloat16*)out, inner, total));
     else
         FR_REFUSE("swiglu: unknown dtype %d", dtype);
     FR_CHECK_LAUNCH("swiglu");
@@ -143,6 +209,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
                                      const int* __restrict__ row_pos, const float* __restrict__ denom, int rot,
                                      int nq, int nkv, int hd, T* __restrict__ k_pool, T* __restrict__ v_pool,
                                      const int* __restrict__ block_table, int table_width, int page, int write) {
+    fr_pdl_wait();
+    fr_pdl_launch();
     const int row = blockIdx.x;
     const int seq = row_seq[row];
     if (seq < 0) return;
@@ -192,9 +260,9 @@ FR_EXPORT int rowwise_rope_kv_write(void* qkv, const int* row_seq, const int* ro
                                                                     hd, (float*)k_pool, (float*)v_pool, block_table,
                                                                     table_width, page, write);
     else if (dtype == FR_BF16)
-        rope_kv_write_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(
-            (__nv_bfloat16*)qkv, row_seq, row_pos, denom, rot, nq, nkv, hd, (__nv_bfloat16*)k_pool,
-            (__nv_bfloat16*)v_pool, block_table, table_width, page, write);
+        FR_CUDA(fr_launch(rope_kv_write_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream,
+                          (__nv_bfloat16*)qkv, row_seq, row_pos, denom, rot, nq, nkv, hd, (__nv_bfloat16*)k_pool,
+                          (__nv_bfloat16*)v_pool, block_table, table_width, page, write));
     else
         FR_REFUSE("rotary: unknown dtype %d", dtype);
     FR_CHECK_LAUNCH("rope_kv_write");
@@ -206,6 +274,8 @@ FR_EXPORT int rowwise_rope_kv_write(void* qkv, const int* row_seq, const int* ro
 // input, position and length of every live row grow by one.
 __global__ void advance_kernel(int* tokens, const int* __restrict__ sampled, int* row_pos, int* kv_len,
                                const int* __restrict__ row_seq, int n) {
+    fr_pdl_wait();
+    fr_pdl_launch();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n || row_seq[i] < 0) return;
     tokens[i] = sampled[i];
@@ -216,7 +286,8 @@ __global__ void advance_kernel(int* tokens, const int* __restrict__ sampled, int
 FR_EXPORT int rowwise_advance(int* tokens, const int* sampled, int* row_pos, int* kv_len, const int* row_seq, int n,
                               cudaStream_t stream) {
     if (n <= 0) return FR_OK;
-    advance_kernel<<<(n + 127) / 128, 128, 0, stream>>>(tokens, sampled, row_pos, kv_len, row_seq, n);
+    FR_CUDA(fr_launch(advance_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, tokens, sampled, row_pos, kv_len,
+                      row_seq, n));
     FR_CHECK_LAUNCH("advance");
     return FR_OK;
 }

@@ -48,6 +48,8 @@ sample_kernel(const float* __restrict__ logits, int vocab, int ld, const float* 
     __shared__ float s_scan[THREADS];
     __shared__ float s_max;
     __shared__ int s_pick;
+    fr_pdl_wait();
+    fr_pdl_launch();
     const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (row_live != nullptr && row_live[row] < 0) {
         if (tid == 0) out[row] = 0;
@@ -135,8 +137,8 @@ FR_EXPORT int sampling_sample(const float* logits, int rows, int vocab, int ld, 
                               int* out, cudaStream_t stream) {
     if (rows <= 0) return FR_OK;
     if (vocab <= 0) FR_REFUSE("sample: vocabulary of %d", vocab);
-    sample_kernel<<<rows, THREADS, 0, stream>>>(logits, vocab, ld, temperature, stream_ids, steps, seed, row_live,
-                                                 out);
+    FR_CUDA(fr_launch(sample_kernel, dim3(rows), dim3(THREADS), 0, stream, logits, vocab, ld, temperature, stream_ids,
+                      steps, seed, row_live, out));
     FR_CHECK_LAUNCH("sample");
     return FR_OK;
 }

@@ -155,15 +155,27 @@ class CudaOps:
                 and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0
                 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
-    def _linear_tc(self, x, weight, bias, residual, out, swap=-1, bn=-1, splits=-1):
+    def _linear_tc(self, x, weight, bias, residual, out, swap=-1, bn=-1, splits=-1, act=0):
         scratch, counters, status, sms = self._tc_buffers(x.device)
         rows, k = x.shape
         lib.family("gemm_tc").call(
-            "gemm_tc", _ptr(x), _ptr(weight), _ptr(out), code_of(out.dtype), _ptr(bias),
+            "gemm_tc_act", _ptr(x), _ptr(weight), _ptr(out), code_of(out.dtype), _ptr(bias),
             code_of(bias.dtype) if bias is not None else 0, _ptr(residual), rows, weight.shape[0], k, x.stride(0),
             weight.stride(0), out.stride(0), _ptr(scratch), scratch.numel(), _ptr(counters), counters.numel(),
-            _ptr(status), sms, swap, bn, splits, _stream())
+            _ptr(status), sms, swap, bn, splits, act, _stream())
         return out
+
+    def linear_swiglu(self, x, weight_pairs):
+        """silu(x Wg^T) * (x Wu^T) for weight_pairs [2 * inner, k] whose rows alternate gate, up: one product
+        with the activation in its epilogue on the tensor cores, else the product followed by the kernel."""
+        _need_cuda(x, weight_pairs)
+        _rowmajor(x, "linear input")
+        _rowmajor(weight_pairs, "linear weight")
+        rows, inner = x.shape[0], weight_pairs.shape[0] // 2
+        out = torch.empty((rows, inner), dtype=x.dtype, device=x.device)
+        if self.tensor_core_ok(x, weight_pairs, out, None) and out.dtype == torch.bfloat16:
+            return self._linear_tc(x, weight_pairs, None, None, out, act=1)
+        return self.swiglu(self.linear(x, weight_pairs))
 
     def check_status(self):
         """Raises if a kernel recorded that one of its waits gave up (reads one word per device; call it
@@ -293,6 +305,10 @@ def rmsnorm(*a, **k):
 
 def swiglu(*a, **k):
     return _backend.swiglu(*a, **k)
+
+
+def linear_swiglu(*a, **k):
+    return _backend.linear_swiglu(*a, **k)
 
 
 def rope_kv_write(*a, **k):

@@ -25,6 +25,7 @@ _SIGNATURES = {
     },
     "gemm_tc": {
         "gemm_tc": [P, P, P, I, P, I, P, I, I, I, I, I, I, P, c_longlong, P, I, P, I, I, I, I, P],
+        "gemm_tc_act": [P, P, P, I, P, I, P, I, I, I, I, I, I, P, c_longlong, P, I, P, I, I, I, I, I, P],
         "gemm_tc_plan": [I, I, I, I, I, I, I, P],
     },
     "attention_simt": {

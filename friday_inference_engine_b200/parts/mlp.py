@@ -1,9 +1,11 @@
 """Gated feed-forward: x + Wd (silu(Wg h) * (Wu h)).
 
-Gate and up are one product over the stacked matrices, as the reference runs the two
-in one launch (transformer.cpp:1064-1066); silu(z) = z / (1 + e^-z) times up
-(cpu_ops.cpp:85-101, without its shortcuts for |z| > 20); the residual is added in the
-down product's epilogue (transformer.cpp:1072).
+Gate and up are one product, as the reference runs the two in one launch
+(transformer.cpp:1064-1066): their rows are stacked alternately (gate 0, up 0, gate 1,
+...), so that every tile of the product holds both halves of a pair and
+silu(z) = z / (1 + e^-z) times up (cpu_ops.cpp:85-101, without its shortcuts for
+|z| > 20) can be applied in the product's epilogue; the residual is added in the down
+product's epilogue (transformer.cpp:1072).
 """
 import torch
 
@@ -27,9 +29,8 @@ class SwiGLU(Part):
         t = self.tensors
         ws = [t.pop("gate_proj.weight"), t.pop("up_proj.weight")]
         wdt = torch.float32 if any(w.dtype == torch.float32 for w in ws) else ws[0].dtype
-        self.w_gate_up = torch.cat([w.to(wdt) for w in ws], dim=0).contiguous()
+        self.w_gate_up = torch.stack([w.to(wdt) for w in ws], dim=1).reshape(2 * self.inner, -1).contiguous()
         self.w_down = t["down_proj.weight"]
 
     def forward(self, h, residual, ctx):
-        gate_up = ops.linear(h, self.w_gate_up)
-        return ops.linear(ops.swiglu(gate_up), self.w_down, residual=residual)
+        return ops.linear(ops.linear_swiglu(h, self.w_gate_up), self.w_down, residual=residual)

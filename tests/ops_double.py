@@ -28,9 +28,11 @@ class TorchOps:
         return y.to(x.dtype)
 
     def swiglu(self, gate_up):
-        inner = gate_up.shape[1] // 2
-        g, u = gate_up[:, :inner].double(), gate_up[:, inner:].double()
+        g, u = gate_up[:, 0::2].double(), gate_up[:, 1::2].double()      # columns alternate gate, up
         return (g / (1.0 + torch.exp(-g)) * u).to(gate_up.dtype)
+
+    def linear_swiglu(self, x, weight_pairs):
+        return self.swiglu(self.linear(x, weight_pairs))
 
     def rope_kv_write(self, qkv, row_seq, row_pos, denom, rotary_dim, n_heads, n_kv_heads, head_dim,
                       k_pool=None, v_pool=None, block_table=None, page_size=0):

@@ -51,7 +51,7 @@ def test_rmsnorm(dtype, width):
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_swiglu(dtype):
     gu = rnd((9, 2 * 177), dtype, 3, 4.0)
-    ref = pm.swiglu(f64(gu)[:, :177], f64(gu)[:, 177:])
+    ref = pm.swiglu(f64(gu)[:, 0::2], f64(gu)[:, 1::2])      # columns alternate gate, up
     close(ops.swiglu(gu), ref, dtype, "swiglu")
 
 
@@ -361,3 +361,22 @@ def test_attention_mma_dead_rows_give_zero():
                                 torch.ones(2, **i32), torch.tensor([5, 9], **i32), live, 2, 1, nq, nkv, hd, None, 1.0,
                                 True, 2, Geo(10))
     assert float(out.float().abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("m,inner,k", [(1, 64, 64), (8, 18944, 3584), (40, 177, 512), (64, 200, 96), (100, 177, 512),
+                                       (300, 1000, 1024), (2048, 2368, 512)])
+def test_gemm_tensor_core_gated_epilogue(m, inner, k):
+    dt = torch.bfloat16
+    x = rnd((m, k), dt, 41)
+    wg, wu = rnd((inner, k), dt, 42, 0.05), rnd((inner, k), dt, 43, 0.05)
+    pairs = torch.stack([wg, wu], dim=1).reshape(2 * inner, k).contiguous()
+    ref = pm.swiglu(pm.linear(f64(x), f64(wg)), pm.linear(f64(x), f64(wu)))
+    close(ops.linear_swiglu(x, pairs), ref, dt, "product with silu(gate) * up in the epilogue", bf16_rel=0.01)
+    be = ops.backend()
+    for swap, bn, splits in ((1, 64, 3), (0, 128, 2), (0, 256, 1)):
+        if swap and m > 64:
+            continue
+        out = torch.empty((m, inner), dtype=dt, device=DEV)
+        close(be._linear_tc(x, pairs, None, None, out, swap=swap, bn=bn, splits=splits, act=1), ref, dt,
+              "gated, swap %d bn %d splits %d" % (swap, bn, splits), bf16_rel=0.01)
+    be.check_status()
