@@ -47,6 +47,8 @@ struct MmaArgs {
     const int* seq_pos0;      // position of its first row
     const int* seq_live;      // may be null; < 0 at seq_start[s]: the sequence has ended (row marker)
     float* part;              // [rows * nq][splits][hd + 2] when splits > 1
+    int* counters;            // keys mode with splits: one per (sequence, kv head, row tile), zero between launches;
+                              // the CTA that finishes a tile's last split merges the splits itself
     int q_stride, table_width, nq, nkv, window, splits;
     float scale_log2;         // softmax scale times log2(e)
 };
@@ -353,6 +355,55 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
                 dst[HD + 1] = l;
             }
         }
+        if (p.splits > 1 && p.counters != nullptr) {
+            // Whoever writes a tile's last partial merges them: no second kernel, the partials are still in L2.
+            __shared__ int s_last;
+            __threadfence();
+            __syncthreads();
+            if (tid == 0) {
+                int* c = p.counters + ((size_t)seq * p.nkv + kvh) * (gridDim.x / p.splits) + tile;
+                s_last = atomicAdd(c, 1) == p.splits - 1;
+                if (s_last) *c = 0;                   // ready for the next launch
+            }
+            __syncthreads();
+            if (s_last) {
+                __threadfence();
+                const bool valid = rr < n_rows;
+                const int t = valid ? rr / G : 0, h = kvh * G + (valid ? rr - t * G : 0);
+                const size_t item = (size_t)(q_start + t) * p.nq + h;
+                const float* base = p.part + item * p.splits * (HD + 2);
+                float big = -INFINITY;
+                if (valid)
+                    for (int sp = tid & 7; sp < p.splits; sp += 8) big = fmaxf(big, __ldcg(base + (size_t)sp * (HD + 2) + HD));
+#pragma unroll
+                for (int o2 = 1; o2 < 8; o2 <<= 1) big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, o2));
+                float l = 0.f;
+                if (valid)
+                    for (int sp = tid & 7; sp < p.splits; sp += 8) {
+                        const float ls = __ldcg(base + (size_t)sp * (HD + 2) + HD + 1);
+                        if (ls > 0.f) l += ls * expf(__ldcg(base + (size_t)sp * (HD + 2) + HD) - big);
+                    }
+#pragma unroll
+                for (int o2 = 1; o2 < 8; o2 <<= 1) l += __shfl_xor_sync(0xffffffffu, l, o2);
+                if (valid) {
+                    constexpr int PER = HD / 8;           // consecutive dims per thread
+                    const int d0 = (tid & 7) * PER;
+                    float acc[PER];
+#pragma unroll
+                    for (int i = 0; i < PER; ++i) acc[i] = 0.f;
+                    for (int sp = 0; sp < p.splits; ++sp) {
+                        const float* ps = base + (size_t)sp * (HD + 2);
+                        const float ls = __ldcg(ps + HD + 1);
+                        const float f = ls > 0.f ? expf(__ldcg(ps + HD) - big) : 0.f;
+#pragma unroll
+                        for (int i = 0; i < PER; ++i) acc[i] += __ldcg(ps + d0 + i) * f;
+                    }
+                    const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+                    for (int i = 0; i < PER; ++i) p.out[item * HD + d0 + i] = __float2bfloat16_rn(acc[i] * inv);
+                }
+            }
+        }
     }
 }
 
@@ -396,12 +447,13 @@ FR_EXPORT int attention_mma_supports(int hd, int page) { return hd % 16 == 0 && 
 // seq_start/seq_qlen/seq_pos0: per sequence, its first row, its rows in this step, the position of its first row.
 // seq_live (may be null): indexed by a sequence's first row; negative marks a sequence that has ended.
 // max_q_len: the longest seq_qlen (sizes the grid).  keys_mode: 1 for one-token steps.  splits > 1 needs
-// scratch of rows * nq * splits * (hd + 2) floats.
+// scratch of rows * nq * splits * (hd + 2) floats.  counters (may be null): n_counters zeroed ints; with them the
+// splits of a one-token step are merged inside the kernel, without them by a second kernel.
 FR_EXPORT int attention_mma(const void* q, int q_stride, void* out, const void* k_pool, const void* v_pool,
                             const int* block_table, int table_width, int page, const int* seq_start,
                             const int* seq_qlen, const int* seq_pos0, const int* seq_live, int n_seqs, int rows,
                             int max_q_len, int nq, int nkv, int hd, int window, float scale, int keys_mode, int splits,
-                            float* scratch, cudaStream_t stream) {
+                            float* scratch, int* counters, int n_counters, cudaStream_t stream) {
     if (n_seqs <= 0 || rows <= 0) return FR_OK;
     if (!attention_mma_supports(hd, page)) FR_REFUSE("attention_mma: head size %d / page %d is not built", hd, page);
     if (nkv <= 0 || nq % nkv != 0) FR_REFUSE("attention: %d heads cannot share %d key/value heads", nq, nkv);
@@ -411,15 +463,16 @@ FR_EXPORT int attention_mma(const void* q, int q_stride, void* out, const void* 
     MmaArgs p;
     p.q = (const bf16*)q; p.out = (bf16*)out; p.k_pool = (const bf16*)k_pool; p.v_pool = (const bf16*)v_pool;
     p.block_table = block_table; p.seq_start = seq_start; p.seq_qlen = seq_qlen; p.seq_pos0 = seq_pos0;
-    p.seq_live = seq_live; p.part = scratch; p.q_stride = q_stride; p.table_width = table_width; p.nq = nq;
+    p.seq_live = seq_live; p.part = scratch; p.counters = keys_mode ? counters : nullptr; p.q_stride = q_stride; p.table_width = table_width; p.nq = nq;
     p.nkv = nkv; p.window = window; p.splits = splits; p.scale_log2 = scale * LOG2E;
     const int G = nq / nkv;
     const int rows_cta = keys_mode ? 16 : 64;
     const int tiles = (max_q_len * G + rows_cta - 1) / rows_cta;
+    if (p.counters != nullptr && (long long)n_seqs * nkv * tiles > n_counters) p.counters = nullptr;   // merge kernel instead
     dim3 grid(tiles * splits, nkv, n_seqs);
     int rc = keys_mode ? launch_hd<true>(hd, p, grid, stream) : launch_hd<false>(hd, p, grid, stream);
     if (rc) return rc;
-    if (splits > 1) {
+    if (splits > 1 && p.counters == nullptr) {
         MergeArgs mp{scratch, out, rows, nq, hd, splits};
         FR_CUDA(fr_launch(attention_merge_kernel<bf16>, dim3((rows * nq + 3) / 4), dim3(128), 0, stream, mp));
         FR_CHECK_LAUNCH("attention merge");

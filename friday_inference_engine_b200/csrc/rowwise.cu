@@ -209,6 +209,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
                                      const int* __restrict__ row_pos, const float* __restrict__ denom, int rot,
                                      int nq, int nkv, int hd, T* __restrict__ k_pool, T* __restrict__ v_pool,
                                      const int* __restrict__ block_table, int table_width, int page, int write) {
+    extern __shared__ float cos_sin[];           // [rot/2][2], the row's angles, shared by all heads
     fr_pdl_wait();
     fr_pdl_launch();
     const int row = blockIdx.x;
@@ -216,32 +217,67 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
     if (seq < 0) return;
     const int pos = row_pos[row];
     T* base = qkv + (size_t)row * (nq + 2 * nkv) * hd;
-    size_t cache_row = 0;
-    if (write) {
-        const int pg = block_table[(size_t)seq * table_width + pos / page];
-        cache_row = ((size_t)pg * page + pos % page) * nkv * hd;
-    }
     const int half = rot / 2;
     if (denom != nullptr) {
-        const int n_pairs = (nq + nkv) * half;
-        for (int idx = threadIdx.x; idx < n_pairs; idx += blockDim.x) {
-            const int h = idx / half, i = idx - h * half;
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
             float s, c;
             sincosf(__fdiv_rn((float)pos, denom[i]), &s, &c);
-            T* v = base + (size_t)h * hd;
-            const float a = fr_load(v + i), b = fr_load(v + i + half);
-            fr_store(v + i, a * c - b * s);
-            fr_store(v + i + half, a * s + b * c);
+            cos_sin[2 * i] = c;
+            cos_sin[2 * i + 1] = s;
         }
         __syncthreads();
     }
+    T* k_dst = nullptr;
+    T* v_dst = nullptr;
     if (write) {
-        const int kv = nkv * hd;
-        const T* k = base + (size_t)nq * hd;
-        const T* v = k + kv;
-        for (int i = threadIdx.x; i < kv; i += blockDim.x) {
-            k_pool[cache_row + i] = k[i];
-            v_pool[cache_row + i] = v[i];
+        const int pg = block_table[(size_t)seq * table_width + pos / page];
+        const size_t cache_row = ((size_t)pg * page + pos % page) * nkv * hd;
+        k_dst = k_pool + cache_row;
+        v_dst = v_pool + cache_row;
+    }
+    // The heads (q, then k, then v) are dealt out to the blocks of this row.
+    const int heads = nq + 2 * nkv;
+    const int per = (heads + gridDim.y - 1) / gridDim.y;
+    const int h0 = blockIdx.y * per, h1 = min(h0 + per, heads);
+    // q and k heads: rotate the pairs (i, i + rot/2) in place; k also goes to the cache.
+    const int rot_heads = max(0, min(h1, nq + nkv) - h0);
+    if (denom != nullptr) {
+        for (int idx = threadIdx.x; idx < rot_heads * half; idx += blockDim.x) {
+            const int h = h0 + idx / half, i = idx % half;
+            const float c = cos_sin[2 * i], s = cos_sin[2 * i + 1];
+            T* v = base + (size_t)h * hd;
+            const float a = fr_load(v + i), b = fr_load(v + i + half);
+            const float ra = a * c - b * s, rb = a * s + b * c;
+            fr_store(v + i, ra);
+            fr_store(v + i + half, rb);
+            if (write && h >= nq) {
+                fr_store(k_dst + (size_t)(h - nq) * hd + i, ra);
+                fr_store(k_dst + (size_t)(h - nq) * hd + i + half, rb);
+            }
+        }
+    }
+    if (write) {
+        // what the rotation did not write: k beyond the rotated dimensions (all of k without rotation), and v
+        const int k_from = denom != nullptr ? rot : 0;
+        const int k_tail = hd - k_from;
+        const int kh0 = max(h0, nq), kh1 = min(h1, nq + nkv);
+        for (int idx = threadIdx.x; idx < max(0, kh1 - kh0) * k_tail; idx += blockDim.x) {
+            const int h = kh0 + idx / k_tail, d = k_from + idx % k_tail;
+            k_dst[(size_t)(h - nq) * hd + d] = base[(size_t)h * hd + d];
+        }
+        const int vh0 = max(h0, nq + nkv), vh1 = h1;
+        constexpr int PER = 16 / sizeof(T);
+        if (hd % PER == 0 && ((((uintptr_t)base) | ((uintptr_t)v_dst)) & 15) == 0) {
+            const int chunks = hd / PER;
+            for (int idx = threadIdx.x; idx < max(0, vh1 - vh0) * chunks; idx += blockDim.x) {
+                const int h = vh0 + idx / chunks, ch = idx % chunks;
+                ((uint4*)(v_dst + (size_t)(h - nq - nkv) * hd))[ch] = ((const uint4*)(base + (size_t)h * hd))[ch];
+            }
+        } else {
+            for (int idx = threadIdx.x; idx < max(0, vh1 - vh0) * hd; idx += blockDim.x) {
+                const int h = vh0 + idx / hd, d = idx % hd;
+                v_dst[(size_t)(h - nq - nkv) * hd + d] = base[(size_t)h * hd + d];
+            }
         }
     }
 }
@@ -255,12 +291,15 @@ FR_EXPORT int rowwise_rope_kv_write(void* qkv, const int* row_seq, const int* ro
     if (write && (k_pool == nullptr || v_pool == nullptr || block_table == nullptr))
         FR_REFUSE("rotary: cache write asked for without a cache");
     const int threads = 256;
+    const int heads = nq + 2 * nkv;
+    const dim3 grid(n_rows, n_rows < 64 ? (heads < 4 ? heads : 4) : 1);     // few rows: spread the heads over more SMs
+    const size_t smem = (size_t)(rot > 0 ? rot : 2) * sizeof(float);
     if (dtype == FR_F32)
-        rope_kv_write_kernel<float><<<n_rows, threads, 0, stream>>>((float*)qkv, row_seq, row_pos, denom, rot, nq, nkv,
-                                                                    hd, (float*)k_pool, (float*)v_pool, block_table,
-                                                                    table_width, page, write);
+        rope_kv_write_kernel<float><<<grid, threads, smem, stream>>>((float*)qkv, row_seq, row_pos, denom, rot, nq, nkv,
+                                                                     hd, (float*)k_pool, (float*)v_pool, block_table,
+                                                                     table_width, page, write);
     else if (dtype == FR_BF16)
-        FR_CUDA(fr_launch(rope_kv_write_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream,
+        FR_CUDA(fr_launch(rope_kv_write_kernel<__nv_bfloat16>, grid, dim3(threads), smem, stream,
                           (__nv_bfloat16*)qkv, row_seq, row_pos, denom, rot, nq, nkv, hd, (__nv_bfloat16*)k_pool,
                           (__nv_bfloat16*)v_pool, block_table, table_width, page, write));
     else

@@ -51,6 +51,7 @@ class CudaOps:
 
     def __init__(self):
         self._tc = {}
+        self._attn_counters = {}
 
     # -- row-wise ---------------------------------------------------------
     def embedding(self, tokens, table):
@@ -240,20 +241,28 @@ class CudaOps:
         scratch = None
         if splits > 1:
             scratch = geometry.scratch(rows * n_heads * splits * (head_dim + 2), q.device)
+        counters = self._attention_counters(q.device)
         lib.family("attention_mma").call(
             "attention_mma", _ptr(q), q_stride, _ptr(out), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
             block_table.shape[1], 64, _ptr(seq_start), _ptr(seq_qlen), _ptr(seq_pos0), _ptr(seq_live), n_seqs, rows,
             max_q_len, n_heads, n_kv_heads, head_dim, window or 0, float(scale), 1 if keys_mode else 0, splits,
-            _ptr(scratch), _stream())
+            _ptr(scratch), _ptr(counters), counters.numel(), _stream())
+
+    def _attention_counters(self, device):
+        """Zeroed ints, one per (sequence, kv head, row tile) of a one-token step; the kernel leaves them zero."""
+        c = self._attn_counters.get(device)
+        if c is None:
+            c = self._attn_counters[device] = torch.zeros((1 << 16,), dtype=torch.int32, device=device)
+        return c
 
     def decode_splits(self, n_seqs, n_heads, n_kv_heads, max_kv_len, device):
-        """CTAs that share one sequence's keys in a one-token step: enough to put about four small CTAs on
-        every SM, never more than there are key blocks."""
+        """CTAs that share one sequence's keys in a one-token step: as many as fit on the GPU at once (three
+        of these CTAs fit an SM at head size 128), never more than there are key blocks."""
         sms = self._tc_buffers(device)[3]
         group = n_heads // n_kv_heads
         base = n_seqs * n_kv_heads * ((group + 15) // 16)
         blocks = (max_kv_len + 63) // 64
-        return int(max(1, min((4 * sms + base - 1) // base, blocks, 256)))
+        return int(max(1, min((3 * sms) // base, blocks, 256)))
 
     @staticmethod
     def attention_splits(rows, n_heads, max_kv_len):
