@@ -372,6 +372,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
                 const int t = valid ? rr / G : 0, h = kvh * G + (valid ? rr - t * G : 0);
                 const size_t item = (size_t)(q_start + t) * p.nq + h;
                 const float* base = p.part + item * p.splits * (HD + 2);
+                float* weight = c_o;                  // [16][splits]: exp(m_s - M), free again after the syncs above
                 float big = -INFINITY;
                 if (valid)
                     for (int sp = tid & 7; sp < p.splits; sp += 8) big = fmaxf(big, __ldcg(base + (size_t)sp * (HD + 2) + HD));
@@ -381,22 +382,25 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
                 if (valid)
                     for (int sp = tid & 7; sp < p.splits; sp += 8) {
                         const float ls = __ldcg(base + (size_t)sp * (HD + 2) + HD + 1);
-                        if (ls > 0.f) l += ls * expf(__ldcg(base + (size_t)sp * (HD + 2) + HD) - big);
+                        const float f = ls > 0.f ? expf(__ldcg(base + (size_t)sp * (HD + 2) + HD) - big) : 0.f;
+                        weight[r * p.splits + sp] = f;
+                        l += ls * f;
                     }
 #pragma unroll
                 for (int o2 = 1; o2 < 8; o2 <<= 1) l += __shfl_xor_sync(0xffffffffu, l, o2);
+                __syncwarp();                         // a row's eight threads sit in one warp
                 if (valid) {
                     constexpr int PER = HD / 8;           // consecutive dims per thread
                     const int d0 = (tid & 7) * PER;
                     float acc[PER];
 #pragma unroll
                     for (int i = 0; i < PER; ++i) acc[i] = 0.f;
+#pragma unroll 4
                     for (int sp = 0; sp < p.splits; ++sp) {
-                        const float* ps = base + (size_t)sp * (HD + 2);
-                        const float ls = __ldcg(ps + HD + 1);
-                        const float f = ls > 0.f ? expf(__ldcg(ps + HD) - big) : 0.f;
+                        const float* ps = base + (size_t)sp * (HD + 2) + d0;
+                        const float f = weight[r * p.splits + sp];
 #pragma unroll
-                        for (int i = 0; i < PER; ++i) acc[i] += __ldcg(ps + d0 + i) * f;
+                        for (int i = 0; i < PER; ++i) acc[i] += __ldcg(ps + i) * f;
                     }
                     const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
@@ -468,7 +472,8 @@ FR_EXPORT int attention_mma(const void* q, int q_stride, void* out, const void* 
     const int G = nq / nkv;
     const int rows_cta = keys_mode ? 16 : 64;
     const int tiles = (max_q_len * G + rows_cta - 1) / rows_cta;
-    if (p.counters != nullptr && (long long)n_seqs * nkv * tiles > n_counters) p.counters = nullptr;   // merge kernel instead
+    if (p.counters != nullptr && ((long long)n_seqs * nkv * tiles > n_counters || splits > 64))
+        p.counters = nullptr;                          // the merge kernel instead
     dim3 grid(tiles * splits, nkv, n_seqs);
     int rc = keys_mode ? launch_hd<true>(hd, p, grid, stream) : launch_hd<false>(hd, p, grid, stream);
     if (rc) return rc;

@@ -44,7 +44,11 @@ class DeviceDecoder:
         self.seed = int(seed)
         self.tables_host = self.cache.tables_for(self.slots)
         self.tables = [torch.from_numpy(t.copy()).to(dev) for t in self.tables_host]
-        self.ctx = StepContext(self, self.slots, [1] * n, [self.cache.max_seq_tokens] * n)
+        # Launch shapes depend on how long the longest sequence may be (how many ways its keys are split), so a
+        # captured step serves lengths up to a bound; when a sequence outgrows it, the next bound's step is
+        # captured.  Bounds double from 1,024 tokens.
+        self.bound = self._bound_for(max(self.cache.lens[s] for s in self.slots) + 1)
+        self.ctx = StepContext(self, self.slots, [1] * n, [self.bound] * n)
         self.ctx.tokens, self.ctx.row_seq, self.ctx.row_pos = self.tokens, self.row_seq, self.row_pos
         self.ctx.seq_start = torch.arange(n, **i32)              # one row per sequence
         self.ctx.seq_qlen = torch.ones(n, **i32)
@@ -56,15 +60,22 @@ class DeviceDecoder:
         self._pinned_out = torch.empty((n,), dtype=torch.int32).pin_memory() if dev.type == "cuda" else None
         self.use_graph = bool(use_graph) and dev.type == "cuda"
         self.graph = None
+        self.graphs = {}              # bound -> captured step
         self.eager_steps = 0
         self.launches_per_step = 0
         self.logits = None
 
+    def _bound_for(self, length):
+        bound = 1024
+        while bound < length:
+            bound *= 2
+        return min(bound, max(self.cache.max_seq_tokens, 1))
+
     # what parts ask of a context
     def scratch(self, n_floats, device):
         if self._scratch is None or self._scratch.numel() < n_floats:
-            if self.graph is not None:
-                raise RuntimeError("scratch grew after the step was captured")
+            self.graphs.clear()       # captured steps point at the old buffer: they are captured again when needed
+            self.graph = None
             self._scratch = torch.empty((int(n_floats),), dtype=torch.float32, device=device)
         return self._scratch
 
@@ -98,6 +109,12 @@ class DeviceDecoder:
         """One decode step.  tokens: host list with each row's input token (dead rows: anything), or None to go
         on with the tokens that the previous step chose.  The chosen tokens are in self.sampled afterwards."""
         self._sync_tables()
+        need = self._bound_for(max([self.cache.lens[s] for s, alive in zip(self.slots, self.live) if alive] or [0]) + 1)
+        if need != self.bound:
+            self.bound = need
+            self.ctx.max_kv_len = need
+            self.ctx.kv_lens = [need] * self.n
+            self.graph = self.graphs.get(need)
         if tokens is not None:
             if self._pinned is not None:
                 self._pinned.numpy()[:] = np.asarray(tokens, dtype=np.int32)
@@ -119,6 +136,7 @@ class DeviceDecoder:
                 with torch.cuda.graph(self.graph):
                     self._body()
                 lib.add_launches(before - lib.launch_count())     # capturing launched nothing
+                self.graphs[self.bound] = self.graph
             self.graph.replay()
             lib.add_launches(self.launches_per_step)
         live_slots = [s for s, alive in zip(self.slots, self.live) if alive]
@@ -139,3 +157,4 @@ class DeviceDecoder:
 
     def close(self):
         self.graph = None
+        self.graphs.clear()
