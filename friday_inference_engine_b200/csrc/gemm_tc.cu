@@ -236,17 +236,28 @@ __device__ __forceinline__ void finish16(const GemmParams& p, int gi, int gj0, f
             }
         }
     } else {
-        // transposed: out[gj][gi]; bias goes with gi
+        // transposed: out[gj][gi]; bias goes with gi.  The residual may be `out` itself, so the compiler must keep
+        // every load before the store that follows it: all loads are issued first, then all stores, or the 16
+        // columns would cost 16 round trips to memory one after the other.
         const float b = p.bias ? bias_at(p, gi) : 0.f;
-        for (int j = 0; j < 16 && gj0 + j < p.q_rows; ++j) {
-            const size_t at = (size_t)(gj0 + j) * p.ldo + gi;
-            float x = v[j] + b;
-            if (p.out_dtype == FR_BF16) {
-                if (p.residual) x += __bfloat162float(((const __nv_bfloat16*)p.residual)[at]);
-                ((__nv_bfloat16*)p.out)[at] = __float2bfloat16_rn(x);
-            } else {
-                if (p.residual) x += ((const float*)p.residual)[at];
-                ((float*)p.out)[at] = x;
+        const int n = min(16, p.q_rows - gj0);
+        float r[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            r[j] = 0.f;
+            if (p.residual != nullptr && j < n) {
+                const size_t at = (size_t)(gj0 + j) * p.ldo + gi;
+                r[j] = p.out_dtype == FR_BF16 ? __bfloat162float(((const __nv_bfloat16*)p.residual)[at])
+                                              : ((const float*)p.residual)[at];
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            if (j < n) {
+                const size_t at = (size_t)(gj0 + j) * p.ldo + gi;
+                const float x = v[j] + b + r[j];
+                if (p.out_dtype == FR_BF16) ((__nv_bfloat16*)p.out)[at] = __float2bfloat16_rn(x);
+                else ((float*)p.out)[at] = x;
             }
         }
     }
@@ -429,6 +440,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                         float v[16];
 #pragma unroll
                         for (int j = 0; j < 16; ++j) v[j] = 0.f;
+#pragma unroll 4
                         for (int s = 0; s < p.splits; ++s) {
                             const float4* src = (const float4*)(first + (size_t)s * TILE_P * BN + c * 16);
 #pragma unroll
