@@ -54,7 +54,7 @@ struct GemmParams {
     void* out;
     const void* bias;
     const void* residual;
-    float* ws;          // [tiles][splits][128][BN] partial tiles when splits > 1
+    float* ws;          // [tiles][splits][BN/16][128][16] partial tiles when splits > 1
     int* counters;      // [tiles], zero between launches
     int* status;        // 0, or a code when a wait gave up
     int p_rows, q_rows, ldo, out_dtype, bias_dtype, swapped;
@@ -407,7 +407,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             tc_fence_after();
             const int gi = p_blk * TILE_P + i_local;
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + a * BN;
-            float* part = p.splits > 1 ? p.ws + ((size_t)w * TILE_P + i_local) * BN : nullptr;
+            // partial tiles are laid out [chunk of 16 columns][row][16]: a warp's 32 rows are 2 KB in one piece
+            float* part = p.splits > 1 ? p.ws + (size_t)w * TILE_P * BN + (size_t)i_local * 16 : nullptr;
 #pragma unroll 1
             for (int c = 0; c < BN / 16; ++c) {
                 uint32_t r[16];
@@ -421,7 +422,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 } else {
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
-                        ((float4*)(part + c * 16))[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                        ((float4*)(part + (size_t)c * TILE_P * 16))[j] =
+                            make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
                 }
             }
             tc_fence_before();
@@ -434,7 +436,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (flags[0]) {
                     __threadfence();
-                    const float* first = p.ws + ((size_t)tile * p.splits * TILE_P + i_local) * BN;
+                    const float* first = p.ws + (size_t)tile * p.splits * TILE_P * BN + (size_t)i_local * 16;
 #pragma unroll 1
                     for (int c = 0; c < BN / 16; ++c) {
                         float v[16];
@@ -442,7 +444,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                         for (int j = 0; j < 16; ++j) v[j] = 0.f;
 #pragma unroll 4
                         for (int s = 0; s < p.splits; ++s) {
-                            const float4* src = (const float4*)(first + (size_t)s * TILE_P * BN + c * 16);
+                            const float4* src = (const float4*)(first + (size_t)s * TILE_P * BN + (size_t)c * TILE_P * 16);
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
                                 const float4 x = __ldcg(src + j);
@@ -516,19 +518,28 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmParams& p, in
 // What the launcher would choose for a shape: fills plan[0..3] = {swapped, BN, splits, scratch floats needed}
 // and plan[4] = counters needed.  bn / splits / swap < 0 let the heuristics decide.
 FR_EXPORT int gemm_tc_plan(int m, int n, int k, int sm_count, int swap, int bn, int splits, long long* plan) {
-    if (swap < 0) swap = m <= 64 ? 1 : 0;
+    // Measured on B200 at the sizes of a 7B model (k = 3584 or 18944, n from 3584 to 152064):
+    //  * up to 16 rows: weights on the M side, the rows as a 16-wide N tile; k split until the SMs are busy;
+    //  * 17 to 128 rows: rows on the M side (one tile, partly empty) and narrow weight tiles, so that about a
+    //    hundred CTAs stream weights without splitting k; very long k is split four ways over wide tiles instead;
+    //  * more rows: 128 x 256 tiles.
+    const int kb_total = (k + TILE_K - 1) / TILE_K;
+    if (swap < 0) swap = m <= 16 ? 1 : 0;
     const int q_rows = swap ? m : n, p_rows = swap ? n : m;
+    const bool skinny = !swap && m <= TILE_P;
     if (bn <= 0) {
         if (swap) bn = q_rows <= 16 ? 16 : q_rows <= 32 ? 32 : 64;
-        else bn = q_rows >= 256 ? 256 : q_rows > 64 ? 128 : 64;
+        else if (!skinny) bn = q_rows >= 256 ? 256 : q_rows > 64 ? 128 : 64;
+        else if (q_rows >= 8192 || kb_total >= 128) bn = 128;
+        else bn = (q_rows + 31) / 32 <= sm_count ? 32 : 64;
     }
     const int tiles = ((p_rows + TILE_P - 1) / TILE_P) * ((q_rows + bn - 1) / bn);
-    const int kb_total = (k + TILE_K - 1) / TILE_K;
     if (splits <= 0) {
         splits = 1;
         if (tiles * 2 <= sm_count) {
             splits = sm_count / tiles;
             if (splits > kb_total / 4) splits = kb_total / 4;      // at least four k-slices per split
+            if (skinny && splits > 4) splits = 4;                  // wide partial tiles are costly to merge
             if (splits < 1) splits = 1;
         }
     }
