@@ -189,6 +189,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64, prefill and e2e")
     ap.add_argument("--prefill-only", action="store_true", help="time the 2,048-token prompt only (for profiling)")
+    ap.add_argument("--slots", type=int, default=64, help="sequences the cache is sized for (smaller for profiling)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -206,7 +207,8 @@ def main():
     cfg["num_hidden_layers"] = layers
     pk = peaks()
     t0 = time.time()
-    eng = Engine(config=cfg, seed=0, dtype="bfloat16", max_ctx=CONTEXT, max_batch=64, prefill_chunk=PREFILL_TOKENS)
+    eng = Engine(config=cfg, seed=0, dtype="bfloat16", max_ctx=CONTEXT, max_batch=max(args.slots, args.batch),
+                 prefill_chunk=PREFILL_TOKENS)
     print("[bench] %s (%.0f s)" % (eng.summary(), time.time() - t0), file=sys.stderr, flush=True)
     nums = model_numbers(cfg, layers)
 
