@@ -49,6 +49,8 @@ struct MmaArgs {
     float* part;              // [rows * nq][splits][hd + 2] when splits > 1
     int* counters;            // keys mode with splits: one per (sequence, kv head, row tile), zero between launches;
                               // the CTA that finishes a tile's last split merges the splits itself
+    int cluster;              // keys mode: the `splits` CTAs of a tile form a thread-block cluster and merge through
+                              // each other's shared memory (no scratch, no counters)
     int q_stride, table_width, nq, nkv, window, splits;
     float scale_log2;         // softmax scale times log2(e)
 };
@@ -94,10 +96,12 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
     uint8_t* s_k = s_q + ROWS_CTA * ROW_BYTES;        // [2][64][ROW_BYTES]
     uint8_t* s_v = s_k + 2 * KV_BYTES;                // [2][64][ROW_BYTES]
 
+    __shared__ int s_pages[WARPS * 32];               // the sequence's first pages, read before anything depends on them
     fr_pdl_wait();
     fr_pdl_launch();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int seq = blockIdx.z, kvh = blockIdx.y;
+    if (tid < p.table_width) s_pages[tid] = p.block_table[(size_t)seq * p.table_width + tid];
     const int split = blockIdx.x % p.splits, tile = blockIdx.x / p.splits;
     const int G = p.nq / p.nkv;
     const int q_len = p.seq_qlen[seq], q_start = p.seq_start[seq], pos0 = p.seq_pos0[seq];
@@ -132,7 +136,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
         }
     };
     auto load_kv = [&](int kb, int buf) {
-        const int page = table[kb];
+        const int page = kb < WARPS * 32 ? s_pages[kb] : table[kb];
         const bf16* kbase = p.k_pool + ((size_t)page * BLOCK_N) * kv_row + (size_t)kvh * HD;
         const bf16* vbase = p.v_pool + ((size_t)page * BLOCK_N) * kv_row + (size_t)kvh * HD;
         for (int c = tid; c < BLOCK_N * CHUNKS; c += WARPS * 32) {
@@ -170,6 +174,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
         for (int e = 0; e < 4; ++e) o[d][e] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
+    __syncthreads();                                   // s_pages
     load_q();
     if (kb_begin <= kb_end) load_kv(kb_begin, 0);
     cp_commit();
@@ -313,6 +318,9 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
         float* c_o = reinterpret_cast<float*>(s_k);                 // [WARPS][16][HD]
         float* c_m = c_o + WARPS * 16 * HD;                         // [WARPS][16]
         float* c_l = c_m + WARPS * 16;
+        float* r_o = c_l + WARPS * 16;                              // [16][HD]: this CTA's merged rows (cluster path)
+        float* r_m = r_o + 16 * HD;                                 // [16]
+        float* r_l = r_m + 16;
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const int r = (lane >> 2) + 8 * i;
@@ -347,15 +355,44 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
 #pragma unroll
                 for (int w = 0; w < WARPS; ++w) acc += c_o[(w * 16 + r) * HD + d] * f[w];
                 if (p.splits == 1) p.out[item * HD + d] = __float2bfloat16_rn(acc * inv);
+                else if (p.cluster) r_o[r * HD + d] = acc;
                 else p.part[(item * p.splits + split) * (HD + 2) + d] = acc;
             }
-            if (p.splits > 1 && (tid & 7) == 0) {
+            if (p.cluster && p.splits > 1 && (tid & 7) == 0) {
+                r_m[r] = big;
+                r_l[r] = l;
+            }
+            if (!p.cluster && p.splits > 1 && (tid & 7) == 0) {
                 float* dst = p.part + (item * p.splits + split) * (HD + 2);
                 dst[HD] = big * LN2;                  // natural-log units, as the merge kernel expects
                 dst[HD + 1] = l;
             }
         }
-        if (p.splits > 1 && p.counters != nullptr) {
+        if (p.splits > 1 && p.cluster) {
+            // The splits of this tile are the CTAs of one cluster: rank 0 reads everybody's merged rows from their
+            // shared memory.  Nothing goes through global memory.
+            fr_cluster_sync();
+            if (fr_cluster_rank() == 0 && rr < n_rows) {
+                float big = -INFINITY;
+                for (int sp = 0; sp < p.splits; ++sp) big = fmaxf(big, fr_cluster_load(r_m + r, sp));
+                float l = 0.f;
+                float f[8];
+                for (int sp = 0; sp < p.splits; ++sp) {
+                    const float ms = fr_cluster_load(r_m + r, sp);
+                    f[sp] = ms == -INFINITY ? 0.f : exp2f(ms - big);
+                    l += fr_cluster_load(r_l + r, sp) * f[sp];
+                }
+                const int t = rr / G, h = kvh * G + (rr - t * G);
+                const size_t item = (size_t)(q_start + t) * p.nq + h;
+                const float inv = l > 0.f ? 1.f / l : 0.f;
+                for (int d = (tid & 7); d < HD; d += 8) {
+                    float acc = 0.f;
+                    for (int sp = 0; sp < p.splits; ++sp) acc += fr_cluster_load(r_o + r * HD + d, sp) * f[sp];
+                    p.out[item * HD + d] = __float2bfloat16_rn(acc * inv);
+                }
+            }
+            fr_cluster_sync();                        // nobody leaves while rank 0 still reads its shared memory
+        } else if (p.splits > 1 && p.counters != nullptr) {
             // Whoever writes a tile's last partial merges them: no second kernel, the partials are still in L2.
             __shared__ int s_last;
             __threadfence();
@@ -411,19 +448,30 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
     }
 }
 
+// FRIDAY_ATTN_CLUSTER=0 merges the splits through global memory instead (for comparison).
+bool use_clusters() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("FRIDAY_ATTN_CLUSTER");
+        v = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return v != 0;
+}
+
 template <int HD, bool KEYS_MODE>
 int launch(const MmaArgs& p, dim3 grid, cudaStream_t stream) {
     constexpr int ROW_BYTES = HD * 2 + 16;
     constexpr int ROWS_CTA = KEYS_MODE ? 16 : 64;
     constexpr int kv = 4 * BLOCK_N * ROW_BYTES;
-    constexpr int merge = KEYS_MODE ? (WARPS * 16 * HD + 2 * WARPS * 16) * 4 : 0;
+    constexpr int merge = KEYS_MODE ? (WARPS * 16 * HD + 2 * WARPS * 16 + 16 * HD + 32) * 4 : 0;
     constexpr int smem = ROWS_CTA * ROW_BYTES + (kv > merge ? kv : merge);
     static bool configured = false;
     if (!configured) {
         FR_CUDA(cudaFuncSetAttribute(attention_mma_kernel<HD, KEYS_MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         configured = true;
     }
-    FR_CUDA(fr_launch(attention_mma_kernel<HD, KEYS_MODE>, grid, dim3(WARPS * 32), smem, stream, p));
+    FR_CUDA(fr_launch_cluster(attention_mma_kernel<HD, KEYS_MODE>, grid, dim3(WARPS * 32), smem, stream,
+                              p.cluster ? (unsigned)p.splits : 1u, p));
     FR_CHECK_LAUNCH("attention_mma");
     return FR_OK;
 }
@@ -462,12 +510,14 @@ FR_EXPORT int attention_mma(const void* q, int q_stride, void* out, const void* 
     if (!attention_mma_supports(hd, page)) FR_REFUSE("attention_mma: head size %d / page %d is not built", hd, page);
     if (nkv <= 0 || nq % nkv != 0) FR_REFUSE("attention: %d heads cannot share %d key/value heads", nq, nkv);
     if (splits < 1 || splits > 4096) FR_REFUSE("attention_mma: %d splits", splits);
-    if (splits > 1 && scratch == nullptr) FR_REFUSE("attention_mma: splits need a scratch buffer");
+    if (splits > 8 && scratch == nullptr) FR_REFUSE("attention_mma: more than 8 splits need a scratch buffer");
     if (n_seqs > 65535 || nkv > 65535) FR_REFUSE("attention_mma: %d sequences x %d kv heads exceed the grid", n_seqs, nkv);
     MmaArgs p;
     p.q = (const bf16*)q; p.out = (bf16*)out; p.k_pool = (const bf16*)k_pool; p.v_pool = (const bf16*)v_pool;
     p.block_table = block_table; p.seq_start = seq_start; p.seq_qlen = seq_qlen; p.seq_pos0 = seq_pos0;
-    p.seq_live = seq_live; p.part = scratch; p.counters = keys_mode ? counters : nullptr; p.q_stride = q_stride; p.table_width = table_width; p.nq = nq;
+    p.seq_live = seq_live; p.part = scratch; p.counters = keys_mode ? counters : nullptr;
+    p.cluster = keys_mode && splits >= 2 && splits <= 8 && use_clusters();
+    p.q_stride = q_stride; p.table_width = table_width; p.nq = nq;
     p.nkv = nkv; p.window = window; p.splits = splits; p.scale_log2 = scale * LOG2E;
     const int G = nq / nkv;
     const int rows_cta = keys_mode ? 16 : 64;
@@ -477,7 +527,7 @@ FR_EXPORT int attention_mma(const void* q, int q_stride, void* out, const void* 
     dim3 grid(tiles * splits, nkv, n_seqs);
     int rc = keys_mode ? launch_hd<true>(hd, p, grid, stream) : launch_hd<false>(hd, p, grid, stream);
     if (rc) return rc;
-    if (splits > 1 && p.counters == nullptr) {
+    if (splits > 1 && p.counters == nullptr && !p.cluster) {
         MergeArgs mp{scratch, out, rows, nq, hd, splits};
         FR_CUDA(fr_launch(attention_merge_kernel<bf16>, dim3((rows * nq + 3) / 4), dim3(128), 0, stream, mp));
         FR_CHECK_LAUNCH("attention merge");

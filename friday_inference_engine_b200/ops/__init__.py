@@ -263,7 +263,7 @@ class CudaOps:
         group = n_heads // n_kv_heads
         base = n_seqs * n_kv_heads * ((group + 15) // 16)
         blocks = (max_kv_len + 63) // 64
-        return int(max(1, min((3 * sms) // base, blocks // 4, 32)))
+        return int(max(1, min((3 * sms) // base, blocks // 4, 8)))     # up to 8: one thread-block cluster
 
     @staticmethod
     def attention_splits(rows, n_heads, max_kv_len):
