@@ -91,10 +91,13 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
     constexpr int NT = KPW / 8;                       // score tiles (8 keys each) per warp
     constexpr int DT = HD / 8;                        // output tiles (8 dims each)
     constexpr int KV_BYTES = BLOCK_N * ROW_BYTES;
+    // Buffers of the K/V ring.  One-token steps do almost no arithmetic per block, so what bounds them is how many
+    // blocks are on their way from memory: three buffers keep two in flight; prompts are bound by arithmetic.
+    constexpr int NS = KEYS_MODE ? 3 : 2;
     extern __shared__ __align__(16) uint8_t smem[];
     uint8_t* s_q = smem;                              // [ROWS_CTA][ROW_BYTES]
-    uint8_t* s_k = s_q + ROWS_CTA * ROW_BYTES;        // [2][64][ROW_BYTES]
-    uint8_t* s_v = s_k + 2 * KV_BYTES;                // [2][64][ROW_BYTES]
+    uint8_t* s_k = s_q + ROWS_CTA * ROW_BYTES;        // [NS][64][ROW_BYTES]
+    uint8_t* s_v = s_k + NS * KV_BYTES;               // [NS][64][ROW_BYTES]
 
     __shared__ int s_pages[WARPS * 32];               // the sequence's first pages, read before anything depends on them
     fr_pdl_wait();
@@ -176,18 +179,20 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
 
     __syncthreads();                                   // s_pages
     load_q();
-    if (kb_begin <= kb_end) load_kv(kb_begin, 0);
-    cp_commit();
+#pragma unroll
+    for (int st = 0; st < NS - 1; ++st) {
+        if (kb_begin + st <= kb_end) load_kv(kb_begin + st, st);
+        cp_commit();                                   // group st holds block st (and the queries, in group 0)
+    }
 
     const uint32_t q_addr = (uint32_t)__cvta_generic_to_shared(s_q);
     int buf = 0;
-    for (int kb = kb_begin; kb <= kb_end; ++kb, buf ^= 1) {
-        if (kb < kb_end) {
-            load_kv(kb + 1, buf ^ 1);
+    for (int kb = kb_begin; kb <= kb_end; ++kb, buf = buf + 1 == NS ? 0 : buf + 1) {
+        {
+            const int ahead = buf + NS - 1 >= NS ? buf - 1 : buf + NS - 1;      // the buffer used one block ago
+            if (kb + NS - 1 <= kb_end) load_kv(kb + NS - 1, ahead);
             cp_commit();
-            cp_wait<1>();
-        } else {
-            cp_wait<0>();
+            cp_wait<NS - 1>();                         // everything but the newest NS-1 groups: block kb is here
         }
         __syncthreads();
         const uint32_t k_addr = (uint32_t)__cvta_generic_to_shared(s_k + buf * KV_BYTES);
@@ -277,7 +282,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
         }
         __syncthreads();          // every warp is done with this buffer before it is loaded again
     }
-    if (kb_begin > kb_end) cp_wait<0>();
+    cp_wait<0>();
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
@@ -462,7 +467,7 @@ template <int HD, bool KEYS_MODE>
 int launch(const MmaArgs& p, dim3 grid, cudaStream_t stream) {
     constexpr int ROW_BYTES = HD * 2 + 16;
     constexpr int ROWS_CTA = KEYS_MODE ? 16 : 64;
-    constexpr int kv = 4 * BLOCK_N * ROW_BYTES;
+    constexpr int kv = 2 * (KEYS_MODE ? 3 : 2) * BLOCK_N * ROW_BYTES;
     constexpr int merge = KEYS_MODE ? (WARPS * 16 * HD + 2 * WARPS * 16 + 16 * HD + 32) * 4 : 0;
     constexpr int smem = ROWS_CTA * ROW_BYTES + (kv > merge ? kv : merge);
     static bool configured = false;

@@ -258,12 +258,12 @@ class CudaOps:
     def decode_splits(self, n_seqs, n_heads, n_kv_heads, max_kv_len, device):
         """CTAs that share one sequence's keys in a one-token step.  A split should have a few blocks of keys to
         stream (its set-up and the merge of the splits cost about as much as two blocks), and all CTAs should
-        fit on the GPU at once (three of them fit an SM at head size 128)."""
+        fit on the GPU at once (two of them fit an SM at head size 128)."""
         sms = self._tc_buffers(device)[3]
         group = n_heads // n_kv_heads
         base = n_seqs * n_kv_heads * ((group + 15) // 16)
         blocks = (max_kv_len + 63) // 64
-        return int(max(1, min((3 * sms) // base, blocks // 4, 8)))     # up to 8: one thread-block cluster
+        return int(max(1, min((2 * sms) // base, blocks // 4, 8)))     # up to 8: one thread-block cluster
 
     @staticmethod
     def attention_splits(rows, n_heads, max_kv_len):
