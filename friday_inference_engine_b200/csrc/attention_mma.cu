@@ -138,18 +138,31 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
             cp_async16((uint32_t)__cvta_generic_to_shared(s_q + r * ROW_BYTES + ch * 16), src, ok ? 16 : 0);
         }
     };
+    // Which pieces of a K/V block this thread copies is the same for every block: row, source offset and
+    // destination offset are worked out once.
+    constexpr int PIECES = BLOCK_N * CHUNKS / (WARPS * 32);
+    int piece_row[PIECES], piece_src[PIECES], piece_dst[PIECES];
+#pragma unroll
+    for (int j = 0; j < PIECES; ++j) {
+        const int c = tid + j * WARPS * 32;
+        const int r = c / CHUNKS, ch = c - r * CHUNKS;
+        piece_row[j] = r;
+        piece_src[j] = r * (int)kv_row + ch * 8;
+        piece_dst[j] = r * ROW_BYTES + ch * 16;
+    }
+    const uint32_t k_smem = (uint32_t)__cvta_generic_to_shared(s_k), v_smem = (uint32_t)__cvta_generic_to_shared(s_v);
     auto load_kv = [&](int kb, int buf) {
         const int page = kb < WARPS * 32 ? s_pages[kb] : table[kb];
         const bf16* kbase = p.k_pool + ((size_t)page * BLOCK_N) * kv_row + (size_t)kvh * HD;
         const bf16* vbase = p.v_pool + ((size_t)page * BLOCK_N) * kv_row + (size_t)kvh * HD;
-        for (int c = tid; c < BLOCK_N * CHUNKS; c += WARPS * 32) {
-            const int r = c / CHUNKS, ch = c - r * CHUNKS;
-            const int bytes = (kb * BLOCK_N + r <= pos_hi) ? 16 : 0;        // beyond the last needed key: zeros
-            const size_t off = (size_t)r * kv_row + ch * 8;
-            cp_async16((uint32_t)__cvta_generic_to_shared(s_k + buf * KV_BYTES + r * ROW_BYTES + ch * 16),
-                       bytes ? (const void*)(kbase + off) : (const void*)p.k_pool, bytes);
-            cp_async16((uint32_t)__cvta_generic_to_shared(s_v + buf * KV_BYTES + r * ROW_BYTES + ch * 16),
-                       bytes ? (const void*)(vbase + off) : (const void*)p.v_pool, bytes);
+        const int valid = pos_hi - kb * BLOCK_N + 1;                        // rows of the block that are needed
+#pragma unroll
+        for (int j = 0; j < PIECES; ++j) {
+            const bool ok = piece_row[j] < valid;                           // beyond the last needed key: zeros
+            cp_async16(k_smem + buf * KV_BYTES + piece_dst[j], ok ? (const void*)(kbase + piece_src[j]) : (const void*)p.k_pool,
+                       ok ? 16 : 0);
+            cp_async16(v_smem + buf * KV_BYTES + piece_dst[j], ok ? (const void*)(vbase + piece_src[j]) : (const void*)p.v_pool,
+                       ok ? 16 : 0);
         }
     };
 
@@ -186,6 +199,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
     }
 
     const uint32_t q_addr = (uint32_t)__cvta_generic_to_shared(s_q);
+    uint32_t q_frag[KEYS_MODE ? HD / 16 : 1][4];       // one-token steps keep the queries in registers
+    bool q_loaded = false;
     int buf = 0;
     for (int kb = kb_begin; kb <= kb_end; ++kb, buf = buf + 1 == NS ? 0 : buf + 1) {
         {
@@ -198,25 +213,44 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
         const uint32_t k_addr = (uint32_t)__cvta_generic_to_shared(s_k + buf * KV_BYTES);
         const uint32_t v_addr = (uint32_t)__cvta_generic_to_shared(s_v + buf * KV_BYTES);
 
-        // scores = Q K^T for this warp's 16 rows and KPW keys
-        float s[NT][4];
+        // scores = Q K^T for this warp's 16 rows and KPW keys.  Two sets of accumulators take alternate slices of
+        // the head dimension, so that consecutive products do not wait for each other.
+        float s[NT][4], s2[NT][4];
 #pragma unroll
         for (int n = 0; n < NT; ++n)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) s[n][e] = 0.f;
+            for (int e = 0; e < 4; ++e) s[n][e] = s2[n][e] = 0.f;
+        if (KEYS_MODE && !q_loaded) {
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks)
+                ldsm4(q_frag[ks], q_addr + (row_base + (lane & 7) + 8 * ((lane >> 3) & 1)) * ROW_BYTES +
+                                      (ks * 16 + 8 * (lane >> 4)) * 2);
+            q_loaded = true;
+        }
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
-            uint32_t a[4];
-            ldsm4(a, q_addr + (row_base + (lane & 7) + 8 * ((lane >> 3) & 1)) * ROW_BYTES + (ks * 16 + 8 * (lane >> 4)) * 2);
+            uint32_t a_now[4];
+            if (!KEYS_MODE)
+                ldsm4(a_now, q_addr + (row_base + (lane & 7) + 8 * ((lane >> 3) & 1)) * ROW_BYTES + (ks * 16 + 8 * (lane >> 4)) * 2);
+            const uint32_t (&a)[4] = KEYS_MODE ? q_frag[ks] : a_now;
 #pragma unroll
             for (int np = 0; np < NT / 2; ++np) {
                 uint32_t b[4];
                 ldsm4(b, k_addr + (key_base + np * 16 + (lane & 7) + 8 * (lane >> 4)) * ROW_BYTES +
                              (ks * 16 + 8 * ((lane >> 3) & 1)) * 2);
-                mma16816(s[2 * np], a, b[0], b[1]);
-                mma16816(s[2 * np + 1], a, b[2], b[3]);
+                if (ks & 1) {
+                    mma16816(s2[2 * np], a, b[0], b[1]);
+                    mma16816(s2[2 * np + 1], a, b[2], b[3]);
+                } else {
+                    mma16816(s[2 * np], a, b[0], b[1]);
+                    mma16816(s[2 * np + 1], a, b[2], b[3]);
+                }
             }
         }
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[n][e] += s2[n][e];
 
         // scale, mask, online softmax
         const int j0 = kb * BLOCK_N + key_base;
