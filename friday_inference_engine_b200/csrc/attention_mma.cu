@@ -213,13 +213,12 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
         const uint32_t k_addr = (uint32_t)__cvta_generic_to_shared(s_k + buf * KV_BYTES);
         const uint32_t v_addr = (uint32_t)__cvta_generic_to_shared(s_v + buf * KV_BYTES);
 
-        // scores = Q K^T for this warp's 16 rows and KPW keys.  Two sets of accumulators take alternate slices of
-        // the head dimension, so that consecutive products do not wait for each other.
-        float s[NT][4], s2[NT][4];
+        // scores = Q K^T for this warp's 16 rows and KPW keys
+        float s[NT][4];
 #pragma unroll
         for (int n = 0; n < NT; ++n)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) s[n][e] = s2[n][e] = 0.f;
+            for (int e = 0; e < 4; ++e) s[n][e] = 0.f;
         if (KEYS_MODE && !q_loaded) {
 #pragma unroll
             for (int ks = 0; ks < HD / 16; ++ks)
@@ -238,19 +237,10 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
                 uint32_t b[4];
                 ldsm4(b, k_addr + (key_base + np * 16 + (lane & 7) + 8 * (lane >> 4)) * ROW_BYTES +
                              (ks * 16 + 8 * ((lane >> 3) & 1)) * 2);
-                if (ks & 1) {
-                    mma16816(s2[2 * np], a, b[0], b[1]);
-                    mma16816(s2[2 * np + 1], a, b[2], b[3]);
-                } else {
-                    mma16816(s[2 * np], a, b[0], b[1]);
-                    mma16816(s[2 * np + 1], a, b[2], b[3]);
-                }
+                mma16816(s[2 * np], a, b[0], b[1]);
+                mma16816(s[2 * np + 1], a, b[2], b[3]);
             }
         }
-#pragma unroll
-        for (int n = 0; n < NT; ++n)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) s[n][e] += s2[n][e];
 
         // scale, mask, online softmax
         const int j0 = kb * BLOCK_N + key_base;
