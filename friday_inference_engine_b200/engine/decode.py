@@ -64,6 +64,9 @@ class DeviceDecoder:
         self.eager_steps = 0
         self.launches_per_step = 0
         self.logits = None
+        # All layers of the step in one persistent kernel, where the model and the batch allow it.
+        from . import fused_decode
+        self.fused = fused_decode.FusedLayers(self) if fused_decode.applicable(self.model, self.cache, n) else None
 
     def _bound_for(self, length):
         bound = 1024
@@ -85,7 +88,11 @@ class DeviceDecoder:
                 for call in self.model.program]
 
     def _body(self):
-        x = self.model.run(self.tokens, self.ctx, self._views())
+        if self.fused is not None:
+            ops.embedding(self.tokens, self.model.embedding, out=self.fused.x)
+            x = self.fused.run(self.row_seq, self.row_pos, self.bound)
+        else:
+            x = self.model.run(self.tokens, self.ctx, self._views())
         self.logits = self.model.logits(x)
         ops.sample(self.logits, self.temperature, self.streams, self.draws, self.seed, row_live=self.row_seq,
                    out=self.sampled)
@@ -141,6 +148,10 @@ class DeviceDecoder:
             lib.add_launches(self.launches_per_step)
         live_slots = [s for s, alive in zip(self.slots, self.live) if alive]
         self.cache.commit(live_slots, [1] * len(live_slots))
+
+    def check(self):
+        if self.fused is not None:
+            self.fused.check()
 
     def read_sampled(self):
         """The tokens that the last step chose, as a host list (waits for the step)."""

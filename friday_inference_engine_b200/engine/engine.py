@@ -159,6 +159,7 @@ class Engine:
                 rows.dec.retire(index)
 
             def close(rows):
+                rows.dec.check()
                 rows.dec.close()
 
         out = _generate.generate(

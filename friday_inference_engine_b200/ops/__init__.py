@@ -54,10 +54,11 @@ class CudaOps:
         self._attn_counters = {}
 
     # -- row-wise ---------------------------------------------------------
-    def embedding(self, tokens, table):
+    def embedding(self, tokens, table, out=None):
         _need_cuda(tokens, table)
         assert tokens.dtype == torch.int32 and tokens.is_contiguous() and table.is_contiguous()
-        out = torch.empty((tokens.numel(), table.shape[1]), dtype=table.dtype, device=table.device)
+        if out is None:
+            out = torch.empty((tokens.numel(), table.shape[1]), dtype=table.dtype, device=table.device)
         lib.family("rowwise").call("rowwise_embedding", _ptr(tokens), _ptr(table), _ptr(out), tokens.numel(),
                                    table.shape[1], code_of(table.dtype), _stream())
         return out

@@ -1,7 +1,7 @@
 """Compiles the CUDA sources under csrc/ for sm_100a, one shared library per file.
 
 Each kernel family (rowwise, gemm_simt, gemm_tc, attention_simt, attention_mma,
-sampling) is one .cu file with a C interface and becomes one .so next to the package
+sampling, decode_layer) is one .cu file with a C interface and becomes one .so next to the package
 (friday_inference_engine_b200/_build/).  A library is compiled when it is first
 needed and was not made from the present sources, so a run compiles what its model
 and dtype use and nothing else.  If the package folder cannot be written, the
@@ -23,7 +23,7 @@ CSRC = os.path.join(os.path.dirname(_HERE), "csrc")
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC,-fvisibility=hidden",
               "--expt-relaxed-constexpr"]
-FAMILIES = ("rowwise", "gemm_simt", "attention_simt", "sampling", "gemm_tc", "attention_mma")
+FAMILIES = ("rowwise", "gemm_simt", "attention_simt", "sampling", "gemm_tc", "attention_mma", "decode_layer")
 # libraries other than the runtime that a family links
 EXTRA_LIBS = {}
 

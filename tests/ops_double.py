@@ -16,7 +16,10 @@ import plain_model
 class TorchOps:
     name = "torch-double"
 
-    def embedding(self, tokens, table):
+    def embedding(self, tokens, table, out=None):
+        if out is not None:
+            out.copy_(table[tokens.long()])
+            return out
         return table[tokens.long()]
 
     def gather_rows(self, rows, src):

@@ -28,7 +28,15 @@ TINY_C = {
     "tie_word_embeddings": False, "use_sliding_window": True, "sliding_window": 80, "max_window_layers": 2,
     "max_position_embeddings": 1024, "torch_dtype": "bfloat16",
 }
-CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2)}
+# Head size 64 with a width that differs from heads * head_dim; no window; an own head.
+TINY_D = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 3, "hidden_size": 136, "num_attention_heads": 6, "num_key_value_heads": 2,
+    "head_dim": 64, "intermediate_size": 328, "vocab_size": 300, "rope_theta": 20000.0, "rms_norm_eps": 2e-6,
+    "tie_word_embeddings": False, "use_sliding_window": False, "max_position_embeddings": 512,
+    "torch_dtype": "bfloat16",
+}
+CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3)}
 
 
 def make_model_dir(path, cfg_dict, seed, dtype=torch.bfloat16):
