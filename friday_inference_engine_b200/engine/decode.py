@@ -58,6 +58,7 @@ class DeviceDecoder:
         self._scratch = None
         self._pinned = torch.empty((n,), dtype=torch.int32).pin_memory() if dev.type == "cuda" else None
         self._pinned_out = torch.empty((n,), dtype=torch.int32).pin_memory() if dev.type == "cuda" else None
+        self._copied = None           # event after the last copy out of _pinned
         self.use_graph = bool(use_graph) and dev.type == "cuda"
         self.graph = None
         self.graphs = {}              # bound -> captured step
@@ -124,8 +125,12 @@ class DeviceDecoder:
             self.graph = self.graphs.get(need)
         if tokens is not None:
             if self._pinned is not None:
+                if self._copied is not None:
+                    self._copied.synchronize()          # the copy of the step before has read the buffer
                 self._pinned.numpy()[:] = np.asarray(tokens, dtype=np.int32)
                 self.tokens.copy_(self._pinned, non_blocking=True)
+                self._copied = torch.cuda.Event()
+                self._copied.record()
             else:
                 self.tokens.copy_(torch.tensor(list(tokens), dtype=torch.int32))
         if not self.use_graph:
