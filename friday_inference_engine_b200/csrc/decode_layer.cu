@@ -40,7 +40,7 @@ constexpr int BN = 16;                              // rows of a step, padded: N
 constexpr int STAGES = 8;
 constexpr int Q_BYTES = BN * TILE_K * 2;
 constexpr int STAGE_BYTES = P_BYTES + Q_BYTES;      // 18 KB
-constexpr int THREADS = 192;
+constexpr int THREADS = 224;                        // producer, MMA, four worker warps, L2 prefetcher
 constexpr int WORKERS = 128;
 constexpr int KEYS = 64;                            // keys per attention block = tokens per cache page
 constexpr int BARRIERS_PER_LAYER = 8;
@@ -79,9 +79,11 @@ struct StepArgs {
     int* gemm_counters;
     float* attn_scratch;    // [rows * nq][attn_splits][hd + 2]
     int* attn_counters;     // [rows * nkv * row tiles]
-    int* grid_bars;         // [16] + 1: barrier slots and the exit counter, all zero between launches
+    int* grid_bars;         // [3]: arrivals, barriers completed, CTAs that have left; all zero between launches
     int* status;
+    unsigned long long* trace;  // may be null; else [n_layers * 8 + 1] times (ns) at which CTA 0 left each grid barrier
     int n_layers, rows, width, nq, nkv, attn_splits;
+    int lookahead;          // weight tiles (16 KB each, per CTA) that the L2 prefetcher may run ahead of the producer
     float scale_log2;
 };
 
@@ -126,8 +128,11 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // ------------------------------------------------------------------ grid barrier (workers only)
-// Barrier number g uses slot g % 16.  The last CTA to arrive clears the slot of the barrier before (everybody
-// has left it); spins are bounded and give up as soon as any CTA has recorded a failure.
+// grid_bars[0] counts arrivals, grid_bars[1] is the number of barriers that have been completed.  The last CTA
+// to arrive clears the count and publishes the next number; the others watch only that second word, so the
+// arrivals (atomics on word 0) and the watching (loads of word 1) do not fight over one address.  Spins are
+// bounded and give up as soon as any CTA has recorded a failure.  Both words are zero between launches: the
+// last CTA to leave the kernel clears the second.
 __device__ bool grid_barrier(const StepArgs& a, int g, int wt, volatile int* passed) {
     __shared__ int ok_flag;
     worker_sync();
@@ -135,14 +140,15 @@ __device__ bool grid_barrier(const StepArgs& a, int g, int wt, volatile int* pas
         int ok = 1;
         __threadfence();
         asm volatile("fence.proxy.async;" ::: "memory");      // writes of this phase, for later TMA loads elsewhere
-        int* slot = a.grid_bars + (g & 15);
         const int n = (int)gridDim.x;
-        const int prev = atomicAdd(slot, 1);
-        if (prev == n - 1 && g > 0) atomicExch(a.grid_bars + ((g - 1) & 15), 0);
-        if (prev != n - 1) {
+        if (atomicAdd(a.grid_bars, 1) == n - 1) {
+            a.grid_bars[0] = 0;
+            __threadfence();
+            atomicExch(a.grid_bars + 1, g + 1);
+        } else {
             const unsigned long long t0 = global_ns();
             for (uint32_t it = 0;; ++it) {
-                if (ld_acquire(slot) >= n) break;
+                if (ld_acquire(a.grid_bars + 1) > g) break;
                 if ((it & 255u) == 255u) {
                     if (ld_acquire(a.status) != 0) { ok = 0; break; }
                     if (global_ns() - t0 > WAIT_LIMIT_NS) { atomicCAS(a.status, 0, 16 + (g & 15)); ok = 0; break; }
@@ -153,24 +159,66 @@ __device__ bool grid_barrier(const StepArgs& a, int g, int wt, volatile int* pas
         asm volatile("fence.proxy.async;" ::: "memory");
         ok_flag = ok;
         *passed = g + 1;                                      // the producer warp polls this
+        if (a.trace != nullptr && blockIdx.x == 0) a.trace[g + 1] = global_ns();
     }
     worker_sync();
     return ok_flag != 0;
 }
 
 // ------------------------------------------------------------------ RMSNorm of one row by the 128 workers
+// Rows of up to 8192 elements, a multiple of 8, are read once in 16-byte pieces and kept in registers.
 __device__ void norm_row(const bf16* __restrict__ x, FrVec w, bf16* __restrict__ y, int width, float eps, int wt,
                          float* red) {
+    constexpr int MAXC = 8;
+    const bool vec = width % 8 == 0 && width <= 8 * WORKERS * MAXC && ((((uintptr_t)x) | ((uintptr_t)y)) & 15) == 0;
+    uint4 v[MAXC];
     float ss = 0.f;
-    for (int i = wt; i < width; i += WORKERS) {
-        const float v = __bfloat162float(x[i]);
-        ss += v * v;
+    if (vec) {
+        const int n_chunks = width / 8;
+#pragma unroll
+        for (int i = 0; i < MAXC; ++i) {
+            const int c = wt + WORKERS * i;
+            if (c < n_chunks) v[i] = __ldcg((const uint4*)x + c);     // written by other SMs a moment ago: from L2
+        }
+#pragma unroll
+        for (int i = 0; i < MAXC; ++i) {
+            const int c = wt + WORKERS * i;
+            if (c < n_chunks) {
+                const __nv_bfloat162* h = (const __nv_bfloat162*)&v[i];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = __bfloat1622float2(h[j]);
+                    ss += f.x * f.x + f.y * f.y;
+                }
+            }
+        }
+    } else {
+        for (int i = wt; i < width; i += WORKERS) {
+            const float f = __bfloat162float(x[i]);
+            ss += f * f;
+        }
     }
     ss = fr_warp_sum(ss);
     if ((wt & 31) == 0) red[wt >> 5] = ss;
     worker_sync();
     const float inv = 1.0f / sqrtf((red[0] + red[1] + red[2] + red[3]) / (float)width + eps);
-    for (int i = wt; i < width; i += WORKERS) y[i] = __float2bfloat16_rn(__bfloat162float(x[i]) * inv * w.at(i));
+    if (vec) {
+        const int n_chunks = width / 8;
+#pragma unroll
+        for (int i = 0; i < MAXC; ++i) {
+            const int c = wt + WORKERS * i;
+            if (c < n_chunks) {
+                const bf16* h = (const bf16*)&v[i];
+                uint4 o;
+                bf16* oh = (bf16*)&o;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) oh[j] = __float2bfloat16_rn(__bfloat162float(h[j]) * inv * w.at(c * 8 + j));
+                ((uint4*)y)[c] = o;
+            }
+        }
+    } else {
+        for (int i = wt; i < width; i += WORKERS) y[i] = __float2bfloat16_rn(__bfloat162float(x[i]) * inv * w.at(i));
+    }
     worker_sync();
 }
 
@@ -457,9 +505,10 @@ __global__ void __launch_bounds__(THREADS, 1) decode_layers_kernel(const StepArg
     uint8_t* smem_attn = smem + STAGES * STAGE_BYTES;
     uint64_t* bars = (uint64_t*)(smem_attn + ((ATTN_BYTES + 15) & ~15));
     uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
-    int* flags = (int*)(tmem_slot + 1);             // [0] split-k: came last; [1] grid barriers passed; [2..5] sums
-    volatile int* passed = flags + 1;
+    int* flags = (int*)(tmem_slot + 1);             // [0] split-k: came last; [1] grid barriers passed; [2..5] sums;
+    volatile int* passed = flags + 1;               // [6] weight tiles the producer has asked for
     float* red = (float*)(flags + 2);
+    volatile int* issued = flags + 6;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
@@ -475,6 +524,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_layers_kernel(const StepArg
         }
         flags[0] = 0;
         flags[1] = 0;
+        flags[6] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -550,6 +600,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_layers_kernel(const StepArg
                             }
                             if (++stage == STAGES) { stage = 0; phase ^= 1; first_pass = false; }
                             ++kb;
+                            *issued = *issued + 1;
                         }
                     }
                     while (ok && !go) {                // do not enter the next product with debts
@@ -593,6 +644,41 @@ __global__ void __launch_bounds__(THREADS, 1) decode_layers_kernel(const StepArg
                 }
             }
         }
+    } else if (warp == 6) {
+        // L2 prefetcher: walks the same sequence of weight tiles as the producer, a bounded distance ahead of it, and
+        // asks for them to be brought into L2.  The waits between phases (barriers, merges, first loads) then cost
+        // no memory time: HBM keeps streaming into L2 and the producer's loads are served from there.
+        if (lane == 0 && a.lookahead > 0) {
+            int done = 0;
+            bool ok = true;
+            for (int l = 0; l < a.n_layers && ok; ++l) {
+                const LayerArgs& L = a.layers[l];
+                for (int ph = 0; ph < 4 && ok; ++ph) {
+                    const GemmPhase& g = ph == 0 ? L.qkv : ph == 1 ? L.o : ph == 2 ? L.gu : L.down;
+                    const int items = g.tiles * g.splits;
+                    for (int w = blockIdx.x; w < items && ok; w += grid) {
+                        const int tile = w / g.splits, split = w - tile * g.splits;
+                        const int kb0 = split * g.kb_per, kb1 = min(kb0 + g.kb_per, g.kb_total);
+                        for (int kb = kb0; kb < kb1 && ok; ++kb, ++done) {
+                            if (done >= *issued + a.lookahead) {
+                                const unsigned long long t0 = global_ns();
+                                for (uint32_t it = 0; done >= *issued + a.lookahead; ++it) {
+                                    __nanosleep(64);
+                                    if ((it & 1023u) == 1023u && (ld_acquire(a.status) != 0 || global_ns() - t0 > 2 * WAIT_LIMIT_NS)) {
+                                        ok = false;
+                                        break;
+                                    }
+                                }
+                                if (!ok) break;
+                            }
+                            asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(&g.map_w),
+                                         "r"(kb * TILE_K), "r"(tile * TILE_P)
+                                         : "memory");
+                        }
+                    }
+                }
+            }
+        }
     } else {
         const int wt = threadIdx.x - 64;               // 0..127 among the workers
         const int quarter = warp & 3;
@@ -602,6 +688,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_layers_kernel(const StepArg
         int it = 0, g_no = 0;
         bool ok = true;
         fr_pdl_wait();
+        if (a.trace != nullptr && blockIdx.x == 0 && wt == 0) a.trace[0] = global_ns();
 
         auto epilogue = [&](const GemmPhase& g) {
             Epi ep{g.out, g.bias, g.residual, g.n, a.rows, g.ldo, FR_BF16, g.bias_dtype, 1, g.act};
@@ -691,9 +778,10 @@ __global__ void __launch_bounds__(THREADS, 1) decode_layers_kernel(const StepArg
         worker_sync();
         if (wt == 0) {
             __threadfence();
-            if (atomicAdd(a.grid_bars + 16, 1) == grid - 1) {
-                for (int i = 0; i < 16; ++i) a.grid_bars[i] = 0;
-                a.grid_bars[16] = 0;
+            if (atomicAdd(a.grid_bars + 2, 1) == grid - 1) {
+                a.grid_bars[0] = 0;
+                a.grid_bars[1] = 0;
+                a.grid_bars[2] = 0;
                 __threadfence();
             }
         }
@@ -839,12 +927,14 @@ FR_EXPORT int decode_layer_scratch(const void* layer, int rows, int nq, int nkv,
 }
 
 // Runs n_layers layers (device array `layers` of LayerArgs) on the rows' residual stream x, in place.
-// grid_bars: 17 zeroed ints (left zeroed); counters zeroed (left zeroed); status: a device int.
+// grid_bars: 3 zeroed ints (left zeroed); counters zeroed (left zeroed); status: a device int; trace: null, or
+// n_layers * 8 + 1 64-bit words that receive the times (ns) at which CTA 0 started and left each grid barrier.
+// lookahead: how many 16 KB weight tiles per CTA the L2 prefetcher may run ahead (0: no prefetching).
 FR_EXPORT int decode_layers_run(const void* layers, int n_layers, void* x, void* xn, void* qkv, void* attn,
                                 const int* row_seq, const int* row_pos, float* gemm_scratch, int* gemm_counters,
                                 float* attn_scratch, int* attn_counters, int attn_splits, int* grid_bars, int* status,
-                                int rows, int width, int nq, int nkv, int hd, float scale, int ctas,
-                                cudaStream_t stream) {
+                                unsigned long long* trace, int rows, int width, int nq, int nkv, int hd, float scale,
+                                int ctas, int lookahead, cudaStream_t stream) {
     if (n_layers <= 0) return FR_OK;
     if (((uintptr_t)layers & 63)) FR_REFUSE("decode_layer: the layer array must be 64-byte aligned");
     if (attn_splits < 1 || attn_splits > 64) FR_REFUSE("decode_layer: %d attention splits", attn_splits);
@@ -852,6 +942,8 @@ FR_EXPORT int decode_layers_run(const void* layers, int n_layers, void* x, void*
     a.layers = (const LayerArgs*)layers; a.x = (bf16*)x; a.xn = (bf16*)xn; a.qkv = (bf16*)qkv; a.attn = (bf16*)attn;
     a.row_seq = row_seq; a.row_pos = row_pos; a.gemm_scratch = gemm_scratch; a.gemm_counters = gemm_counters;
     a.attn_scratch = attn_scratch; a.attn_counters = attn_counters; a.grid_bars = grid_bars; a.status = status;
+    a.trace = trace;
+    a.lookahead = lookahead;
     a.n_layers = n_layers; a.rows = rows; a.width = width; a.nq = nq; a.nkv = nkv; a.attn_splits = attn_splits;
     a.scale_log2 = scale * LOG2E;
     switch (hd) {

@@ -32,8 +32,8 @@ def _family():
         fam.declare("decode_layer_fill", [_P, _I, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P, _P, _P, _I, _F, _P, _I, _F,
                                           _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P, _I, _I])
         fam.declare("decode_layer_scratch", [_P, _I, _I, _I, _I, _I, _P])
-        fam.declare("decode_layers_run", [_P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I,
-                                          _I, _F, _I, _P])
+        fam.declare("decode_layers_run", [_P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I,
+                                          _I, _I, _F, _I, _I, _P])
         fam._declared = True
     return fam
 
@@ -133,6 +133,12 @@ class FusedLayers:
         self.attn_counters = torch.zeros((self.items_base + 4,), dtype=torch.int32, device=dev)
         self.grid_bars = torch.zeros((32,), dtype=torch.int32, device=dev)
         self.status = torch.zeros((4,), dtype=torch.int32, device=dev)
+        # Weight tiles (16 KB) per CTA that the kernel's L2 prefetcher runs ahead of the loads: 24 tiles on 148 SMs
+        # are 57 MB, under half of the 126 MB L2.
+        self.lookahead = int(os.environ.get("FRIDAY_L2_LOOKAHEAD", "24"))
+        # FRIDAY_PROFILE=1, as in the reference (transformer.cpp:603-613): times of the phases of every layer
+        self.trace = (torch.zeros((n * 8 + 1,), dtype=torch.int64, device=dev)
+                      if os.environ.get("FRIDAY_PROFILE", "0") == "1" else None)
 
     def splits_for(self, bound):
         """CTAs that share one sequence's keys: enough to give every SM an item, a few blocks of keys each."""
@@ -144,9 +150,19 @@ class FusedLayers:
         self.fam.call("decode_layers_run", _ptr(self.layers), self.n_layers, _ptr(self.x), _ptr(self.xn), _ptr(self.qkv),
                       _ptr(self.attn), _ptr(row_seq), _ptr(row_pos), _ptr(self.gemm_scratch), _ptr(self.gemm_counters),
                       _ptr(self.attn_scratch), _ptr(self.attn_counters), self.splits_for(bound), _ptr(self.grid_bars),
-                      _ptr(self.status), self.rows, self.width, self.nq, self.nkv, self.hd, float(self.scale), self.ctas,
-                      torch.cuda.current_stream().cuda_stream)
+                      _ptr(self.status), _ptr(self.trace), self.rows, self.width, self.nq, self.nkv, self.hd, float(self.scale), self.ctas,
+                      self.lookahead, torch.cuda.current_stream().cuda_stream)
         return self.x
+
+    PHASES = ("norm1", "qkv", "rotary+cache", "attention", "o_proj", "norm2", "gate_up", "down")
+
+    def phase_times(self):
+        """With FRIDAY_PROFILE=1: microseconds that CTA 0 spent in each phase (barrier included), mean over layers."""
+        if self.trace is None:
+            return None
+        t = self.trace.cpu().numpy().astype(np.float64)
+        d = np.diff(t).reshape(self.n_layers, 8) / 1e3
+        return {name: float(d[:, i].mean()) for i, name in enumerate(self.PHASES)}
 
     def check(self):
         code = int(self.status[0].item())
