@@ -40,7 +40,7 @@ constexpr int BN = 16;                              // rows of a step, padded: N
 constexpr int STAGES = 8;
 constexpr int Q_BYTES = BN * TILE_K * 2;
 constexpr int STAGE_BYTES = P_BYTES + Q_BYTES;      // 18 KB
-constexpr int THREADS = 224;                        // producer, MMA, four worker warps, L2 prefetcher
+constexpr int THREADS = 192;
 constexpr int WORKERS = 128;
 constexpr int KEYS = 64;                            // keys per attention block = tokens per cache page
 constexpr int BARRIERS_PER_LAYER = 8;
@@ -83,7 +83,6 @@ struct StepArgs {
     int* status;
     unsigned long long* trace;  // may be null; else [n_layers * 8 + 1] times (ns) at which CTA 0 left each grid barrier
     int n_layers, rows, width, nq, nkv, attn_splits;
-    int lookahead;          // weight tiles (16 KB each, per CTA) that the L2 prefetcher may run ahead of the producer
     float scale_log2;
 };
 
@@ -505,10 +504,9 @@ __global__ void __launch_bounds__(THREADS, 1) decode_layers_kernel(const StepArg
     uint8_t* smem_attn = smem + STAGES * STAGE_BYTES;
     uint64_t* bars = (uint64_t*)(smem_attn + ((ATTN_BYTES + 15) & ~15));
     uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
-    int* flags = (int*)(tmem_slot + 1);             // [0] split-k: came last; [1] grid barriers passed; [2..5] sums;
-    volatile int* passed = flags + 1;               // [6] weight tiles the producer has asked for
+    int* flags = (int*)(tmem_slot + 1);             // [0] split-k: came last; [1] grid barriers passed; [2..5] sums
+    volatile int* passed = flags + 1;
     float* red = (float*)(flags + 2);
-    volatile int* issued = flags + 6;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
@@ -524,7 +522,6 @@ __global__ void __launch_bounds__(THREADS, 1) decode_layers_kernel(const StepArg
         }
         flags[0] = 0;
         flags[1] = 0;
-        flags[6] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -600,7 +597,6 @@ __global__ void __launch_bounds__(THREADS, 1) decode_layers_kernel(const StepArg
                             }
                             if (++stage == STAGES) { stage = 0; phase ^= 1; first_pass = false; }
                             ++kb;
-                            *issued = *issued + 1;
                         }
                     }
                     while (ok && !go) {                // do not enter the next product with debts
@@ -640,41 +636,6 @@ __global__ void __launch_bounds__(THREADS, 1) decode_layers_kernel(const StepArg
                             if (++stage == STAGES) { stage = 0; phase ^= 1; }
                         }
                         if (ok) tc_commit(accf0 + 8 * ai);
-                    }
-                }
-            }
-        }
-    } else if (warp == 6) {
-        // L2 prefetcher: walks the same sequence of weight tiles as the producer, a bounded distance ahead of it, and
-        // asks for them to be brought into L2.  The waits between phases (barriers, merges, first loads) then cost
-        // no memory time: HBM keeps streaming into L2 and the producer's loads are served from there.
-        if (lane == 0 && a.lookahead > 0) {
-            int done = 0;
-            bool ok = true;
-            for (int l = 0; l < a.n_layers && ok; ++l) {
-                const LayerArgs& L = a.layers[l];
-                for (int ph = 0; ph < 4 && ok; ++ph) {
-                    const GemmPhase& g = ph == 0 ? L.qkv : ph == 1 ? L.o : ph == 2 ? L.gu : L.down;
-                    const int items = g.tiles * g.splits;
-                    for (int w = blockIdx.x; w < items && ok; w += grid) {
-                        const int tile = w / g.splits, split = w - tile * g.splits;
-                        const int kb0 = split * g.kb_per, kb1 = min(kb0 + g.kb_per, g.kb_total);
-                        for (int kb = kb0; kb < kb1 && ok; ++kb, ++done) {
-                            if (done >= *issued + a.lookahead) {
-                                const unsigned long long t0 = global_ns();
-                                for (uint32_t it = 0; done >= *issued + a.lookahead; ++it) {
-                                    __nanosleep(64);
-                                    if ((it & 1023u) == 1023u && (ld_acquire(a.status) != 0 || global_ns() - t0 > 2 * WAIT_LIMIT_NS)) {
-                                        ok = false;
-                                        break;
-                                    }
-                                }
-                                if (!ok) break;
-                            }
-                            asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(&g.map_w),
-                                         "r"(kb * TILE_K), "r"(tile * TILE_P)
-                                         : "memory");
-                        }
                     }
                 }
             }
@@ -929,12 +890,11 @@ FR_EXPORT int decode_layer_scratch(const void* layer, int rows, int nq, int nkv,
 // Runs n_layers layers (device array `layers` of LayerArgs) on the rows' residual stream x, in place.
 // grid_bars: 3 zeroed ints (left zeroed); counters zeroed (left zeroed); status: a device int; trace: null, or
 // n_layers * 8 + 1 64-bit words that receive the times (ns) at which CTA 0 started and left each grid barrier.
-// lookahead: how many 16 KB weight tiles per CTA the L2 prefetcher may run ahead (0: no prefetching).
 FR_EXPORT int decode_layers_run(const void* layers, int n_layers, void* x, void* xn, void* qkv, void* attn,
                                 const int* row_seq, const int* row_pos, float* gemm_scratch, int* gemm_counters,
                                 float* attn_scratch, int* attn_counters, int attn_splits, int* grid_bars, int* status,
                                 unsigned long long* trace, int rows, int width, int nq, int nkv, int hd, float scale,
-                                int ctas, int lookahead, cudaStream_t stream) {
+                                int ctas, cudaStream_t stream) {
     if (n_layers <= 0) return FR_OK;
     if (((uintptr_t)layers & 63)) FR_REFUSE("decode_layer: the layer array must be 64-byte aligned");
     if (attn_splits < 1 || attn_splits > 64) FR_REFUSE("decode_layer: %d attention splits", attn_splits);
@@ -943,7 +903,6 @@ FR_EXPORT int decode_layers_run(const void* layers, int n_layers, void* x, void*
     a.row_seq = row_seq; a.row_pos = row_pos; a.gemm_scratch = gemm_scratch; a.gemm_counters = gemm_counters;
     a.attn_scratch = attn_scratch; a.attn_counters = attn_counters; a.grid_bars = grid_bars; a.status = status;
     a.trace = trace;
-    a.lookahead = lookahead;
     a.n_layers = n_layers; a.rows = rows; a.width = width; a.nq = nq; a.nkv = nkv; a.attn_splits = attn_splits;
     a.scale_log2 = scale * LOG2E;
     switch (hd) {
