@@ -57,6 +57,58 @@ struct GemmParams {
     int p_rows, q_rows, ldo, out_dtype, bias_dtype, swapped;
     int act;            // 1: the product's columns are (gate, up) pairs; out gets silu(gate) * up, half as wide
     int tiles_p, tiles_q, splits, kb_total, kb_per;
+    // Work decomposition.  The first dp_tiles tiles are cut into `splits` equal k ranges each and dealt out round
+    // robin (splits = 1: whole tiles).  The remaining sk_tiles tiles ("stream-k"): their k blocks, laid end to end,
+    // are cut into one contiguous run of sk_units per CTA, so that a last, partial wave of tiles keeps every SM busy.
+    int dp_tiles, sk_tiles, sk_units;
+};
+
+struct Item {
+    int tile;        // which tile
+    int kb0, kb1;    // its k blocks [kb0, kb1)
+    int nseg;        // items that share the tile (1: this item has it alone and writes the output itself)
+    int part;        // slot of this item's partial tile in the scratch buffer (nseg > 1)
+    int first;       // stream-k: the first CTA that contributes to the tile (their slots follow from that)
+};
+
+// The items of one CTA, in the order in which all three roles walk them.
+struct Work {
+    const GemmParams& p;
+    int cta, grid, i, u, u_end;
+    __device__ Work(const GemmParams& p_, int cta_, int grid_) : p(p_), cta(cta_), grid(grid_), i(0) {
+        const int total = p.sk_tiles * p.kb_total;
+        u = min(cta * p.sk_units, total);
+        u_end = min(u + p.sk_units, total);
+    }
+    __device__ bool next(Item& it) {
+        const int w = cta + i * grid;
+        if (w < p.dp_tiles * p.splits) {
+            ++i;
+            it.tile = w / p.splits;
+            const int split = w - it.tile * p.splits;
+            it.kb0 = split * p.kb_per;
+            it.kb1 = min(it.kb0 + p.kb_per, p.kb_total);
+            it.nseg = p.splits;
+            it.part = w;
+            it.first = -1;
+            return true;
+        }
+        if (u >= u_end) return false;
+        const int t = u / p.kb_total;                      // tile among the stream-k tiles
+        it.tile = p.dp_tiles + t;
+        it.kb0 = u - t * p.kb_total;
+        it.kb1 = min(p.kb_total, it.kb0 + (u_end - u));
+        u += it.kb1 - it.kb0;
+        it.first = (t * p.kb_total) / p.sk_units;
+        it.nseg = ((t + 1) * p.kb_total - 1) / p.sk_units - it.first + 1;
+        it.part = sk_slot(cta, t);
+        return true;
+    }
+    // A CTA writes at most two partial tiles: of the first tile of its run (slot 0) and of a later one (slot 1).
+    __device__ int sk_slot(int c, int t) const { return 2 * c + (t > (c * p.sk_units) / p.kb_total ? 1 : 0); }
+    __device__ int contributor(const Item& it, int s) const {          // slot of the s-th partial of the tile
+        return it.first < 0 ? it.tile * p.splits + s : sk_slot(it.first + s, it.tile - p.dp_tiles);
+    }
 };
 
 template <int BN, int STAGES>
@@ -101,39 +153,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     const uint32_t tmem_base = *tmem_slot;
     if (threadIdx.x == 0) fr_pdl_launch();     // the next kernel may be scheduled; it waits for this one itself
 
-    const int n_tiles = p.tiles_p * p.tiles_q;
-    const int n_items = n_tiles * p.splits;
-
     if (warp == 0) {
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_p) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
             // The k-slices this CTA will load, in order: (work item, k block).
             struct Walk {
-                int w, kb, kb1, p_blk, q_blk;
-            };
-            auto open_item = [&](Walk& k, int w) {
-                k.w = w;
-                if (w >= n_items) return;
-                const int tile = w / p.splits, split = w - tile * p.splits;
-                k.q_blk = tile / p.tiles_p;
-                k.p_blk = tile - k.q_blk * p.tiles_p;
-                k.kb = split * p.kb_per;
-                k.kb1 = min(k.kb + p.kb_per, p.kb_total);
-            };
-            auto step = [&](Walk& k) {
-                if (++k.kb >= k.kb1) open_item(k, k.w + gridDim.x);
+                Work work;
+                Item item;
+                int kb, p_blk, q_blk;
+                bool live;
+                __device__ Walk(const GemmParams& pp, int cta, int grid) : work(pp, cta, grid), live(true) { open(pp); }
+                __device__ void open(const GemmParams& pp) {
+                    live = work.next(item);
+                    if (!live) return;
+                    q_blk = item.tile / pp.tiles_p;
+                    p_blk = item.tile - q_blk * pp.tiles_p;
+                    kb = item.kb0;
+                }
+                __device__ void step(const GemmParams& pp) {
+                    if (++kb >= item.kb1) open(pp);
+                }
             };
             // The weights do not depend on the kernel before this one; the activations do.  Fill the ring with
             // weight slices first, then wait for the predecessor, then add the activation slices.
             const CUtensorMap* map_w = p.swapped ? &map_p : &map_q;
             const CUtensorMap* map_x = p.swapped ? &map_q : &map_p;
             const uint32_t off_w = p.swapped ? 0 : P_BYTES, off_x = p.swapped ? P_BYTES : 0;
-            Walk head;
-            open_item(head, blockIdx.x);
-            Walk ahead = head;
+            Walk head(p, blockIdx.x, gridDim.x);
+            Walk ahead(p, blockIdx.x, gridDim.x);
             int early = 0;
-            for (; early < STAGES && ahead.w < n_items; ++early, step(ahead)) {
+            for (; early < STAGES && ahead.live; ++early, ahead.step(p)) {
                 mbar_expect_tx(full0 + 8 * early, STAGE_BYTES);
                 tma_load_2d(smem_u32(smem + early * STAGE_BYTES) + off_w, map_w, ahead.kb * TILE_K,
                             p.swapped ? ahead.p_blk * TILE_P : ahead.q_blk * BN, full0 + 8 * early);
@@ -142,7 +192,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (; head.w < n_items && ok; step(head)) {
+            for (; head.live && ok; head.step(p)) {
                 const uint32_t dst = smem_u32(smem + stage * STAGE_BYTES);
                 if (early > 0) {
                     --early;                                 // the weight slice of this stage is already on its way
@@ -165,9 +215,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             uint32_t phase = 0;
             bool ok = true;
             int it = 0;
-            for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x, ++it) {
-                const int tile = w / p.splits, split = w - tile * p.splits;
-                const int kb0 = split * p.kb_per, kb1 = min(kb0 + p.kb_per, p.kb_total);
+            Work work(p, blockIdx.x, gridDim.x);
+            Item item;
+            for (; ok && work.next(item); ++it) {
+                const int kb0 = item.kb0, kb1 = item.kb1;
                 const int a = it & 1;
                 const uint32_t acc_phase = (it >> 1) & 1;
                 if (!(ok = mbar_wait(acce0 + 8 * a, acc_phase ^ 1, p.status, 2))) break;
@@ -194,8 +245,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         fr_pdl_wait();
         bool ok = true;
         int it = 0;
-        for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x, ++it) {
-            const int tile = w / p.splits, split = w - tile * p.splits;
+        Work work(p, blockIdx.x, gridDim.x);
+        Item item;
+        for (; ok && work.next(item); ++it) {
+            const int tile = item.tile;
             const int q_blk = tile / p.tiles_p, p_blk = tile - q_blk * p.tiles_p;
             const int a = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
@@ -204,7 +257,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             const int gi = p_blk * TILE_P + i_local;
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + a * BN;
             // partial tiles are laid out [chunk of 16 columns][row][16]: a warp's 32 rows are 2 KB in one piece
-            float* part = p.splits > 1 ? p.ws + (size_t)w * TILE_P * BN + (size_t)i_local * 16 : nullptr;
+            float* part = item.nseg > 1 ? p.ws + (size_t)item.part * TILE_P * BN + (size_t)i_local * 16 : nullptr;
 #pragma unroll 1
             for (int c = 0; c < BN / 16; ++c) {
                 uint32_t r[16];
@@ -225,22 +278,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acce0 + 8 * a);     // the accumulator may be overwritten
-            if (p.splits > 1) {
+            if (item.nseg > 1) {
                 __threadfence();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (et == 0) flags[0] = atomicAdd(p.counters + tile, 1) == p.splits - 1;
+                if (et == 0) flags[0] = atomicAdd(p.counters + tile, 1) == item.nseg - 1;
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (flags[0]) {
                     __threadfence();
-                    const float* first = p.ws + (size_t)tile * p.splits * TILE_P * BN + (size_t)i_local * 16;
+                    const float* mine = p.ws + (size_t)i_local * 16;
 #pragma unroll 1
                     for (int c = 0; c < BN / 16; ++c) {
                         float v[16];
 #pragma unroll
                         for (int j = 0; j < 16; ++j) v[j] = 0.f;
 #pragma unroll 4
-                        for (int s = 0; s < p.splits; ++s) {
-                            const float4* src = (const float4*)(first + (size_t)s * TILE_P * BN + (size_t)c * TILE_P * 16);
+                        for (int s = 0; s < item.nseg; ++s) {
+                            const float4* src = (const float4*)(mine + (size_t)work.contributor(item, s) * TILE_P * BN +
+                                                                (size_t)c * TILE_P * 16);
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
                                 const float4 x = __ldcg(src + j);
@@ -294,6 +348,16 @@ int make_map(CUtensorMap* map, const void* base, int rows, int k, int ld, int bo
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) FR_REFUSE("gemm_tc: cuTensorMapEncodeTiled failed with %d (rows %d, k %d, ld %d)", (int)r, rows, k, ld);
     return FR_OK;
+}
+
+// FRIDAY_STREAM_K=0 keeps whole tiles per CTA in every wave (for comparison).
+bool use_stream_k() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("FRIDAY_STREAM_K");
+        v = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return v != 0;
 }
 
 template <int BN, int STAGES>
@@ -391,13 +455,26 @@ FR_EXPORT int gemm_tc_act(const void* x, const void* w, void* out, int out_dtype
     p.act = act;
     p.tiles_p = (p.p_rows + TILE_P - 1) / TILE_P; p.tiles_q = (p.q_rows + bn - 1) / bn;
     p.splits = splits; p.kb_total = (k + TILE_K - 1) / TILE_K; p.kb_per = (p.kb_total + splits - 1) / splits;
+    // A last wave that would leave most SMs idle is spread over all of them instead (stream-k), if the scratch
+    // buffer holds two partial tiles per CTA.
+    const int tiles = p.tiles_p * p.tiles_q;
+    p.dp_tiles = tiles; p.sk_tiles = 0; p.sk_units = 1;
+    int grid = tiles * splits < sm_count ? tiles * splits : sm_count;
+    if (!swap && splits == 1 && tiles > sm_count && use_stream_k()) {
+        const int rem = tiles % sm_count;
+        if (rem != 0 && rem * 100 < sm_count * 85 && p.kb_total >= 4 && 2LL * sm_count * TILE_P * bn <= scratch_floats &&
+            tiles <= n_counters) {
+            p.sk_tiles = rem;
+            p.dp_tiles = tiles - rem;
+            p.sk_units = (rem * p.kb_total + sm_count - 1) / sm_count;
+            grid = sm_count;
+        }
+    }
     CUtensorMap mp, mq;
     int rc = swap ? make_map(&mp, w, n, k, ldw, TILE_P) : make_map(&mp, x, m, k, lda, TILE_P);
     if (rc) return rc;
     rc = swap ? make_map(&mq, x, m, k, lda, bn) : make_map(&mq, w, n, k, ldw, bn);
     if (rc) return rc;
-    const int items = p.tiles_p * p.tiles_q * splits;
-    const int grid = items < sm_count ? items : sm_count;
     switch (bn) {
         case 16: return launch<16, 10>(mp, mq, p, grid, stream);
         case 32: return launch<32, 10>(mp, mq, p, grid, stream);

@@ -134,8 +134,8 @@ class CudaOps:
 
     # Scratch of the tensor-core product (partial tiles of split-k), its tile counters and the word in which
     # a kernel records a wait that gave up: one set per device, made once, so that captured graphs keep
-    # their addresses.  At most one CTA per SM holds a partial tile of 128 x 256 floats.
-    _TC_SCRATCH_FLOATS = 148 * 128 * 256
+    # their addresses.  At most two partial tiles of 128 x 256 floats per CTA, one CTA per SM.
+    _TC_SCRATCH_FLOATS = 2 * 148 * 128 * 256
     _TC_COUNTERS = 4096
 
     def _tc_buffers(self, device):

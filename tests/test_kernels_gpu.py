@@ -380,3 +380,17 @@ def test_gemm_tensor_core_gated_epilogue(m, inner, k):
         close(be._linear_tc(x, pairs, None, None, out, swap=swap, bn=bn, splits=splits, act=1), ref, dt,
               "gated, swap %d bn %d splits %d" % (swap, bn, splits), bf16_rel=0.01)
     be.check_status()
+
+
+@pytest.mark.parametrize("m,n,k", [(2048, 3584, 512), (1100, 3584 + 256, 1024), (2048 + 77, 2400, 320), (2048, 3584, 18944)])
+def test_gemm_tensor_core_partial_last_wave(m, n, k):
+    """More 128 x 256 tiles than SMs with a remainder: the last wave is cut along k over all SMs (stream-k)."""
+    dt = torch.bfloat16
+    a, w = rnd((m, k), dt, 44), rnd((n, k), dt, 45, 0.05)
+    res = rnd((m, n), dt, 46)
+    io = res.clone()
+    ops.linear(a, w, residual=io, out=io)
+    ref = (a.float() @ w.float().t()).double() + res.double()          # fp32 matmul of exact bf16 inputs as the yardstick
+    err = float((io.double() - ref).abs().max() / ref.abs().max())
+    assert err <= 0.01, err
+    ops.backend().check_status()
