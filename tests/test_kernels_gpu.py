@@ -1,6 +1,8 @@
 """Each kernel alone against the plain implementation's function for the same step, at
 sizes other than the test models': widths and vocabularies that are no power of two,
 head sizes in steps of 16 up to 256, odd head counts and groups, long contexts."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -383,8 +385,19 @@ def test_gemm_tensor_core_gated_epilogue(m, inner, k):
 
 
 @pytest.mark.parametrize("m,n,k", [(2048, 3584, 512), (1100, 3584 + 256, 1024), (2048 + 77, 2400, 320), (2048, 3584, 18944)])
-def test_gemm_tensor_core_partial_last_wave(m, n, k):
-    """More 128 x 256 tiles than SMs with a remainder: the last wave is cut along k over all SMs (stream-k)."""
+def test_gemm_tensor_core_partial_last_wave(m, n, k, monkeypatch):
+    """More 128 x 256 tiles than SMs with a remainder: with FRIDAY_STREAM_K=1 the last wave is cut along k over
+    all SMs.  The switch is read once per process, so this test runs the product in a child process."""
+    import subprocess
+    import sys
+    code = ("import os, sys; os.environ['FRIDAY_STREAM_K']='1'; sys.path.insert(0, %r); sys.path.insert(0, %r);"
+            "import test_kernels_gpu as t; t.partial_last_wave(%d, %d, %d)"
+            % (os.path.dirname(os.path.dirname(os.path.abspath(__file__))), os.path.dirname(os.path.abspath(__file__)), m, n, k))
+    subprocess.run([sys.executable, "-c", code], check=True)
+    partial_last_wave(m, n, k)
+
+
+def partial_last_wave(m, n, k):
     dt = torch.bfloat16
     a, w = rnd((m, k), dt, 44), rnd((n, k), dt, 45, 0.05)
     res = rnd((m, n), dt, 46)
