@@ -1,0 +1,80 @@
+"""The engine at the layer sizes of the benchmark model (width 3584, 28 heads in 4 groups of head size
+128, inner width 18944) with two layers and a smaller vocabulary, against the plain implementation:
+the tiny test models never reach these tile counts, split-k ranges or head sizes."""
+import numpy as np
+import pytest
+import torch
+
+import harness
+import plain_model
+
+# In 32-bit the bound is the one the task states for the full-size models: |engine - plain| <= 1e-4 on the logits
+# (sums over 18,944 terms in another order than the plain implementation's float64 move the last bits; the tiny
+# models' tighter bound of 2e-5 is not meant for these sizes).
+WIDE_FP32_ABS = 1e-4
+import tiny_configs
+from friday_inference_engine_b200 import Engine
+
+pytestmark = pytest.mark.gpu
+
+WIDE = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "num_hidden_layers": 2, "hidden_size": 3584,
+    "num_attention_heads": 28, "num_key_value_heads": 4, "head_dim": 128, "intermediate_size": 18944,
+    "vocab_size": 5000, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
+    "use_sliding_window": False, "max_position_embeddings": 4096, "torch_dtype": "bfloat16",
+}
+
+
+@pytest.fixture(scope="module")
+def wide(tmp_path_factory):
+    d = str(tmp_path_factory.mktemp("wide") / "model")
+    tiny_configs.make_model_dir(d, WIDE, 9)
+    harness.sharpen(d, 2.0)
+    return d, plain_model.PlainModel.from_dir(d)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_wide_layers_prompt_then_tokens(wide, dtype):
+    d, pm = wide
+    eng = Engine(model_path=d, dtype=dtype, max_ctx=512, max_batch=3)
+    lens, extra = [70, 9, 130], 3
+    prompts = tiny_configs.random_prompts([n + extra for n in lens], WIDE["vocab_size"], 60)
+    at = [[n - 1, n, n + extra - 1] for n in lens]
+    refs = [plain_model.logits(pm, p, at=a) for p, a in zip(prompts, at)]
+    slots = [eng.alloc_slot() for _ in prompts]
+    got = eng.step(slots, [p[:n] for p, n in zip(prompts, lens)], [[n - 1] for n in lens])
+    def check(got_rows, ref_rows, what):
+        if dtype == "float32":
+            err = float(np.abs(got_rows - ref_rows).max())
+            assert err <= WIDE_FP32_ABS, "%s: |engine - plain| = %.3g > %.3g" % (what, err, WIDE_FP32_ABS)
+        else:
+            harness.check_logits(got_rows, ref_rows, dtype, what)
+
+    for i in range(3):
+        check(harness.to_np(got[i:i + 1]), refs[i][0:1], "wide prompt %d" % i)
+    for t in range(extra):
+        got = eng.step(slots, [[p[n + t]] for p, n in zip(prompts, lens)], [[0]] * 3)
+        if t in (0, extra - 1):
+            for i in range(3):
+                check(harness.to_np(got[i:i + 1]), refs[i][1 if t == 0 else 2][None], "wide decode %d of request %d" % (t, i))
+    eng.check()
+
+
+def test_wide_layers_device_decoder(wide, monkeypatch):
+    d, pm = wide
+    for fused in ("0", "1"):
+        monkeypatch.setenv("FRIDAY_FUSED_DECODE", fused)
+        eng = Engine(model_path=d, dtype="bfloat16", max_ctx=512, max_batch=2)
+        lens, extra = [100, 61], 6
+        prompts = tiny_configs.random_prompts([n + extra for n in lens], WIDE["vocab_size"], 61)
+        refs = [plain_model.logits(pm, p, at=[len(p) - 1]) for p in prompts]
+        slots = [eng.alloc_slot() for _ in prompts]
+        eng.step(slots, [p[:n] for p, n in zip(prompts, lens)], [[]] * 2)
+        dec = eng.decoder(slots, [p[n] for p, n in zip(prompts, lens)])
+        for t in range(extra):
+            dec.step([p[n + t] for p, n in zip(prompts, lens)])
+        got = harness.to_np(dec.logits)
+        for i in range(2):
+            harness.check_logits(got[i:i + 1], refs[i], "bfloat16", "wide decoder (fused %s) row %d" % (fused, i))
+        dec.check()
+        dec.close()
