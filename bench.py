@@ -172,6 +172,35 @@ def time_prefill(eng, warmup, reps):
     return sorted(times)[len(times) // 2]
 
 
+def timeline(eng, batch):
+    """Kernels of the last of three profiled decode steps: name, start, duration, and `real`, the time from the end
+    of the kernel before to the end of this one (kernels overlap under programmatic dependent launch)."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    prompts = random_prompts(batch, PROMPT, eng.vocab_size, 1)
+    slots = [eng.alloc_slot() for _ in prompts]
+    for lo in range(0, batch, 8):
+        eng.step(slots[lo:lo + 8], prompts[lo:lo + 8], [[]] * len(slots[lo:lo + 8]))
+    dec = eng.decoder(slots, [p[-1] for p in prompts])
+    for _ in range(5):
+        dec.step()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(3):
+            dec.step()
+        torch.cuda.synchronize()
+    evs = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA),
+                 key=lambda e: e.time_range.start)
+    last = evs[-(len(evs) // 3):]
+    t0 = prev_end = last[0].time_range.start
+    for e in last:
+        st, en = e.time_range.start, e.time_range.end
+        print("%-64s start %8.1f us  duration %7.1f us  real %7.1f us" % (e.name[:64], st - t0, en - st, en - max(prev_end, st) if st < prev_end else en - st))
+        prev_end = max(prev_end, en)
+    print("step: %.1f us, %d kernels" % (prev_end - t0, len(last)))
+    return 0
+
+
 def reference_arm():
     why = ("the reference is a C++/CMake program with no Python packaging (pip install of its tree fails: "
            "no setup.py or pyproject.toml), has no bf16 or batched path and targets sm_86 with GGUF k-quant weights")
@@ -190,6 +219,8 @@ def main():
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64, prefill and e2e")
     ap.add_argument("--prefill-only", action="store_true", help="time the 2,048-token prompt only (for profiling)")
     ap.add_argument("--slots", type=int, default=64, help="sequences the cache is sized for (smaller for profiling)")
+    ap.add_argument("--timeline", action="store_true",
+                    help="print the kernels of one decode step as they run inside the captured graph (torch profiler)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -212,6 +243,8 @@ def main():
     print("[bench] %s (%.0f s)" % (eng.summary(), time.time() - t0), file=sys.stderr, flush=True)
     nums = model_numbers(cfg, layers)
 
+    if args.timeline:
+        return timeline(eng, args.batch)
     if args.prefill_only:
         ms_pre = time_prefill(eng, max(1, args.warmup - 2), max(1, args.steps))
         print(json.dumps({"prefill_ms": round(ms_pre, 3), "layers_run": layers}))
