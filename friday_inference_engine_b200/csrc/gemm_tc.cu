@@ -124,6 +124,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     // bars: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
     uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
     int* flags = (int*)(tmem_slot + 1);      // flags[0]: this CTA came last for the tile (split-k)
+    // Narrow tiles (the swapped orientation) write their output transposed: [BN rows][128 features] goes through
+    // this buffer so that global memory sees 16-byte pieces of whole rows instead of 2-byte strided accesses.
+    constexpr int T_BYTES = BN <= 64 ? BN * TILE_P * 4 : 0;
+    uint8_t* s_tile = (uint8_t*)(bars + 2 * STAGES + 4) + 64;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
@@ -247,6 +251,49 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         int it = 0;
         Work work(p, blockIdx.x, gridDim.x);
         Item item;
+        // The transposed output of the swapped orientation, staged through s_tile: [rows of the step][128 features].
+        const int elem = p.out_dtype == FR_BF16 ? 2 : 4;
+        const int row_bytes = TILE_P * elem, pieces = row_bytes / 16;
+        const bool can_stage = T_BYTES > 0 && p.swapped && !p.act && ((size_t)p.ldo * elem) % 16 == 0 &&
+                               (((uintptr_t)p.out | (uintptr_t)p.residual) & 15) == 0;
+        auto stage_in = [&](int p_blk, int q_blk) {        // residual rows of the tile -> s_tile
+            if (p.residual != nullptr) {
+                const int nt = min(BN, p.q_rows - q_blk * BN);
+                for (int c = et; c < nt * pieces; c += 128) {
+                    const int token = c / pieces, piece = c - token * pieces;
+                    const char* src = (const char*)p.residual + ((size_t)(q_blk * BN + token) * p.ldo + (size_t)p_blk * TILE_P) * elem;
+                    *(uint4*)(s_tile + token * row_bytes + piece * 16) = __ldcg((const uint4*)src + piece);
+                }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        };
+        auto put16 = [&](int q_blk, int c, int gi, const float (&v)[16]) {    // 16 rows of this thread's feature
+            const float b = p.bias ? bias_at(p, gi) : 0.f;
+            const int n = min(16, p.q_rows - q_blk * BN - c * 16);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                if (j < n) {
+                    uint8_t* at = s_tile + (c * 16 + j) * row_bytes + i_local * elem;
+                    if (p.out_dtype == FR_BF16) {
+                        const float r = p.residual ? __bfloat162float(*(const __nv_bfloat16*)at) : 0.f;
+                        *(__nv_bfloat16*)at = __float2bfloat16_rn(v[j] + b + r);
+                    } else {
+                        const float r = p.residual ? *(const float*)at : 0.f;
+                        *(float*)at = v[j] + b + r;
+                    }
+                }
+            }
+        };
+        auto stage_out = [&](int p_blk, int q_blk) {       // s_tile -> output rows of the tile
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const int nt = min(BN, p.q_rows - q_blk * BN);
+            for (int c = et; c < nt * pieces; c += 128) {
+                const int token = c / pieces, piece = c - token * pieces;
+                char* dst = (char*)p.out + ((size_t)(q_blk * BN + token) * p.ldo + (size_t)p_blk * TILE_P) * elem;
+                *((uint4*)dst + piece) = *(const uint4*)(s_tile + token * row_bytes + piece * 16);
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        };
         for (; ok && work.next(item); ++it) {
             const int tile = item.tile;
             const int q_blk = tile / p.tiles_p, p_blk = tile - q_blk * p.tiles_p;
@@ -255,9 +302,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             if (!(ok = mbar_wait(accf0 + 8 * a, acc_phase, p.status, 4))) break;
             tc_fence_after();
             const int gi = p_blk * TILE_P + i_local;
+            const bool staged = can_stage && (p_blk + 1) * TILE_P <= p.p_rows;
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + a * BN;
             // partial tiles are laid out [chunk of 16 columns][row][16]: a warp's 32 rows are 2 KB in one piece
             float* part = item.nseg > 1 ? p.ws + (size_t)item.part * TILE_P * BN + (size_t)i_local * 16 : nullptr;
+            if (part == nullptr && staged) stage_in(p_blk, q_blk);
 #pragma unroll 1
             for (int c = 0; c < BN / 16; ++c) {
                 uint32_t r[16];
@@ -267,7 +316,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
 #pragma unroll
                 for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
                 if (part == nullptr) {
-                    finish16(p, gi, q_blk * BN + c * 16, v);
+                    if (staged) put16(q_blk, c, gi, v);
+                    else finish16(p, gi, q_blk * BN + c * 16, v);
                 } else {
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
@@ -278,6 +328,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acce0 + 8 * a);     // the accumulator may be overwritten
+            if (part == nullptr && staged) stage_out(p_blk, q_blk);
             if (item.nseg > 1) {
                 __threadfence();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -286,6 +337,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 if (flags[0]) {
                     __threadfence();
                     const float* mine = p.ws + (size_t)i_local * 16;
+                    if (staged) stage_in(p_blk, q_blk);
 #pragma unroll 1
                     for (int c = 0; c < BN / 16; ++c) {
                         float v[16];
@@ -301,8 +353,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                                 v[4 * j] += x.x; v[4 * j + 1] += x.y; v[4 * j + 2] += x.z; v[4 * j + 3] += x.w;
                             }
                         }
-                        finish16(p, gi, q_blk * BN + c * 16, v);
+                        if (staged) put16(q_blk, c, gi, v);
+                        else finish16(p, gi, q_blk * BN + c * 16, v);
                     }
+                    if (staged) stage_out(p_blk, q_blk);
                     if (et == 0) p.counters[tile] = 0;     // ready for the next launch
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -364,7 +418,7 @@ bool use_stream_k() {
 
 template <int BN, int STAGES>
 int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmParams& p, int grid, cudaStream_t stream) {
-    constexpr int smem = STAGES * (P_BYTES + BN * TILE_K * 2) + 1024 + 256;
+    constexpr int smem = STAGES * (P_BYTES + BN * TILE_K * 2) + 1024 + 256 + (BN <= 64 ? BN * TILE_P * 4 : 0);
     static bool configured = false;
     if (!configured) {
         FR_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -505,7 +559,7 @@ NoAllocDevice noalloc_devices[64];
 template <int BN, int STAGES>
 cudaError_t allow_smem() {
     return cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                STAGES * (P_BYTES + BN * TILE_K * 2) + 1024 + 256);
+                                STAGES * (P_BYTES + BN * TILE_K * 2) + 1024 + 256 + (BN <= 64 ? BN * TILE_P * 4 : 0));
 }
 
 // Once per device, with that device current.

@@ -202,8 +202,12 @@ __device__ __forceinline__ void finish16(const P& p, int gi, int gj0, float (&v)
             r[j] = 0.f;
             if (p.residual != nullptr && j < n) {
                 const size_t at = (size_t)(gj0 + j) * p.ldo + gi;
-                r[j] = p.out_dtype == FR_BF16 ? __bfloat162float(((const __nv_bfloat16*)p.residual)[at])
-                                              : ((const float*)p.residual)[at];
+                if (p.out_dtype == FR_BF16) {
+                    const unsigned short raw = __ldcg((const unsigned short*)p.residual + at);
+                    r[j] = __uint_as_float((uint32_t)raw << 16);
+                } else {
+                    r[j] = __ldcg((const float*)p.residual + at);
+                }
             }
         }
 #pragma unroll
