@@ -148,6 +148,8 @@ def time_e2e(eng, batch, steps, seed):
     def on_step(live, drawn):
         marks.append(time.perf_counter())
 
+    eng.generate(prompts, max_new_tokens=4, temperature=0.0, ignore_eos=True)       # warm-up: captures the step
+    marks.clear()
     torch.cuda.synchronize()
     out = eng.generate(prompts, max_new_tokens=steps + 1, temperature=0.0, ignore_eos=True, on_step=on_step)
     assert all(len(g.tokens) == steps + 1 for g in out)

@@ -69,6 +69,39 @@ class DeviceDecoder:
         from . import fused_decode
         self.fused = fused_decode.FusedLayers(self) if fused_decode.applicable(self.model, self.cache, n) else None
 
+    def reset(self, slots, first_tokens, temperature=0.0, seed=0, streams=None, steps_done=None):
+        """Takes over another batch of the same size: the buffers keep their addresses, so the captured steps
+        stay valid (they are captured again only if the sampler's seed changes, which is a kernel argument, or
+        if a mixer keeps state that it addresses from the host)."""
+        n = self.n
+        assert len(slots) == n
+        self.slots[:] = list(slots)
+        self.ctx.slots[:] = self.slots
+        self.live = [True] * n
+        i32 = dict(dtype=torch.int32)
+        self.tokens.copy_(torch.tensor(list(first_tokens), **i32))
+        self.row_seq.copy_(torch.arange(n, **i32))
+        self.row_pos.copy_(torch.tensor([self.cache.lens[s] for s in self.slots], **i32))
+        self.kv_len.copy_(self.row_pos + 1)
+        self.temperature.fill_(float(temperature))
+        self.streams.copy_(torch.tensor(list(streams) if streams is not None else list(range(n)), **i32))
+        self.draws.copy_(torch.tensor(list(steps_done) if steps_done is not None else [0] * n, **i32))
+        if int(seed) != self.seed or self.cache.states:
+            self.seed = int(seed)
+            self.graphs.clear()
+        if self.ctx.seq_slots is not None:
+            self.ctx.seq_slots.copy_(torch.as_tensor(self.slots, dtype=torch.int64))
+        fresh = self.cache.tables_for(self.slots)
+        for t_host, t_dev, t_new in zip(self.tables_host, self.tables, fresh):
+            t_host[:] = t_new
+            t_dev.copy_(torch.from_numpy(t_new))
+        self.bound = self._bound_for(max(self.cache.lens[s] for s in self.slots) + 1)
+        self.ctx.max_kv_len = self.bound
+        self.ctx.kv_lens = [self.bound] * n
+        self.graph = self.graphs.get(self.bound)
+        self._copied = None
+        return self
+
     def _bound_for(self, length):
         bound = 1024
         while bound < length:
@@ -172,5 +205,6 @@ class DeviceDecoder:
         self.row_seq[index] = -1
 
     def close(self):
-        self.graph = None
-        self.graphs.clear()
+        """Hands the decoder back to the engine, which keeps it (buffers, captured steps) for the next batch of
+        this size."""
+        self.engine.keep_decoder(self)

@@ -84,6 +84,7 @@ class Engine:
                            max_slots=self.max_batch)
         self.stepper = Stepper(self.model, self.cache, chunk=opt.prefill_chunk)
         self._single = None     # slot of the single-sequence conveniences
+        self._decoders = {}     # batch size -> a decoder that is not in use (buffers and captured steps kept)
 
     # -- facts -------------------------------------------------------------
     @property
@@ -181,5 +182,12 @@ class Engine:
         """Decoding of the sequences in `slots`, one token each per step(), from buffers that stay on the
         device (engine/decode.py); the step is captured in a CUDA graph unless cuda_graphs is off."""
         from .decode import DeviceDecoder
+        kept = self._decoders.pop(len(slots), None)
+        if kept is not None:
+            return kept.reset(slots, first_tokens, temperature=temperature, seed=seed, streams=streams,
+                              steps_done=steps_done)
         return DeviceDecoder(self, slots, first_tokens, temperature=temperature, seed=seed, streams=streams,
                              steps_done=steps_done, use_graph=self.options.cuda_graphs)
+
+    def keep_decoder(self, decoder):
+        self._decoders[decoder.n] = decoder
