@@ -53,7 +53,16 @@ struct MmaArgs {
                               // each other's shared memory (no scratch, no counters)
     int q_stride, table_width, nq, nkv, window, splits;
     float scale_log2;         // softmax scale times log2(e)
+    unsigned long long* trace;  // for measurements (may be null): [cta][8] timestamps of a one-token step's CTAs
 };
+
+__device__ __forceinline__ void mark(const MmaArgs& p, int point) {
+    if (p.trace != nullptr && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        p.trace[((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8 + point] = t;
+    }
+}
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
@@ -100,11 +109,15 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
     uint8_t* s_v = s_k + NS * KV_BYTES;               // [NS][64][ROW_BYTES]
 
     __shared__ int s_pages[WARPS * 32];               // the sequence's first pages, read before anything depends on them
-    fr_pdl_wait();
-    fr_pdl_launch();
+    mark(p, 0);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int seq = blockIdx.z, kvh = blockIdx.y;
+    // The page table is written by copies from the host, never by a kernel, so it may be read before the
+    // kernel before this one has finished; everything else waits.
     if (tid < p.table_width) s_pages[tid] = p.block_table[(size_t)seq * p.table_width + tid];
+    fr_pdl_wait();
+    fr_pdl_launch();
+    mark(p, 1);
     const int split = blockIdx.x % p.splits, tile = blockIdx.x / p.splits;
     const int G = p.nq / p.nkv;
     const int q_len = p.seq_qlen[seq], q_start = p.seq_start[seq], pos0 = p.seq_pos0[seq];
@@ -198,6 +211,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
         cp_commit();                                   // group st holds block st (and the queries, in group 0)
     }
 
+    mark(p, 2);
     const uint32_t q_addr = (uint32_t)__cvta_generic_to_shared(s_q);
     uint32_t q_frag[KEYS_MODE ? HD / 16 : 1][4];       // one-token steps keep the queries in registers
     bool q_loaded = false;
@@ -210,6 +224,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
             cp_wait<NS - 1>();                         // everything but the newest NS-1 groups: block kb is here
         }
         __syncthreads();
+        if (kb == kb_begin) mark(p, 3);
         const uint32_t k_addr = (uint32_t)__cvta_generic_to_shared(s_k + buf * KV_BYTES);
         const uint32_t v_addr = (uint32_t)__cvta_generic_to_shared(s_v + buf * KV_BYTES);
 
@@ -307,6 +322,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
         __syncthreads();          // every warp is done with this buffer before it is loaded again
     }
     cp_wait<0>();
+    mark(p, 4);
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
@@ -344,8 +360,9 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
     } else {
         // The four warps saw different keys of the same 16 rows: merge through shared memory
         // (the K/V buffers are free now).
-        float* c_o = reinterpret_cast<float*>(s_k);                 // [WARPS][16][HD]
-        float* c_m = c_o + WARPS * 16 * HD;                         // [WARPS][16]
+        constexpr int HDP = HD + 4;                                 // padded: the 8 rows of a warp's store hit 8 bank groups
+        float* c_o = reinterpret_cast<float*>(s_k);                 // [WARPS][16][HDP]
+        float* c_m = c_o + WARPS * 16 * HDP;                        // [WARPS][16]
         float* c_l = c_m + WARPS * 16;
         float* r_o = c_l + WARPS * 16;                              // [16][HD]: this CTA's merged rows (cluster path)
         float* r_m = r_o + 16 * HD;                                 // [16]
@@ -355,8 +372,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
             const int r = (lane >> 2) + 8 * i;
 #pragma unroll
             for (int d = 0; d < DT; ++d) {
-                c_o[(warp * 16 + r) * HD + d * 8 + 2 * (lane & 3)] = o[d][2 * i];
-                c_o[(warp * 16 + r) * HD + d * 8 + 2 * (lane & 3) + 1] = o[d][2 * i + 1];
+                *reinterpret_cast<float2*>(c_o + (warp * 16 + r) * HDP + d * 8 + 2 * (lane & 3)) = make_float2(o[d][2 * i], o[d][2 * i + 1]);
             }
             if ((lane & 3) == 0) {
                 c_m[warp * 16 + r] = m_run[i];
@@ -382,7 +398,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
             for (int d = (tid & 7); d < HD; d += 8) {
                 float acc = 0.f;
 #pragma unroll
-                for (int w = 0; w < WARPS; ++w) acc += c_o[(w * 16 + r) * HD + d] * f[w];
+                for (int w = 0; w < WARPS; ++w) acc += c_o[(w * 16 + r) * HDP + d] * f[w];
                 if (p.splits == 1) p.out[item * HD + d] = __float2bfloat16_rn(acc * inv);
                 else if (p.cluster) r_o[r * HD + d] = acc;
                 else p.part[(item * p.splits + split) * (HD + 2) + d] = acc;
@@ -398,29 +414,55 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
             }
         }
         if (p.splits > 1 && p.cluster) {
-            // The splits of this tile are the CTAs of one cluster: rank 0 reads everybody's merged rows from their
-            // shared memory.  Nothing goes through global memory.
+            // The splits of this tile are the CTAs of one cluster.  Every CTA merges a share of the 16 rows, reading
+            // all CTAs' merged rows from their shared memory, four dimensions per thread and pass; all loads of a
+            // pass are issued before the first is used, so a pass costs one trip through the cluster's network, not
+            // one per load.  Nothing goes through global memory.
+            mark(p, 5);
             fr_cluster_sync();
-            if (fr_cluster_rank() == 0 && rr < n_rows) {
-                float big = -INFINITY;
-                for (int sp = 0; sp < p.splits; ++sp) big = fmaxf(big, fr_cluster_load(r_m + r, sp));
-                float l = 0.f;
-                float f[8];
-                for (int sp = 0; sp < p.splits; ++sp) {
-                    const float ms = fr_cluster_load(r_m + r, sp);
-                    f[sp] = ms == -INFINITY ? 0.f : exp2f(ms - big);
-                    l += fr_cluster_load(r_l + r, sp) * f[sp];
+            mark(p, 6);
+            const int rank = (int)fr_cluster_rank();
+            const int rows_per = (16 + p.splits - 1) / p.splits;
+            constexpr int VEC = HD / 4;                                 // float4 pieces per row
+            for (int idx = tid; idx < rows_per * VEC; idx += WARPS * 32) {
+                const int r2 = rank * rows_per + idx / VEC, d4 = idx % VEC;
+                const int rr2 = r0 + r2;
+                if (r2 >= 16 || rr2 >= n_rows) continue;
+                float ms[8], ls[8];
+                float4 vs[8];
+#pragma unroll
+                for (int sp = 0; sp < 8; ++sp) {
+                    if (sp < p.splits) {
+                        ms[sp] = fr_cluster_load(r_m + r2, sp);
+                        ls[sp] = fr_cluster_load(r_l + r2, sp);
+                        vs[sp] = fr_cluster_load4(r_o + r2 * HD + d4 * 4, sp);
+                    } else {
+                        ms[sp] = -INFINITY;
+                        ls[sp] = 0.f;
+                        vs[sp] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
                 }
-                const int t = rr / G, h = kvh * G + (rr - t * G);
+                float big = -INFINITY;
+#pragma unroll
+                for (int sp = 0; sp < 8; ++sp) big = fmaxf(big, ms[sp]);
+                float l = 0.f;
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int sp = 0; sp < 8; ++sp) {
+                    const float f = ms[sp] == -INFINITY ? 0.f : exp2f(ms[sp] - big);
+                    l += ls[sp] * f;
+                    acc.x += vs[sp].x * f; acc.y += vs[sp].y * f; acc.z += vs[sp].z * f; acc.w += vs[sp].w * f;
+                }
+                const int t = rr2 / G, h = kvh * G + (rr2 - t * G);
                 const size_t item = (size_t)(q_start + t) * p.nq + h;
                 const float inv = l > 0.f ? 1.f / l : 0.f;
-                for (int d = (tid & 7); d < HD; d += 8) {
-                    float acc = 0.f;
-                    for (int sp = 0; sp < p.splits; ++sp) acc += fr_cluster_load(r_o + r * HD + d, sp) * f[sp];
-                    p.out[item * HD + d] = __float2bfloat16_rn(acc * inv);
-                }
+                uint2 packed;
+                packed.x = pack_bf16(acc.x * inv, acc.y * inv);
+                packed.y = pack_bf16(acc.z * inv, acc.w * inv);
+                *reinterpret_cast<uint2*>(p.out + item * HD + d4 * 4) = packed;
             }
-            fr_cluster_sync();                        // nobody leaves while rank 0 still reads its shared memory
+            mark(p, 7);
+            fr_cluster_sync();                        // nobody leaves while another CTA still reads its shared memory
         } else if (p.splits > 1 && p.counters != nullptr) {
             // Whoever writes a tile's last partial merges them: no second kernel, the partials are still in L2.
             __shared__ int s_last;
@@ -492,7 +534,7 @@ int launch(const MmaArgs& p, dim3 grid, cudaStream_t stream) {
     constexpr int ROW_BYTES = HD * 2 + 16;
     constexpr int ROWS_CTA = KEYS_MODE ? 16 : 64;
     constexpr int kv = 2 * (KEYS_MODE ? 3 : 2) * BLOCK_N * ROW_BYTES;
-    constexpr int merge = KEYS_MODE ? (WARPS * 16 * HD + 2 * WARPS * 16 + 16 * HD + 32) * 4 : 0;
+    constexpr int merge = KEYS_MODE ? (WARPS * 16 * (HD + 4) + 2 * WARPS * 16 + 16 * HD + 32) * 4 : 0;
     constexpr int smem = ROWS_CTA * ROW_BYTES + (kv > merge ? kv : merge);
     static bool configured = false;
     if (!configured) {
@@ -503,6 +545,37 @@ int launch(const MmaArgs& p, dim3 grid, cudaStream_t stream) {
                               p.cluster ? (unsigned)p.splits : 1u, p));
     FR_CHECK_LAUNCH("attention_mma");
     return FR_OK;
+}
+
+// Clusters of `size` CTAs of the one-token kernel that the device runs at once (0 if the query fails).
+template <int HD>
+int clusters_at_once(int size) {
+    static int known[9] = {-1, -1, -1, -1, -1, -1, -1, -1, -1};
+    if (size < 1 || size > 8) return 0;
+    if (known[size] < 0) {
+        known[size] = 0;
+        constexpr int ROW_BYTES = HD * 2 + 16;
+        constexpr int kv = 2 * 3 * BLOCK_N * ROW_BYTES;
+        constexpr int merge = (WARPS * 16 * (HD + 4) + 2 * WARPS * 16 + 16 * HD + 32) * 4;
+        constexpr int smem = 16 * ROW_BYTES + (kv > merge ? kv : merge);
+        if (cudaFuncSetAttribute(attention_mma_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(size * 64);
+            cfg.blockDim = dim3(WARPS * 32);
+            cfg.dynamicSmemBytes = smem;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = size;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, attention_mma_kernel<HD, true>, &cfg) == cudaSuccess) known[size] = n;
+        }
+        cudaGetLastError();
+    }
+    return known[size];
 }
 
 template <bool KEYS_MODE>
@@ -521,6 +594,30 @@ int launch_hd(int hd, const MmaArgs& p, dim3 grid, cudaStream_t stream) {
 }
 
 }  // namespace
+
+// For measurements: one-token steps launched after this call record their CTAs' timestamps in `trace`
+// ([cta][8] 64-bit words, cta = (sequence * kv heads + kv head) * grid.x + block; null switches it off).
+static unsigned long long* attention_trace = nullptr;
+FR_EXPORT int attention_mma_set_trace(unsigned long long* trace) {
+    attention_trace = trace;
+    return FR_OK;
+}
+
+// How many clusters of `size` CTAs (the splits of one sequence and kv head in a one-token step) run at once on
+// the current device, for head size hd; 0 if unknown.
+FR_EXPORT int attention_mma_clusters_at_once(int hd, int size) {
+    switch (hd) {
+        case 16: return clusters_at_once<16>(size);
+        case 32: return clusters_at_once<32>(size);
+        case 48: return clusters_at_once<48>(size);
+        case 64: return clusters_at_once<64>(size);
+        case 80: return clusters_at_once<80>(size);
+        case 96: return clusters_at_once<96>(size);
+        case 112: return clusters_at_once<112>(size);
+        case 128: return clusters_at_once<128>(size);
+        default: return 0;
+    }
+}
 
 FR_EXPORT int attention_mma_supports(int hd, int page) { return hd % 16 == 0 && hd >= 16 && hd <= 128 && page == BLOCK_N; }
 
@@ -548,6 +645,7 @@ FR_EXPORT int attention_mma(const void* q, int q_stride, void* out, const void* 
     p.cluster = keys_mode && splits >= 2 && splits <= 8 && use_clusters();
     p.q_stride = q_stride; p.table_width = table_width; p.nq = nq;
     p.nkv = nkv; p.window = window; p.splits = splits; p.scale_log2 = scale * LOG2E;
+    p.trace = keys_mode ? attention_trace : nullptr;
     const int G = nq / nkv;
     const int rows_cta = keys_mode ? 16 : 64;
     const int tiles = (max_q_len * G + rows_cta - 1) / rows_cta;
