@@ -61,6 +61,12 @@ struct FrVec {
     }
 };
 
+// The rotation of one pair of a rotary encoding, the same instructions wherever it is applied.
+__device__ __forceinline__ void fr_rotate(float a, float b, float c, float s, float& ra, float& rb) {
+    ra = __fmaf_rn(-b, s, __fmul_rn(a, c));
+    rb = __fmaf_rn(a, s, __fmul_rn(b, c));
+}
+
 __device__ __forceinline__ float fr_warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -140,5 +146,13 @@ __device__ __forceinline__ float fr_cluster_load(const float* local, uint32_t ra
     float v;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
     asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+__device__ __forceinline__ float4 fr_cluster_load4(const float* local, uint32_t rank) {      // 16-byte aligned
+    uint32_t remote;
+    float4 v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
     return v;
 }

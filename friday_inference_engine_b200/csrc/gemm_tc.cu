@@ -42,12 +42,24 @@
 
 FR_EXPORT const char* gemm_tc_last_error() { return fr_error_text; }
 
+#include "gemm_tc_fusion.h"
+
 namespace {
 
 using namespace tc;
 constexpr int THREADS = 192;
+constexpr int SIDE_BYTES = 3 * TILE_P * 4 + 3 * 64 * 4 + 64 * 8;      // row factors and what the epilogue of narrow tiles prefetches
+
+// Dynamic shared memory of a kernel instance: the ring of stages (1 KB alignment slack), barriers, the TMEM
+// slot and flags (64 bytes), the row factors, and the staging tile of narrow instances.
+template <int BN, int STAGES>
+constexpr int smem_bytes() {
+    return STAGES * (P_BYTES + BN * TILE_K * 2) + 1024 + (2 * STAGES + 4) * 8 + 64 + SIDE_BYTES +
+           (BN <= 64 ? BN * TILE_P * 4 : 0) + (BN == 16 ? 16 * 64 * 8 : 0);
+}
 
 struct GemmParams {
+    GemmFusion f;
     void* out;
     const void* bias;
     const void* residual;
@@ -111,6 +123,15 @@ struct Work {
     }
 };
 
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+__device__ __forceinline__ void mark(const GemmParams& p, int point) {
+    if (p.f.trace != nullptr) p.f.trace[(size_t)blockIdx.x * 16 + point] = global_ns();
+}
+
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
@@ -124,16 +145,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     // bars: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
     uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
     int* flags = (int*)(tmem_slot + 1);      // flags[0]: this CTA came last for the tile (split-k)
-    // Narrow tiles (the swapped orientation) write their output transposed: [BN rows][128 features] goes through
-    // this buffer so that global memory sees 16-byte pieces of whole rows instead of 2-byte strided accesses.
+    // One factor per row of the step in this tile (the deferred RMSNorm of the input).
+    float* s_scale = (float*)((uint8_t*)(bars + 2 * STAGES + 4) + 64);      // [128]
+    // What the epilogue of a narrow tile reads per tile, fetched early: bias and norm weights of the tile's columns,
+    // rotary denominators, each row's sequence, position and cache row, the rotation's (cos, sin) per row and pair.
+    float* s_g = s_scale + TILE_P;                                           // [128]
+    float* s_bias = s_g + TILE_P;                                            // [128]
+    float* s_den = s_bias + TILE_P;                                          // [64]
+    int* s_seq = (int*)(s_den + 64);                                         // [64]
+    int* s_pos = s_seq + 64;                                                 // [64]
+    long long* s_crow = (long long*)(s_pos + 64);                            // [64]
+    // Narrow tiles (the swapped orientation) write their output transposed: the sums of [BN rows][128 columns]
+    // go through this buffer so that global memory sees 16-byte pieces of whole rows.
     constexpr int T_BYTES = BN <= 64 ? BN * TILE_P * 4 : 0;
-    uint8_t* s_tile = (uint8_t*)(bars + 2 * STAGES + 4) + 64;
-
+    uint8_t* s_tile = (uint8_t*)s_scale + SIDE_BYTES;
+    float2* s_cs = (float2*)(s_tile + T_BYTES);                              // [16][64], 16-wide tiles only
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
     const uint32_t accf0 = smem_u32(bars + 2 * STAGES), acce0 = smem_u32(bars + 2 * STAGES + 2);
 
     if (threadIdx.x == 0) {
+        mark(p, 0);
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, 1);
@@ -155,7 +187,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    if (threadIdx.x == 0) fr_pdl_launch();     // the next kernel may be scheduled; it waits for this one itself
+    if (threadIdx.x == 0) {
+        fr_pdl_launch();                       // the next kernel may be scheduled; it waits for this one itself
+        mark(p, 1);
+    }
 
     if (warp == 0) {
         if (lane == 0) {
@@ -192,7 +227,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 tma_load_2d(smem_u32(smem + early * STAGE_BYTES) + off_w, map_w, ahead.kb * TILE_K,
                             p.swapped ? ahead.p_blk * TILE_P : ahead.q_blk * BN, full0 + 8 * early);
             }
+            mark(p, 2);
             fr_pdl_wait();
+            mark(p, 3);
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -230,6 +267,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 const uint32_t d_tmem = tmem_base + a * BN;
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (!(ok = mbar_wait(full0 + 8 * stage, phase, p.status, 3))) break;
+                    if (it == 0 && kb == kb0) mark(p, 4);
                     tc_fence_after();
                     const uint32_t pa = smem_u32(smem + stage * STAGE_BYTES);
                     const uint64_t da = smem_desc(pa), db = smem_desc(pa + P_BYTES);
@@ -241,6 +279,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 }
                 if (ok) tc_commit(accf0 + 8 * a);         // the accumulator is complete
             }
+            mark(p, 5);
         }
     } else {
         const int quarter = warp & 3;                      // TMEM lanes this warp may read: 32*quarter ..
@@ -251,62 +290,207 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         int it = 0;
         Work work(p, blockIdx.x, gridDim.x);
         Item item;
-        // The transposed output of the swapped orientation, staged through s_tile: [rows of the step][128 features].
-        const int elem = p.out_dtype == FR_BF16 ? 2 : 4;
-        const int row_bytes = TILE_P * elem, pieces = row_bytes / 16;
-        const bool can_stage = T_BYTES > 0 && p.swapped && !p.act && ((size_t)p.ldo * elem) % 16 == 0 &&
-                               (((uintptr_t)p.out | (uintptr_t)p.residual) & 15) == 0;
-        auto stage_in = [&](int p_blk, int q_blk) {        // residual rows of the tile -> s_tile
+        const GemmFusion& f = p.f;
+        // Narrow tiles of the swapped orientation are written transposed.  Their sums go through s_sum as
+        // [rows of the step][128 columns] floats; then every thread finishes pieces of 8 consecutive columns of one
+        // row (bias, residual, rounding, and the fused work) with 16-byte accesses to global memory.
+        const bool bf16_out = p.out_dtype == FR_BF16;
+        const bool can_stage = T_BYTES > 0 && p.swapped && !p.act && (p.ldo % 8) == 0 &&
+                               (((uintptr_t)p.out | (uintptr_t)p.residual) & 15) == 0 && (bf16_out || p.residual == nullptr);
+        const bool rope = f.row_pos != nullptr;            // the launcher grants it to 16-wide tiles only
+        float* s_sum = (float*)s_tile;
+        constexpr int ITEMS = BN <= 64 ? BN / 8 : 1;       // pieces per thread: BN * 16 pieces over 128 threads
+        uint4 res[ITEMS];                                  // this thread's pieces of the residual rows, fetched early
+        if (rope && f.denom != nullptr && et < (f.rot >> 1)) s_den[et] = f.denom[et];
+        // What a staged tile's epilogue reads besides the sums is fetched as soon as the tile is known, while the
+        // products are still running: bias and norm weights of the tile's columns, the residual pieces, each row's
+        // sequence, position and cache row, and the rotation's cosines and sines.  What remains after the last product
+        // is one trip to memory for split-k's partial sums, arithmetic, and stores.
+        auto prefetch_tile = [&](int p_blk, int q_blk) {
+            const int nt = min(BN, p.q_rows - q_blk * BN);
+            s_bias[et] = p.bias != nullptr ? bias_at(p, p_blk * TILE_P + et) : 0.f;
+            if (f.norm_out != nullptr)
+                s_g[et] = f.norm_w_dtype == FR_F32 ? ((const float*)f.norm_w)[p_blk * TILE_P + et]
+                                                   : __bfloat162float(((const __nv_bfloat16*)f.norm_w)[p_blk * TILE_P + et]);
             if (p.residual != nullptr) {
-                const int nt = min(BN, p.q_rows - q_blk * BN);
-                for (int c = et; c < nt * pieces; c += 128) {
-                    const int token = c / pieces, piece = c - token * pieces;
-                    const char* src = (const char*)p.residual + ((size_t)(q_blk * BN + token) * p.ldo + (size_t)p_blk * TILE_P) * elem;
-                    *(uint4*)(s_tile + token * row_bytes + piece * 16) = __ldcg((const uint4*)src + piece);
+#pragma unroll
+                for (int k = 0; k < ITEMS; ++k) {
+                    const int idx = et + 128 * k;
+                    if (idx < nt * 16)
+                        res[k] = __ldcg((const uint4*)((const __nv_bfloat16*)p.residual + (size_t)(q_blk * BN + (idx >> 4)) * p.ldo +
+                                                       (size_t)p_blk * TILE_P + (idx & 15) * 8));
                 }
             }
+            if (rope && et < nt) {
+                const int row = q_blk * BN + et;
+                const int seq = f.row_seq[row], pos = f.row_pos[row];
+                s_seq[et] = seq;
+                s_pos[et] = pos;
+                long long crow = -1;
+                if (seq >= 0 && f.k_pool != nullptr) {
+                    const int pg = f.table[(size_t)seq * f.table_width + pos / f.page];
+                    crow = ((long long)pg * f.page + pos % f.page) * f.nkv * f.hd;
+                }
+                s_crow[et] = crow;
+            }
             asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (rope && f.denom != nullptr) {
+                const int half = f.rot >> 1;
+                for (int idx = et; idx < nt * half; idx += 128) {
+                    const int token = idx / half, i = idx - token * half;
+                    float sn = 0.f, cs = 1.f;
+                    if (s_seq[token] >= 0) sincosf(__fdiv_rn((float)s_pos[token], s_den[i]), &sn, &cs);
+                    s_cs[token * 64 + i] = make_float2(cs, sn);
+                }
+            }
         };
-        auto put16 = [&](int q_blk, int c, int gi, const float (&v)[16]) {    // 16 rows of this thread's feature
-            const float b = p.bias ? bias_at(p, gi) : 0.f;
-            const int n = min(16, p.q_rows - q_blk * BN - c * 16);
+        // 16 rows of the step for this thread's column: into the transposed tile.
+        auto put16 = [&](int c, const float (&v)[16]) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                if (j < n) {
-                    uint8_t* at = s_tile + (c * 16 + j) * row_bytes + i_local * elem;
-                    if (p.out_dtype == FR_BF16) {
-                        const float r = p.residual ? __bfloat162float(*(const __nv_bfloat16*)at) : 0.f;
-                        *(__nv_bfloat16*)at = __float2bfloat16_rn(v[j] + b + r);
+            for (int j = 0; j < 16; ++j) s_sum[(c * 16 + j) * TILE_P + i_local] = v[j];
+        };
+        // bias and residual added to 8 sums of one row; the values as they will be stored (bf16: rounded)
+        auto load_piece = [&](int token, int f0, float (&x)[8]) {
+            const float4 a0 = *(const float4*)(s_sum + token * TILE_P + f0), a1 = *(const float4*)(s_sum + token * TILE_P + f0 + 4);
+            const float4 b0 = *(const float4*)(s_bias + f0), b1 = *(const float4*)(s_bias + f0 + 4);
+            x[0] = a0.x + b0.x; x[1] = a0.y + b0.y; x[2] = a0.z + b0.z; x[3] = a0.w + b0.w;
+            x[4] = a1.x + b1.x; x[5] = a1.y + b1.y; x[6] = a1.z + b1.z; x[7] = a1.w + b1.w;
+        };
+        auto round8 = [&](const float (&x)[8]) {
+            uint4 w;
+            w.x = pack2(x[0], x[1]); w.y = pack2(x[2], x[3]); w.z = pack2(x[4], x[5]); w.w = pack2(x[6], x[7]);
+            return w;
+        };
+        auto finish_rows = [&](int p_blk, int q_blk) {
+            const int nt = min(BN, p.q_rows - q_blk * BN);
+            const int half = f.rot >> 1;
+#pragma unroll
+            for (int k = 0; k < ITEMS; ++k) {
+                if (k * 128 >= nt * 16) break;
+                const int idx = k * 128 + et, token = idx >> 4, f0 = (idx & 15) * 8;
+                const bool active = idx < nt * 16;
+                const int row = q_blk * BN + token, col = p_blk * TILE_P + f0;
+                float ss = 0.f;
+                if (active) {
+                    float x[8];
+                    load_piece(token, f0, x);
+                    if (!bf16_out) {
+                        float4* dst = (float4*)((float*)p.out + (size_t)row * p.ldo + col);
+                        dst[0] = make_float4(x[0], x[1], x[2], x[3]);
+                        dst[1] = make_float4(x[4], x[5], x[6], x[7]);
                     } else {
-                        const float r = p.residual ? *(const float*)at : 0.f;
-                        *(float*)at = v[j] + b + r;
+                        if (p.residual != nullptr) {
+                            const uint32_t r[4] = {res[k].x, res[k].y, res[k].z, res[k].w};
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                x[2 * j] += __uint_as_float(r[j] << 16);
+                                x[2 * j + 1] += __uint_as_float(r[j] & 0xffff0000u);
+                            }
+                        }
+                        __nv_bfloat16* out_at = (__nv_bfloat16*)p.out + (size_t)row * p.ldo + col;
+                        uint4 w = round8(x);
+                        if (rope) {
+                            // heads never straddle tiles; f_in: the piece's first column within its head
+                            const int h = col / f.hd, f_in = col - h * f.hd;
+                            const long long crow = s_crow[token];
+                            __nv_bfloat16* cache_at = nullptr;
+                            if (crow >= 0 && h >= f.nq)
+                                cache_at = (h < f.nq + f.nkv ? (__nv_bfloat16*)f.k_pool + (size_t)(h - f.nq) * f.hd
+                                                             : (__nv_bfloat16*)f.v_pool + (size_t)(h - f.nq - f.nkv) * f.hd) + crow + f_in;
+                            if (f.denom != nullptr && h < f.nq + f.nkv && f_in < f.rot && s_seq[token] >= 0) {
+                                if (f_in < half) {
+                                    // this piece and its partner `half` columns on, rotated together
+                                    float y[8];
+                                    load_piece(token, f0 + half, y);
+                                    const uint4 wy = round8(y);
+                                    const uint32_t lo[4] = {w.x, w.y, w.z, w.w}, hi[4] = {wy.x, wy.y, wy.z, wy.w};
+                                    float ra[8], rb[8];
+#pragma unroll
+                                    for (int j = 0; j < 8; ++j) {
+                                        const float a = __uint_as_float(j & 1 ? lo[j >> 1] & 0xffff0000u : lo[j >> 1] << 16);
+                                        const float b = __uint_as_float(j & 1 ? hi[j >> 1] & 0xffff0000u : hi[j >> 1] << 16);
+                                        const float2 cs = s_cs[token * 64 + f_in + j];
+                                        fr_rotate(a, b, cs.x, cs.y, ra[j], rb[j]);
+                                    }
+                                    const uint4 wa = round8(ra), wb = round8(rb);
+                                    *(uint4*)out_at = wa;
+                                    *(uint4*)(out_at + half) = wb;
+                                    if (cache_at != nullptr) {
+                                        *(uint4*)cache_at = wa;
+                                        *(uint4*)(cache_at + half) = wb;
+                                    }
+                                }
+                            } else {
+                                *(uint4*)out_at = w;
+                                if (cache_at != nullptr) *(uint4*)cache_at = w;
+                            }
+                        } else {
+                            *(uint4*)out_at = w;
+                            if (f.norm_out != nullptr) {
+                                // the RMSNorm that follows, begun: g (*) x rounded, and this piece's share of the row's
+                                // sum of squares (sixteen lanes per row, summed in a fixed order below)
+                                const uint32_t r[4] = {w.x, w.y, w.z, w.w};
+                                float hx[8];
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) {
+                                    const float xr = __uint_as_float(j & 1 ? r[j >> 1] & 0xffff0000u : r[j >> 1] << 16);
+                                    ss += xr * xr;
+                                    hx[j] = xr * s_g[f0 + j];
+                                }
+                                *(uint4*)((__nv_bfloat16*)f.norm_out + (size_t)row * p.ldo + col) = round8(hx);
+                            }
+                        }
                     }
                 }
+                if (f.norm_out != nullptr) {
+#pragma unroll
+                    for (int o = 1; o < 16; o <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                    if (active && f0 == 0) f.out_ssq[(size_t)p_blk * p.q_rows + row] = ss;
+                }
             }
         };
-        auto stage_out = [&](int p_blk, int q_blk) {       // s_tile -> output rows of the tile
+        // The factors 1 / sqrt(mean x^2 + eps) of the rows of the step that this tile covers.
+        int scale_blk = -1;
+        auto load_scale = [&](int blk) {
+            if (f.in_ssq == nullptr || blk == scale_blk) return;
             asm volatile("bar.sync 1, 128;" ::: "memory");
-            const int nt = min(BN, p.q_rows - q_blk * BN);
-            for (int c = et; c < nt * pieces; c += 128) {
-                const int token = c / pieces, piece = c - token * pieces;
-                char* dst = (char*)p.out + ((size_t)(q_blk * BN + token) * p.ldo + (size_t)p_blk * TILE_P) * elem;
-                *((uint4*)dst + piece) = *(const uint4*)(s_tile + token * row_bytes + piece * 16);
+            const int rows = p.swapped ? p.q_rows : p.p_rows, per = p.swapped ? BN : TILE_P;
+            if (et < per) {
+                const int row = blk * per + et;
+                float ss = 0.f;
+                if (row < rows)
+                    for (int t = 0; t < f.in_parts; ++t) ss += __ldcg(f.in_ssq + (size_t)t * rows + row);
+                s_scale[et] = 1.0f / sqrtf(ss / f.in_width + f.in_eps);
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
+            scale_blk = blk;
+        };
+        auto scale16 = [&](int c, float (&v)[16]) {
+            if (f.in_ssq == nullptr) return;
+            if (p.swapped) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] *= s_scale[(c * 16 + j) & (TILE_P - 1)];
+            } else {
+                const float r = s_scale[i_local];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] *= r;
+            }
         };
         for (; ok && work.next(item); ++it) {
             const int tile = item.tile;
             const int q_blk = tile / p.tiles_p, p_blk = tile - q_blk * p.tiles_p;
             const int a = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
-            if (!(ok = mbar_wait(accf0 + 8 * a, acc_phase, p.status, 4))) break;
-            tc_fence_after();
             const int gi = p_blk * TILE_P + i_local;
             const bool staged = can_stage && (p_blk + 1) * TILE_P <= p.p_rows;
+            load_scale(p.swapped ? q_blk : p_blk);
+            if (staged) prefetch_tile(p_blk, q_blk);
+            if (!(ok = mbar_wait(accf0 + 8 * a, acc_phase, p.status, 4))) break;
+            if (et == 0) mark(p, 6);
+            tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + a * BN;
             // partial tiles are laid out [chunk of 16 columns][row][16]: a warp's 32 rows are 2 KB in one piece
             float* part = item.nseg > 1 ? p.ws + (size_t)item.part * TILE_P * BN + (size_t)i_local * 16 : nullptr;
-            if (part == nullptr && staged) stage_in(p_blk, q_blk);
 #pragma unroll 1
             for (int c = 0; c < BN / 16; ++c) {
                 uint32_t r[16];
@@ -316,7 +500,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
 #pragma unroll
                 for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
                 if (part == nullptr) {
-                    if (staged) put16(q_blk, c, gi, v);
+                    scale16(c, v);
+                    if (staged) put16(c, v);
                     else finish16(p, gi, q_blk * BN + c * 16, v);
                 } else {
 #pragma unroll
@@ -328,39 +513,68 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acce0 + 8 * a);     // the accumulator may be overwritten
-            if (part == nullptr && staged) stage_out(p_blk, q_blk);
-            if (item.nseg > 1) {
-                __threadfence();
+            if (part == nullptr && staged) {
                 asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (et == 0) flags[0] = atomicAdd(p.counters + tile, 1) == item.nseg - 1;
+                finish_rows(p_blk, q_blk);
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+            }
+            if (item.nseg > 1) {
+                // The partial tile is written; whoever adds the tile's last one sums them all (thread 0 of the epilogue
+                // publishes for the CTA: the barrier before it orders the other threads' stores before its fence).
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (et == 0) {
+                    __threadfence();
+                    flags[0] = atomicAdd(p.counters + tile, 1) == item.nseg - 1;
+                    __threadfence();
+                }
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (flags[0]) {
-                    __threadfence();
+                    if (et == 0) mark(p, 8);
                     const float* mine = p.ws + (size_t)i_local * 16;
-                    if (staged) stage_in(p_blk, q_blk);
 #pragma unroll 1
                     for (int c = 0; c < BN / 16; ++c) {
                         float v[16];
 #pragma unroll
                         for (int j = 0; j < 16; ++j) v[j] = 0.f;
-#pragma unroll 4
-                        for (int s = 0; s < item.nseg; ++s) {
-                            const float4* src = (const float4*)(mine + (size_t)work.contributor(item, s) * TILE_P * BN +
-                                                                (size_t)c * TILE_P * 16);
+                        // eight partial tiles at a time: all their loads are on their way before the first sum
+                        for (int s0 = 0; s0 < item.nseg; s0 += 8) {
+                            float4 x[8][4];
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const float4 x = __ldcg(src + j);
-                                v[4 * j] += x.x; v[4 * j + 1] += x.y; v[4 * j + 2] += x.z; v[4 * j + 3] += x.w;
+                            for (int s = 0; s < 8; ++s) {
+                                if (s0 + s < item.nseg) {
+                                    const float4* src = (const float4*)(mine + (size_t)work.contributor(item, s0 + s) * TILE_P * BN +
+                                                                        (size_t)c * TILE_P * 16);
+#pragma unroll
+                                    for (int j = 0; j < 4; ++j) x[s][j] = __ldcg(src + j);
+                                }
+                            }
+#pragma unroll
+                            for (int s = 0; s < 8; ++s) {
+                                if (s0 + s < item.nseg) {
+#pragma unroll
+                                    for (int j = 0; j < 4; ++j) {
+                                        v[4 * j] += x[s][j].x; v[4 * j + 1] += x[s][j].y;
+                                        v[4 * j + 2] += x[s][j].z; v[4 * j + 3] += x[s][j].w;
+                                    }
+                                }
                             }
                         }
-                        if (staged) put16(q_blk, c, gi, v);
+                        if (et == 0) mark(p, 10);
+                        scale16(c, v);
+                        if (staged) put16(c, v);
                         else finish16(p, gi, q_blk * BN + c * 16, v);
                     }
-                    if (staged) stage_out(p_blk, q_blk);
+                    if (staged) {
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                        if (et == 0) mark(p, 11);
+                        finish_rows(p_blk, q_blk);
+                    }
+                    if (et == 0) mark(p, 12);
                     if (et == 0) p.counters[tile] = 0;     // ready for the next launch
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");
             }
+            if (et == 0) mark(p, 7);
         }
     }
     tc_fence_before();
@@ -417,14 +631,21 @@ bool use_stream_k() {
 }
 
 template <int BN, int STAGES>
-int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmParams& p, int grid, cudaStream_t stream) {
-    constexpr int smem = STAGES * (P_BYTES + BN * TILE_K * 2) + 1024 + 256 + (BN <= 64 ? BN * TILE_P * 4 : 0);
+int configure() {
     static bool configured = false;
     if (!configured) {
-        FR_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        FR_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     smem_bytes<BN, STAGES>()));
         configured = true;
     }
-    FR_CUDA(fr_launch(gemm_tc_kernel<BN, STAGES>, dim3(grid), dim3(THREADS), smem, stream, mp, mq, p));
+    return FR_OK;
+}
+
+template <int BN, int STAGES>
+int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmParams& p, int grid, cudaStream_t stream) {
+    const int rc = configure<BN, STAGES>();
+    if (rc) return rc;
+    FR_CUDA(fr_launch(gemm_tc_kernel<BN, STAGES>, dim3(grid), dim3(THREADS), smem_bytes<BN, STAGES>(), stream, mp, mq, p));
     FR_CHECK_LAUNCH("gemm_tc");
     return FR_OK;
 }
@@ -468,10 +689,10 @@ FR_EXPORT int gemm_tc_plan(int m, int n, int k, int sm_count, int swap, int bn, 
     return FR_OK;
 }
 
-FR_EXPORT int gemm_tc_act(const void* x, const void* w, void* out, int out_dtype, const void* bias, int bias_dtype,
-                          const void* residual, int m, int n, int k, int lda, int ldw, int ldo, float* scratch,
-                          long long scratch_floats, int* counters, int n_counters, int* status, int sm_count, int swap,
-                          int bn, int splits, int act, cudaStream_t stream);
+FR_EXPORT int gemm_tc_fused(const void* x, const void* w, void* out, int out_dtype, const void* bias, int bias_dtype,
+                            const void* residual, int m, int n, int k, int lda, int ldw, int ldo, float* scratch,
+                            long long scratch_floats, int* counters, int n_counters, int* status, int sm_count,
+                            int swap, int bn, int splits, int act, const GemmFusion* fusion, cudaStream_t stream);
 
 // x [m][k] (row stride lda), w [n][k] (ldw): bf16.  out, residual [m][n] (ldo), bf16 or fp32 (out_dtype).
 // scratch/counters/status: device buffers of the caller; counters must be zero on entry and are zero on return.
@@ -479,8 +700,8 @@ FR_EXPORT int gemm_tc(const void* x, const void* w, void* out, int out_dtype, co
                       const void* residual, int m, int n, int k, int lda, int ldw, int ldo, float* scratch,
                       long long scratch_floats, int* counters, int n_counters, int* status, int sm_count, int swap,
                       int bn, int splits, cudaStream_t stream) {
-    return gemm_tc_act(x, w, out, out_dtype, bias, bias_dtype, residual, m, n, k, lda, ldw, ldo, scratch, scratch_floats,
-                       counters, n_counters, status, sm_count, swap, bn, splits, 0, stream);
+    return gemm_tc_fused(x, w, out, out_dtype, bias, bias_dtype, residual, m, n, k, lda, ldw, ldo, scratch,
+                         scratch_floats, counters, n_counters, status, sm_count, swap, bn, splits, 0, nullptr, stream);
 }
 
 // The same with an activation in the epilogue.  act = 1: the rows of w are (gate, up) pairs, n is even, and
@@ -489,6 +710,16 @@ FR_EXPORT int gemm_tc_act(const void* x, const void* w, void* out, int out_dtype
                           const void* residual, int m, int n, int k, int lda, int ldw, int ldo, float* scratch,
                           long long scratch_floats, int* counters, int n_counters, int* status, int sm_count, int swap,
                           int bn, int splits, int act, cudaStream_t stream) {
+    return gemm_tc_fused(x, w, out, out_dtype, bias, bias_dtype, residual, m, n, k, lda, ldw, ldo, scratch,
+                         scratch_floats, counters, n_counters, status, sm_count, swap, bn, splits, act, nullptr, stream);
+}
+
+// The same with work fused at either end (gemm_tc_fusion.h); fusion may be null.  What a fused part needs of the
+// shape is checked here, and refused with the reason: the caller then runs the separate kernels.
+FR_EXPORT int gemm_tc_fused(const void* x, const void* w, void* out, int out_dtype, const void* bias, int bias_dtype,
+                            const void* residual, int m, int n, int k, int lda, int ldw, int ldo, float* scratch,
+                            long long scratch_floats, int* counters, int n_counters, int* status, int sm_count,
+                            int swap, int bn, int splits, int act, const GemmFusion* fusion, cudaStream_t stream) {
     if (m <= 0 || n <= 0) return FR_OK;
     if (act != 0 && act != 1) FR_REFUSE("gemm_tc: unknown activation %d", act);
     if (act && (n % 2 || bias != nullptr || residual != nullptr || out_dtype != FR_BF16))
@@ -505,6 +736,35 @@ FR_EXPORT int gemm_tc_act(const void* x, const void* w, void* out, int out_dtype
         FR_REFUSE("gemm_tc: split-k needs %lld scratch floats and %lld counters, given %lld and %d", plan[3], plan[4],
                   scratch_floats, n_counters);
     GemmParams p;
+    p.f = GemmFusion{};
+    if (fusion != nullptr) {
+        p.f = *fusion;
+        const GemmFusion& f = p.f;
+        const bool rope = f.row_pos != nullptr || f.row_seq != nullptr || f.denom != nullptr || f.k_pool != nullptr;
+        if (f.in_ssq != nullptr && (f.in_parts <= 0 || !(f.in_width > 0.f) || (swap && bn > TILE_P)))
+            FR_REFUSE("gemm_tc: a deferred norm of the input needs its partial sums, the width, and tiles of at most %d rows", TILE_P);
+        if (f.norm_out != nullptr || rope) {
+            // both work on the staged tile of the swapped orientation: whole tiles of 128 columns, rows of 16-byte pieces
+            if (!swap || act || out_dtype != FR_BF16 || bn > 64 || n % TILE_P || ldo % 8 ||
+                (((uintptr_t)out | (uintptr_t)residual | (uintptr_t)f.norm_out) & 15))
+                FR_REFUSE("gemm_tc: a fused norm or rotation needs few rows (swapped tiles up to 64 wide), bf16 output "
+                          "without activation, n a multiple of %d and 16-byte aligned rows", TILE_P);
+        }
+        if (f.norm_out != nullptr && (f.norm_w == nullptr || f.out_ssq == nullptr))
+            FR_REFUSE("gemm_tc: a fused norm needs its weight and a buffer for the sums of squares");
+        if (rope) {
+            if (f.row_pos == nullptr || f.row_seq == nullptr) FR_REFUSE("gemm_tc: rotation and cache write need row_seq and row_pos");
+            if (f.hd <= 0 || TILE_P % f.hd || f.hd % 8 || (long long)(f.nq + 2 * f.nkv) * f.hd != n)
+                FR_REFUSE("gemm_tc: fused rotation needs a head size that divides %d and n = (q + 2 kv heads) * head size", TILE_P);
+            if (f.denom != nullptr && (f.rot <= 0 || f.rot > f.hd || f.rot % 16))
+                FR_REFUSE("gemm_tc: fused rotation needs a rotary size (%d) that is a multiple of 16, at most the head size %d", f.rot, f.hd);
+            if (bn != 16 || f.norm_out != nullptr || residual != nullptr)
+                FR_REFUSE("gemm_tc: fused rotation needs at most 16 rows and goes without residual or fused norm");
+            if (f.k_pool != nullptr && (f.v_pool == nullptr || f.table == nullptr || f.page <= 0 ||
+                                        (((uintptr_t)f.k_pool | (uintptr_t)f.v_pool) & 15)))
+                FR_REFUSE("gemm_tc: cache write asked for without a whole cache");
+        }
+    }
     p.out = out; p.bias = bias; p.residual = residual; p.ws = scratch; p.counters = counters; p.status = status;
     p.p_rows = swap ? n : m; p.q_rows = swap ? m : n; p.ldo = ldo; p.out_dtype = out_dtype; p.bias_dtype = bias_dtype;
     p.swapped = swap;
@@ -534,7 +794,7 @@ FR_EXPORT int gemm_tc_act(const void* x, const void* w, void* out, int out_dtype
     switch (bn) {
         case 16: return launch<16, 10>(mp, mq, p, grid, stream);
         case 32: return launch<32, 10>(mp, mq, p, grid, stream);
-        case 64: return launch<64, 8>(mp, mq, p, grid, stream);
+        case 64: return launch<64, 7>(mp, mq, p, grid, stream);
         case 128: return launch<128, 6>(mp, mq, p, grid, stream);
         default: return launch<256, 4>(mp, mq, p, grid, stream);
     }
@@ -559,7 +819,7 @@ NoAllocDevice noalloc_devices[64];
 template <int BN, int STAGES>
 cudaError_t allow_smem() {
     return cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                STAGES * (P_BYTES + BN * TILE_K * 2) + 1024 + 256 + (BN <= 64 ? BN * TILE_P * 4 : 0));
+                                smem_bytes<BN, STAGES>());
 }
 
 // Once per device, with that device current.
@@ -570,7 +830,7 @@ int noalloc_setup(int device) {
     FR_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, device));
     FR_CUDA((allow_smem<16, 10>()));
     FR_CUDA((allow_smem<32, 10>()));
-    FR_CUDA((allow_smem<64, 8>()));
+    FR_CUDA((allow_smem<64, 7>()));
     FR_CUDA((allow_smem<128, 6>()));
     FR_CUDA((allow_smem<256, 4>()));
     d.base = (unsigned char*)ptr;

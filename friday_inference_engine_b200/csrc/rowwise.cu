@@ -247,7 +247,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
             const float c = cos_sin[2 * i], s = cos_sin[2 * i + 1];
             T* v = base + (size_t)h * hd;
             const float a = fr_load(v + i), b = fr_load(v + i + half);
-            const float ra = a * c - b * s, rb = a * s + b * c;
+            float ra, rb;
+            fr_rotate(a, b, c, s, ra, rb);
             fr_store(v + i, ra);
             fr_store(v + i + half, rb);
             if (write && h >= nq) {

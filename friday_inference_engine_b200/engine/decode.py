@@ -13,6 +13,8 @@ It uses the same model, cache, kernels and page tables as the step function; onl
 buffers are long-lived.  A row whose sequence has ended is marked dead (row_seq < 0):
 kernels skip it and the sampler returns 0 for it.
 """
+import gc
+
 import numpy as np
 import torch
 
@@ -124,10 +126,10 @@ class DeviceDecoder:
     def _body(self):
         if self.fused is not None:
             ops.embedding(self.tokens, self.model.embedding, out=self.fused.x)
-            x = self.fused.run(self.row_seq, self.row_pos, self.bound)
+            x, normed = self.fused.run(self.row_seq, self.row_pos, self.bound), None
         else:
-            x = self.model.run(self.tokens, self.ctx, self._views())
-        self.logits = self.model.logits(x)
+            x, normed = self.model.run(self.tokens, self.ctx, self._views(), final_norm=True)
+        self.logits = self.model.logits(x, normed=normed)
         ops.sample(self.logits, self.temperature, self.streams, self.draws, self.seed, row_live=self.row_seq,
                    out=self.sampled)
         ops.advance(self.tokens, self.sampled, self.row_pos, self.kv_len, self.row_seq)
@@ -178,8 +180,18 @@ class DeviceDecoder:
                 self.graph = torch.cuda.CUDAGraph()
                 torch.cuda.synchronize()
                 before = lib.launch_count()
-                with torch.cuda.graph(self.graph):
-                    self._body()
+                # Captured steps of decoders that nothing refers to any more must not be destroyed while this one
+                # is being captured (the runtime refuses that and the capture is lost): collect them now, and keep
+                # the collector quiet until the capture has ended.
+                gc.collect()
+                collecting = gc.isenabled()
+                gc.disable()
+                try:
+                    with torch.cuda.graph(self.graph):
+                        self._body()
+                finally:
+                    if collecting:
+                        gc.enable()
                 lib.add_launches(before - lib.launch_count())     # capturing launched nothing
                 self.graphs[self.bound] = self.graph
             self.graph.replay()

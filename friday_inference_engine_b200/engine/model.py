@@ -54,18 +54,35 @@ class DecoderModel:
         return {entry: self.layers[self.program[i].layer].cache_request() for entry, i in self.owners.items()}
 
     # -- the forward pass of one pass of the step function -------------------
-    def run(self, tokens, ctx, views):
-        """tokens: int32 [rows] on the device; views: one cache view (or None) per program entry."""
-        x = ops.embedding(tokens, self.embedding)
-        for call, view in zip(self.program, views):
-            x = self.layers[call.layer].forward(x, ctx, view)
-        return x
+    def run(self, tokens, ctx, views, final_norm=False):
+        """tokens: int32 [rows] on the device; views: one cache view (or None) per program entry.  Returns the
+        residual stream, and with final_norm also its final norm (every row's), as `logits` takes it.
 
-    def logits(self, x, rows=None):
-        """fp32 logits [n, vocab] of the rows `rows` (int32 device tensor) of x, or of all rows."""
+        A block that chains norms is told which norm follows it (the next block's first, or the final one), so
+        that its last product can begin that norm, and is handed its own first norm if the block before did so."""
+        x = ops.embedding(tokens, self.embedding)
+        normed = None
+        for i, (call, view) in enumerate(zip(self.program, views)):
+            block = self.layers[call.layer]
+            if not block.chains_norm:
+                x, normed = block.forward(x, ctx, view), None
+                continue
+            if i + 1 < len(self.program):
+                nxt = self.layers[self.program[i + 1].layer]
+                then = nxt.first_norm if nxt.chains_norm else None
+            else:
+                then = self.final_norm if final_norm else None
+            x, normed = block.forward(x, ctx, view, normed=normed, then=then)
+        return (x, normed) if final_norm else x
+
+    def logits(self, x, rows=None, normed=None):
+        """fp32 logits [n, vocab] of the rows `rows` (int32 device tensor) of x, or of all rows.  normed: the
+        final norm of all rows of x, if the caller has it."""
         if rows is not None:
-            x = ops.gather_rows(rows, x)
-        return ops.linear(self.final_norm.forward(x), self.head, out_dtype=torch.float32)
+            x, normed = ops.gather_rows(rows, x), None
+        if normed is None:
+            normed = self.final_norm.forward(x)
+        return ops.linear(normed, self.head, out_dtype=torch.float32)
 
     def parameter_bytes(self):
         seen, total = set(), 0

@@ -38,6 +38,31 @@ def _need_cuda(*tensors):
             raise KernelError("tensor on %s: this library runs on CUDA devices only, it has no CPU path" % t.device)
 
 
+class DeferredNorm:
+    """Rows whose RMSNorm is half done by the product that made them: `scaled` holds weight (*) x rounded to
+    bf16, `ssq` [parts, rows] each part's share of the rows' sums of squares.  The product that takes the rows
+    finishes the norm by scaling its own rows with 1 / sqrt(sum / width + eps); anything else asks for
+    `materialize()`, which runs the norm's kernel on the rows themselves."""
+
+    def __init__(self, scaled, ssq, eps, source, weight):
+        self.scaled, self.ssq, self.eps, self.source, self.weight = scaled, ssq, float(eps), source, weight
+        self.shape, self.dtype, self.device = scaled.shape, scaled.dtype, scaled.device
+
+    def materialize(self):
+        return rmsnorm(self.source, self.weight, self.eps)
+
+
+def materialize(h):
+    """The plain tensor behind what a product returned as normed rows."""
+    return h.materialize() if isinstance(h, DeferredNorm) else h
+
+
+def fusion_enabled():
+    """FRIDAY_FUSE=0 keeps norms, rotation and cache write in kernels of their own (for comparison)."""
+    import os
+    return os.environ.get("FRIDAY_FUSE", "1") != "0"
+
+
 def _rowmajor(t, what):
     if t.dim() != 2 or t.stride(1) != 1:
         raise KernelError("%s must be a 2-d tensor with unit inner stride, got shape %s strides %s"
@@ -52,6 +77,7 @@ class CudaOps:
     def __init__(self):
         self._tc = {}
         self._attn_counters = {}
+        self._cluster_fit = {}
 
     # -- row-wise ---------------------------------------------------------
     def embedding(self, tokens, table, out=None):
@@ -114,7 +140,10 @@ class CudaOps:
 
     # -- matrix products --------------------------------------------------
     def linear(self, x, weight, bias=None, residual=None, out_dtype=None, out=None):
-        """x [rows, k] @ weight [n, k]^T (+ bias [n]) (+ residual [rows, n])."""
+        """x [rows, k] @ weight [n, k]^T (+ bias [n]) (+ residual [rows, n]).  x may be a DeferredNorm."""
+        deferred = x if isinstance(x, DeferredNorm) else None
+        if deferred is not None:
+            x = deferred.scaled
         _need_cuda(x, weight, bias, residual)
         _rowmajor(x, "linear input")
         _rowmajor(weight, "linear weight")
@@ -128,9 +157,82 @@ class CudaOps:
         if residual is not None:
             assert residual.shape == out.shape and residual.dtype == out.dtype and residual.stride() == out.stride()
         if self.tensor_core_ok(x, weight, out, residual):
-            return self._linear_tc(x, weight, bias, residual, out)
+            return self._linear_tc(x, weight, bias, residual, out, fusion=self._fusion_in(deferred))
+        if deferred is not None:
+            x = deferred.materialize()
         self._linear_simt(x, weight, bias, residual, out)
         return out
+
+    @staticmethod
+    def _fusion_in(deferred, fusion=None):
+        """The fields of the fusion struct that finish a deferred norm of the input."""
+        if deferred is None:
+            return fusion
+        fusion = fusion or lib.GemmFusion()
+        fusion.in_ssq, fusion.in_parts = _ptr(deferred.ssq), deferred.ssq.shape[0]
+        fusion.in_width, fusion.in_eps = float(deferred.scaled.shape[1]), deferred.eps
+        return fusion
+
+    def _few_rows_tile_ok(self, x, weight, out, residual):
+        """What the fused epilogues of the tensor-core product need: a one-token step's few rows, bf16, whole
+        tiles of 128 output columns."""
+        return (fusion_enabled() and out.dtype == torch.bfloat16 and x.shape[0] <= 16 and weight.shape[0] % 128 == 0
+                and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0
+                and (residual is None or residual.data_ptr() % 16 == 0)
+                and self.tensor_core_ok(x, weight, out, residual))
+
+    def linear_norm(self, x, weight, norm_weight, eps, bias=None, residual=None):
+        """linear(...) and the RMSNorm of its result: (out, normed).  For a few bf16 rows the norm is begun in
+        the product's epilogue and `normed` is a DeferredNorm that the next product finishes; otherwise the
+        norm's kernel runs and `normed` is a tensor."""
+        deferred = x if isinstance(x, DeferredNorm) else None
+        xt = deferred.scaled if deferred is not None else x
+        _need_cuda(xt, weight, bias, residual, norm_weight)
+        rows, n = xt.shape[0], weight.shape[0]
+        if xt.dim() == 2 and weight.dim() == 2 and xt.shape[1] == weight.shape[1] and norm_weight.numel() == n:
+            out = torch.empty((rows, n), dtype=xt.dtype, device=xt.device)
+            if self._few_rows_tile_ok(xt, weight, out, residual) and norm_weight.is_contiguous():
+                if residual is not None:
+                    assert residual.shape == out.shape and residual.dtype == out.dtype and residual.stride() == out.stride()
+                scaled = torch.empty_like(out)
+                ssq = torch.empty((n // 128, rows), dtype=torch.float32, device=out.device)
+                fusion = self._fusion_in(deferred, lib.GemmFusion())
+                fusion.norm_w, fusion.norm_w_dtype = _ptr(norm_weight), code_of(norm_weight.dtype)
+                fusion.norm_out, fusion.out_ssq = _ptr(scaled), _ptr(ssq)
+                self._linear_tc(xt, weight, bias, residual, out, fusion=fusion)
+                return out, DeferredNorm(scaled, ssq, eps, out, norm_weight)
+        out = self.linear(x, weight, bias=bias, residual=residual)
+        return out, self.rmsnorm(out, norm_weight, eps)
+
+    def qkv_rope_write(self, x, weight, bias, row_seq, row_pos, denom, rotary_dim, n_heads, n_kv_heads, head_dim,
+                       k_pool=None, v_pool=None, block_table=None, page_size=0):
+        """linear(x, weight, bias) followed by rope_kv_write on its result, which it returns.  For a few bf16
+        rows and a head size that divides 128 both happen in the product's epilogue."""
+        deferred = x if isinstance(x, DeferredNorm) else None
+        xt = deferred.scaled if deferred is not None else x
+        n = weight.shape[0]
+        write = k_pool is not None
+        if xt.dim() == 2 and weight.dim() == 2 and xt.shape[1] == weight.shape[1] and 128 % head_dim == 0 \
+                and head_dim % 8 == 0 and n == (n_heads + 2 * n_kv_heads) * head_dim \
+                and (denom is None or rotary_dim % 16 == 0):
+            out = torch.empty((xt.shape[0], n), dtype=xt.dtype, device=xt.device)
+            if self._few_rows_tile_ok(xt, weight, out, None) and (not write or k_pool.dtype == torch.bfloat16):
+                _need_cuda(xt, weight, bias, row_seq, row_pos, denom, k_pool, v_pool, block_table)
+                fusion = self._fusion_in(deferred, lib.GemmFusion())
+                fusion.row_seq, fusion.row_pos, fusion.denom = _ptr(row_seq), _ptr(row_pos), _ptr(denom)
+                fusion.rot, fusion.nq, fusion.nkv, fusion.hd = int(rotary_dim), n_heads, n_kv_heads, head_dim
+                if denom is not None:
+                    assert denom.dtype == torch.float32 and denom.numel() == rotary_dim // 2
+                if write:
+                    assert k_pool.is_contiguous() and v_pool.is_contiguous() and block_table.dim() == 2
+                    fusion.k_pool, fusion.v_pool, fusion.table = _ptr(k_pool), _ptr(v_pool), _ptr(block_table)
+                    fusion.table_width, fusion.page = block_table.shape[1], int(page_size)
+                return self._linear_tc(xt, weight, bias, None, out, fusion=fusion)
+        qkv = self.linear(x, weight, bias=bias)
+        if denom is not None or write:
+            self.rope_kv_write(qkv, row_seq, row_pos, denom, rotary_dim, n_heads, n_kv_heads, head_dim, k_pool, v_pool,
+                               block_table, page_size)
+        return qkv
 
     # Scratch of the tensor-core product (partial tiles of split-k), its tile counters and the word in which
     # a kernel records a wait that gave up: one set per device, made once, so that captured graphs keep
@@ -157,27 +259,40 @@ class CudaOps:
                 and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0
                 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
-    def _linear_tc(self, x, weight, bias, residual, out, swap=-1, bn=-1, splits=-1, act=0):
+    # For measurements: a tensor [launches, 148, 16] of int64 that every tensor-core product from now on fills
+    # with its CTAs' timestamps, one launch after the other (gemm_tc_fusion.h, part 4); None switches it off.
+    trace = None
+    trace_next = 0
+
+    def _linear_tc(self, x, weight, bias, residual, out, swap=-1, bn=-1, splits=-1, act=0, fusion=None):
+        import ctypes
         scratch, counters, status, sms = self._tc_buffers(x.device)
         rows, k = x.shape
+        if self.trace is not None and self.trace_next < self.trace.shape[0]:
+            fusion = fusion or lib.GemmFusion()
+            fusion.trace = self.trace[self.trace_next].data_ptr()
+            self.trace_next += 1
         lib.family("gemm_tc").call(
-            "gemm_tc_act", _ptr(x), _ptr(weight), _ptr(out), code_of(out.dtype), _ptr(bias),
+            "gemm_tc_fused", _ptr(x), _ptr(weight), _ptr(out), code_of(out.dtype), _ptr(bias),
             code_of(bias.dtype) if bias is not None else 0, _ptr(residual), rows, weight.shape[0], k, x.stride(0),
             weight.stride(0), out.stride(0), _ptr(scratch), scratch.numel(), _ptr(counters), counters.numel(),
-            _ptr(status), sms, swap, bn, splits, act, _stream())
+            _ptr(status), sms, swap, bn, splits, act, ctypes.byref(fusion) if fusion is not None else None, _stream())
         return out
 
     def linear_swiglu(self, x, weight_pairs):
         """silu(x Wg^T) * (x Wu^T) for weight_pairs [2 * inner, k] whose rows alternate gate, up: one product
         with the activation in its epilogue on the tensor cores, else the product followed by the kernel."""
+        deferred = x if isinstance(x, DeferredNorm) else None
+        if deferred is not None:
+            x = deferred.scaled
         _need_cuda(x, weight_pairs)
         _rowmajor(x, "linear input")
         _rowmajor(weight_pairs, "linear weight")
         rows, inner = x.shape[0], weight_pairs.shape[0] // 2
         out = torch.empty((rows, inner), dtype=x.dtype, device=x.device)
         if self.tensor_core_ok(x, weight_pairs, out, None) and out.dtype == torch.bfloat16:
-            return self._linear_tc(x, weight_pairs, None, None, out, act=1)
-        return self.swiglu(self.linear(x, weight_pairs))
+            return self._linear_tc(x, weight_pairs, None, None, out, act=1, fusion=self._fusion_in(deferred))
+        return self.swiglu(self.linear(deferred if deferred is not None else x, weight_pairs))
 
     def check_status(self):
         """Raises if a kernel recorded that one of its waits gave up (reads one word per device; call it
@@ -216,7 +331,7 @@ class CudaOps:
             keys_mode = bool(geometry.decode)
             splits = 1
             if keys_mode:
-                splits = self.decode_splits(geometry.n_seqs, n_heads, n_kv_heads, geometry.max_kv_len, q.device)
+                splits = self.decode_splits(geometry.n_seqs, n_heads, n_kv_heads, head_dim, geometry.max_kv_len, q.device)
             return self.attention_mma(q, q_stride, out, k_pool, v_pool, block_table, geometry.seq_start,
                                       geometry.seq_qlen, geometry.seq_pos0, row_seq, geometry.n_seqs,
                                       geometry.max_q_len, n_heads, n_kv_heads, head_dim, window, scale, keys_mode,
@@ -256,15 +371,23 @@ class CudaOps:
             c = self._attn_counters[device] = torch.zeros((1 << 16,), dtype=torch.int32, device=device)
         return c
 
-    def decode_splits(self, n_seqs, n_heads, n_kv_heads, max_kv_len, device):
-        """CTAs that share one sequence's keys in a one-token step.  A split should have a few blocks of keys to
-        stream (its set-up and the merge of the splits cost about as much as two blocks), and all CTAs should
-        fit on the GPU at once (two of them fit an SM at head size 128)."""
-        sms = self._tc_buffers(device)[3]
+    def decode_splits(self, n_seqs, n_heads, n_kv_heads, head_dim, max_kv_len, device):
+        """CTAs that share one sequence's keys in a one-token step: as many as leave every CTA at least two blocks
+        of keys, up to the 8 of a thread-block cluster, as long as all clusters run at once (a second wave would
+        cost a whole CTA's set-up and merge again).  The device says how many clusters of a size it holds when it
+        is empty; SMs that the kernel before frees one by one are packed less well (measured on a B200: 32 clusters
+        of 8 ran in two waves although 33 fit), hence the margin of one half."""
         group = n_heads // n_kv_heads
-        base = n_seqs * n_kv_heads * ((group + 15) // 16)
+        base = n_seqs * n_kv_heads * ((group + 15) // 16)              # clusters of the launch
         blocks = (max_kv_len + 63) // 64
-        return int(max(1, min((2 * sms) // base, blocks // 4, 8)))     # up to 8: one thread-block cluster
+        fits = lib.family("attention_mma").cdll.attention_mma_clusters_at_once
+        for size in range(min(8, max(1, blocks // 2)), 1, -1):
+            key = (device, head_dim, size)
+            if key not in self._cluster_fit:
+                self._cluster_fit[key] = int(fits(head_dim, size))
+            if 2 * self._cluster_fit[key] >= 3 * base:
+                return size
+        return 1
 
     @staticmethod
     def attention_splits(rows, n_heads, max_kv_len):
@@ -332,6 +455,14 @@ def advance(*a, **k):
 
 def linear(*a, **k):
     return _backend.linear(*a, **k)
+
+
+def linear_norm(*a, **k):
+    return _backend.linear_norm(*a, **k)
+
+
+def qkv_rope_write(*a, **k):
+    return _backend.qkv_rope_write(*a, **k)
 
 
 def attention(*a, **k):

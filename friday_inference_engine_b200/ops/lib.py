@@ -11,6 +11,15 @@ from . import build
 
 P, I, F = c_void_p, c_int, c_float
 
+
+class GemmFusion(ctypes.Structure):
+    """csrc/gemm_tc_fusion.h, field for field."""
+    _fields_ = [("in_ssq", P), ("in_parts", I), ("in_width", F), ("in_eps", F),
+                ("norm_w", P), ("norm_out", P), ("out_ssq", P), ("norm_w_dtype", I),
+                ("row_seq", P), ("row_pos", P), ("denom", P), ("k_pool", P), ("v_pool", P), ("table", P),
+                ("rot", I), ("nq", I), ("nkv", I), ("hd", I), ("table_width", I), ("page", I), ("trace", P)]
+
+
 _SIGNATURES = {
     "rowwise": {
         "rowwise_embedding": [P, P, P, I, I, I, P],
@@ -26,6 +35,7 @@ _SIGNATURES = {
     "gemm_tc": {
         "gemm_tc": [P, P, P, I, P, I, P, I, I, I, I, I, I, P, c_longlong, P, I, P, I, I, I, I, P],
         "gemm_tc_act": [P, P, P, I, P, I, P, I, I, I, I, I, I, P, c_longlong, P, I, P, I, I, I, I, I, P],
+        "gemm_tc_fused": [P, P, P, I, P, I, P, I, I, I, I, I, I, P, c_longlong, P, I, P, I, I, I, I, I, P, P],
         "gemm_tc_plan": [I, I, I, I, I, I, I, P],
     },
     "attention_simt": {
@@ -34,6 +44,7 @@ _SIGNATURES = {
     "attention_mma": {
         "attention_mma": [P, I, P, P, P, P, I, I, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, I, P],
         "attention_mma_supports": [I, I],
+        "attention_mma_clusters_at_once": [I, I],
     },
     "sampling": {
         "sampling_sample": [P, I, I, I, P, P, P, c_ulonglong, P, P, P],

@@ -58,20 +58,24 @@ class GQAttention(Part):
         self.w_o = t["o_proj.weight"]
         self.b_o = t.get("o_proj.bias")
 
-    def forward(self, h, residual, ctx, cache):
+    chains_norm = True
+
+    def forward(self, h, residual, ctx, cache, then=None):
         nq, nkv, hd = self.n_heads, self.n_kv_heads, self.head_dim
-        qkv = ops.linear(h, self.w_qkv, bias=self.b_qkv)
         write = cache.write
+        pools = (cache.k_pool, cache.v_pool, cache.block_table) if write else (None, None, None)
         if getattr(self.position, "rotary", False):
-            denom, rot = self.position.denominators(), self.position.rotary_dim
+            qkv = ops.qkv_rope_write(h, self.w_qkv, self.b_qkv, ctx.row_seq, ctx.row_pos, self.position.denominators(),
+                                     self.position.rotary_dim, nq, nkv, hd, *pools, cache.page_size)
         else:                                   # another encoding: it changes q and k itself
+            qkv = ops.linear(h, self.w_qkv, bias=self.b_qkv)
             self.position.apply(qkv, ctx, nq, nkv, hd)
-            denom, rot = None, 0
-        if denom is not None or write:
-            ops.rope_kv_write(qkv, ctx.row_seq, ctx.row_pos, denom, rot, nq, nkv, hd,
-                              cache.k_pool if write else None, cache.v_pool if write else None,
-                              cache.block_table if write else None, cache.page_size)
+            if write:
+                ops.rope_kv_write(qkv, ctx.row_seq, ctx.row_pos, None, 0, nq, nkv, hd, *pools, cache.page_size)
         mixed = torch.empty((qkv.shape[0], nq * hd), dtype=qkv.dtype, device=qkv.device)
         ops.attention(qkv, qkv.stride(0), mixed, cache.k_pool, cache.v_pool, cache.block_table, cache.page_size,
                       ctx.row_seq, ctx.row_pos, nq, nkv, hd, self.window, self.scale, ctx)
-        return ops.linear(mixed, self.w_o, bias=self.b_o, residual=residual)
+        norm = then.as_rmsnorm() if then is not None else None
+        if norm is not None:
+            return ops.linear_norm(mixed, self.w_o, norm[0], norm[1], bias=self.b_o, residual=residual)
+        return ops.linear(mixed, self.w_o, bias=self.b_o, residual=residual), None

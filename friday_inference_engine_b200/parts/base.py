@@ -11,6 +11,15 @@ Categories and the interface each must offer:
   feed_forward   forward(h, residual, ctx) -> residual + f(h)               [rows, width]
   block          cache_request() (its mixer's), forward(x, ctx, cache) -> x
 
+Optional, for parts that end in a product: a mixer, feed-forward or block whose class sets
+`chains_norm = True` takes `then=` (the norm part that will be applied to its result, or
+None) and returns the pair (result, normed result or None); its input `h` may then be an
+`ops.DeferredNorm`, which products accept as it is and `ops.materialize` turns into a
+tensor.  A norm part that is a plain RMSNorm says so with `as_rmsnorm() -> (weight, eps)`,
+so that the product before it can begin it (ops.linear_norm).  A chaining block also takes
+`normed=` (its first norm already applied by the block before) and offers `first_norm`.
+Parts that do none of this are called with the plain interface above.
+
 `ctx` is the step's geometry (engine/step.py, StepContext): rows, n_seqs, row_seq and
 row_pos (int32 device tensors: the sequence of the step and the position of every row),
 seq_slots, q_lens, kv_lens, max_q_len, max_kv_len, and scratch(n_floats).  `cache` is
@@ -89,6 +98,10 @@ class StateRequest:
 class Part:
     category = None
     prefix = ""
+    chains_norm = False
+
+    def as_rmsnorm(self):
+        return None
 
     def __init__(self, env):
         self.env = env

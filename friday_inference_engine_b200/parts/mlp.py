@@ -32,5 +32,11 @@ class SwiGLU(Part):
         self.w_gate_up = torch.stack([w.to(wdt) for w in ws], dim=1).reshape(2 * self.inner, -1).contiguous()
         self.w_down = t["down_proj.weight"]
 
-    def forward(self, h, residual, ctx):
-        return ops.linear(ops.linear_swiglu(h, self.w_gate_up), self.w_down, residual=residual)
+    chains_norm = True
+
+    def forward(self, h, residual, ctx, then=None):
+        inner = ops.linear_swiglu(h, self.w_gate_up)
+        norm = then.as_rmsnorm() if then is not None else None
+        if norm is not None:
+            return ops.linear_norm(inner, self.w_down, norm[0], norm[1], residual=residual)
+        return ops.linear(inner, self.w_down, residual=residual), None

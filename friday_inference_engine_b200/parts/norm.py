@@ -19,3 +19,6 @@ class RMSNorm(Part):
 
     def forward(self, x):
         return ops.rmsnorm(x, self.tensors["weight"], self.eps)
+
+    def as_rmsnorm(self):
+        return self.tensors["weight"], self.eps

@@ -79,6 +79,18 @@ class TorchOps:
             return out
         return y
 
+    def linear_norm(self, x, weight, norm_weight, eps, bias=None, residual=None):
+        out = self.linear(x, weight, bias=bias, residual=residual)
+        return out, self.rmsnorm(out, norm_weight, eps)
+
+    def qkv_rope_write(self, x, weight, bias, row_seq, row_pos, denom, rotary_dim, n_heads, n_kv_heads, head_dim,
+                       k_pool=None, v_pool=None, block_table=None, page_size=0):
+        qkv = self.linear(x, weight, bias=bias)
+        if denom is not None or k_pool is not None:
+            self.rope_kv_write(qkv, row_seq, row_pos, denom, rotary_dim, n_heads, n_kv_heads, head_dim, k_pool, v_pool,
+                               block_table, page_size)
+        return qkv
+
     def attention(self, q, q_stride, out, k_pool, v_pool, block_table, page_size, row_seq, row_pos, n_heads,
                   n_kv_heads, head_dim, window, scale, geometry):
         rows = out.shape[0]

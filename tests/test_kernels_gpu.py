@@ -407,3 +407,104 @@ def partial_last_wave(m, n, k):
     err = float((io.double() - ref).abs().max() / ref.abs().max())
     assert err <= 0.01, err
     ops.backend().check_status()
+
+
+# ---------------------------------------------------------------- work fused into the tensor-core product's ends
+def denominators(theta, rot):
+    return torch.from_numpy(np.power(np.float32(theta), np.float32(2.0) * np.arange(rot // 2, dtype=np.float32)
+                                     / np.float32(rot)).astype(np.float32)).to(DEV)
+
+
+@pytest.mark.parametrize("m,nq,nkv,hd,rot,k", [(1, 4, 2, 32, 32, 64), (8, 28, 4, 128, 128, 3584), (16, 2, 1, 64, 32, 512),
+                                                 (5, 6, 1, 16, 16, 1024), (9, 2, 3, 128, 64, 200)])
+def test_gemm_with_rotation_and_cache_write_in_its_epilogue(m, nq, nkv, hd, rot, k, monkeypatch):
+    """The fused epilogue against the product followed by the rotation kernel: same bits in q, k, v and in the
+    cache; against the plain rotation for the values."""
+    n = (nq + 2 * nkv) * hd
+    x, w, b = rnd((m, k), torch.bfloat16, 70, 0.5), rnd((n, k), torch.bfloat16, 71, 0.1), rnd((n,), torch.bfloat16, 72)
+    row_seq = torch.tensor([i % 2 for i in range(m)], dtype=torch.int32, device=DEV)
+    if m > 2:
+        row_seq[2] = -1                                                   # a padding row
+    row_pos = torch.tensor([60 + 3 * i for i in range(m)], dtype=torch.int32, device=DEV)
+    table = torch.tensor([[3, 1, 7, 5], [2, 0, 6, 4]], dtype=torch.int32, device=DEV)
+    denom = denominators(1e6, rot)
+    results = []
+    for fuse in ("1", "0"):
+        monkeypatch.setenv("FRIDAY_FUSE", fuse)
+        kp = torch.zeros((8, PAGE, nkv, hd), dtype=torch.bfloat16, device=DEV)
+        vp = torch.zeros_like(kp)
+        before = ops.lib.launch_count()
+        qkv = ops.qkv_rope_write(x, w, b, row_seq, row_pos, denom, rot, nq, nkv, hd, kp, vp, table, PAGE)
+        assert ops.lib.launch_count() - before == (1 if fuse == "1" else 2), "fused: one launch; else two"
+        results.append((qkv, kp, vp))
+    ops.backend().check_status()
+    live = (row_seq >= 0).cpu().numpy()
+    for got, want, what in zip(results[0], results[1], ("q, k, v", "key cache", "value cache")):
+        if what == "q, k, v":
+            got, want = got[torch.from_numpy(live).to(DEV)], want[torch.from_numpy(live).to(DEV)]
+        assert torch.equal(got, want), what
+    plain = f64(x) @ f64(w).T + f64(b)
+    plain = np.asarray(f64(torch.from_numpy(plain).to(torch.bfloat16))).reshape(m, nq + 2 * nkv, hd)
+    for r in range(m):
+        if not live[r]:
+            continue
+        ref = plain[r].copy()
+        ref[: nq + nkv, :rot] = pm.rope_neox(plain[r:r + 1, : nq + nkv, :rot], [int(row_pos[r])], 1e6)[0]
+        close(results[0][0][r].reshape(nq + 2 * nkv, hd), ref, torch.bfloat16, "row %d" % r)
+    # no rotation and no cache: the product alone
+    qkv = ops.qkv_rope_write(x, w, b, row_seq, row_pos, None, 0, nq, nkv, hd)
+    assert torch.equal(qkv, ops.linear(x, w, bias=b))
+
+
+@pytest.mark.parametrize("m,n,k,k2", [(1, 128, 64, 64), (8, 3584, 3584, 1024), (16, 256, 18944, 512), (7, 640, 200, 136)])
+def test_gemm_begins_a_norm_that_the_next_gemm_finishes(m, n, k, k2, monkeypatch):
+    x, w = rnd((m, k), torch.bfloat16, 80, 0.5), rnd((n, k), torch.bfloat16, 81, 0.05)
+    res = rnd((m, n), torch.bfloat16, 82, 2.0)
+    g = rnd((n,), torch.bfloat16, 83) + 1.0
+    eps = 1e-5
+    out, h = ops.linear_norm(x, w, g, eps, residual=res)
+    assert isinstance(h, ops.DeferredNorm), "few bf16 rows and whole tiles: the norm is begun in the epilogue"
+    assert torch.equal(out, ops.linear(x, w, residual=res)), "the product itself is unchanged"
+    normed = pm.rms_norm(f64(out), f64(g), eps)
+    close(h.materialize(), normed, torch.bfloat16, "materialised")
+    # the sums of squares: shares of 128 columns each
+    ssq = (f64(out) ** 2).reshape(m, n // 128, 128).sum(-1).T
+    close(h.ssq, ssq, torch.float32, "partial sums of squares", fp32_tol=1e-5)
+    # consumers: a plain product with bias (bf16 and fp32 output), the gated one, and one that begins the next norm
+    w2, b2 = rnd((k2 * 2, n), torch.bfloat16, 84, 0.05), rnd((k2 * 2,), torch.bfloat16, 85)
+    ref = normed @ f64(w2).T
+    close(ops.linear(h, w2, bias=b2), ref + f64(b2), torch.bfloat16, "consumer with bias")
+    close(ops.linear(h, w2, out_dtype=torch.float32), ref, torch.bfloat16, "consumer with fp32 output", bf16_rel=0.01)
+    close(ops.linear_swiglu(h, w2), pm.swiglu(ref[:, 0::2], ref[:, 1::2]), torch.bfloat16, "gated consumer")
+    if (2 * k2) % 128 == 0:
+        g2 = rnd((2 * k2,), torch.bfloat16, 86) + 1.0
+        out2, h2 = ops.linear_norm(h, w2, g2, eps)
+        assert isinstance(h2, ops.DeferredNorm)
+        close(out2, ref, torch.bfloat16, "consumer that begins a norm")
+        close(h2.materialize(), pm.rms_norm(f64(out2), f64(g2), eps), torch.bfloat16, "second norm")
+    # a consumer that cannot finish the norm itself (a k that is no multiple of 8 is not for the tensor cores;
+    # here: fp32 weights) gets the rows from the norm's own kernel
+    close(ops.linear(h, w2.float()), ref, torch.bfloat16, "consumer on the CUDA cores")
+    # many rows: the norm's own kernel runs and a tensor comes back
+    xs = rnd((40, k), torch.bfloat16, 87, 0.5)
+    out3, h3 = ops.linear_norm(xs, w, g, eps)
+    assert torch.is_tensor(h3)
+    close(h3, pm.rms_norm(f64(out3), f64(g), eps), torch.bfloat16, "unfused norm")
+    monkeypatch.setenv("FRIDAY_FUSE", "0")
+    assert torch.is_tensor(ops.linear_norm(x, w, g, eps, residual=res)[1])
+    ops.backend().check_status()
+
+
+def test_norm_and_rotation_fused_into_split_k_products():
+    """Shapes whose k is split over several CTAs: the last one to arrive runs the fused epilogue."""
+    m, nq, nkv, hd, k = 4, 2, 1, 128, 4096
+    n = (nq + 2 * nkv) * hd
+    x, w = rnd((m, k), torch.bfloat16, 90, 0.5), rnd((n, k), torch.bfloat16, 91, 0.05)
+    plan = np.zeros(5, dtype=np.int64)
+    ops.lib.family("gemm_tc").call("gemm_tc_plan", m, n, k, 148, -1, -1, -1, plan.ctypes.data)
+    assert plan[0] == 1 and plan[2] > 1, "this shape is meant to be split along k"
+    g = rnd((n,), torch.bfloat16, 92) + 1.0
+    out, h = ops.linear_norm(x, w, g, 1e-6)
+    assert isinstance(h, ops.DeferredNorm) and torch.equal(out, ops.linear(x, w))
+    w2 = rnd((256, n), torch.bfloat16, 93, 0.05)
+    close(ops.linear(h, w2), pm.rms_norm(f64(out), f64(g), 1e-6) @ f64(w2).T, torch.bfloat16, "split-k consumer")

@@ -77,10 +77,23 @@ def test_rotary_part_makes_the_reference_table():
     assert part.rotary_dim == 32 and d.dtype == np.float32
 
 
+def chained_norm(dtype, width, seed):
+    """A norm part and a function that measures what a part returned beside its result when told that this norm
+    follows: that norm of the result, as a tensor or as rows whose norm the next product finishes."""
+    from friday_inference_engine_b200 import ops
+    norm = build_part("norm", PartSpec("rmsnorm", {"eps": 1e-5}), env(width, dtype))
+    g = fill(norm, seed)["weight"]
+    return norm, lambda x, normed: np.abs(ops.materialize(normed).double().cpu().numpy()
+                                          - pm.rms_norm(x.double().cpu().numpy(), g, 1e-5)).max()
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("window", [None, 10])
-def test_attention_part(dtype, window):
-    nq, nkv, hd, width, n = 6, 2, 48, 120, 90
+@pytest.mark.parametrize("nq,nkv,hd,width,n", [(6, 2, 48, 120, 90), (4, 2, 64, 256, 9)])
+def test_attention_part(dtype, window, nq, nkv, hd, width, n):
+    """The second shape is a step of few rows whose sizes let rotation, cache write and the following norm ride in
+    the products' epilogues (bf16); the first goes through the kernels of their own."""
+    from friday_inference_engine_b200 import ops
     spec = PartSpec("gqa_attention", {"n_heads": nq, "n_kv_heads": nkv, "head_dim": hd, "window": window,
                                       "position": PartSpec("rotary_neox", {"theta": 5e4, "head_dim": hd})})
     part = build_part("mixer", spec, env(width, dtype))
@@ -88,7 +101,9 @@ def test_attention_part(dtype, window):
     one = OneSeq(part.cache_request(), n, dtype)
     h = torch.randn(n, width).to(dtype).to(DEV)
     res = torch.randn(n, width).to(dtype).to(DEV)
-    got = part.forward(h, res, one.ctx, one.view).double().cpu().numpy()
+    out, nothing = part.forward(h, res, one.ctx, one.view)
+    assert nothing is None
+    got = out.double().cpu().numpy()
     hn = h.double().cpu().numpy()
     q = pm.linear(hn, w["q_proj.weight"], w["q_proj.bias"]).reshape(n, nq, hd)
     k = pm.linear(hn, w["k_proj.weight"], w["k_proj.bias"]).reshape(n, nkv, hd)
@@ -98,20 +113,42 @@ def test_attention_part(dtype, window):
     ref = res.double().cpu().numpy() + pm.linear(o, w["o_proj.weight"])
     tol = 2e-5 if dtype == torch.float32 else 3e-2
     assert np.abs(got - ref).max() <= tol * np.abs(ref).max()
+    # told which norm follows, it returns that norm of its result as well
+    norm, err = chained_norm(dtype, width, 9)
+    out2, normed = part.forward(h, res, one.ctx, one.view, then=norm)
+    assert torch.equal(out2, out) and normed is not None
+    fused = dtype == torch.bfloat16 and n <= 16 and width % 128 == 0
+    assert isinstance(normed, ops.DeferredNorm) == fused
+    assert err(out2, normed) <= (2e-5 if dtype == torch.float32 else 3e-2) * 4
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_feed_forward_part(dtype):
-    part = build_part("feed_forward", PartSpec("swiglu", {"inner": 200}), env(120, dtype))
+@pytest.mark.parametrize("width,inner,n", [(120, 200, 7), (256, 384, 5)])
+def test_feed_forward_part(dtype, width, inner, n):
+    from friday_inference_engine_b200 import ops
+    part = build_part("feed_forward", PartSpec("swiglu", {"inner": inner}), env(width, dtype))
     w = fill(part, 2)
-    h = torch.randn(7, 120).to(dtype).to(DEV)
-    res = torch.randn(7, 120).to(dtype).to(DEV)
+    h = torch.randn(n, width).to(dtype).to(DEV)
+    res = torch.randn(n, width).to(dtype).to(DEV)
     hn = h.double().cpu().numpy()
     ref = res.double().cpu().numpy() + pm.linear(
         pm.swiglu(pm.linear(hn, w["gate_proj.weight"]), pm.linear(hn, w["up_proj.weight"])), w["down_proj.weight"])
-    got = part.forward(h, res, None).double().cpu().numpy()
+    out, nothing = part.forward(h, res, None)
+    assert nothing is None
     tol = 2e-5 if dtype == torch.float32 else 3e-2
-    assert np.abs(got - ref).max() <= tol * np.abs(ref).max()
+    assert np.abs(out.double().cpu().numpy() - ref).max() <= tol * np.abs(ref).max()
+    norm, err = chained_norm(dtype, width, 9)
+    out2, normed = part.forward(h, res, None, then=norm)
+    assert torch.equal(out2, out)
+    assert isinstance(normed, ops.DeferredNorm) == (dtype == torch.bfloat16 and width % 128 == 0)
+    assert err(out2, normed) <= tol * 4
+    # and it takes such rows as its input: the norm is finished inside its first product
+    if isinstance(normed, ops.DeferredNorm):
+        hn2 = pm.rms_norm(out2.double().cpu().numpy(), norm.tensors["weight"].double().cpu().numpy(), 1e-5)
+        ref2 = out2.double().cpu().numpy() + pm.linear(
+            pm.swiglu(pm.linear(hn2, w["gate_proj.weight"]), pm.linear(hn2, w["up_proj.weight"])), w["down_proj.weight"])
+        out3, _ = part.forward(normed, out2, None)
+        assert np.abs(out3.double().cpu().numpy() - ref2).max() <= tol * np.abs(ref2).max()
 
 
 # ---------------------------------------------------------------------------------------
