@@ -113,44 +113,13 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int seq = blockIdx.z, kvh = blockIdx.y;
     // The page table is written by copies from the host, never by a kernel, so it may be read before the
-    // kernel before this one has finished; everything else waits.
+    // kernel before this one has finished; so may everything that is arithmetic only.  The rest waits.
     if (tid < p.table_width) s_pages[tid] = p.block_table[(size_t)seq * p.table_width + tid];
-    fr_pdl_wait();
-    fr_pdl_launch();
-    mark(p, 1);
     const int split = blockIdx.x % p.splits, tile = blockIdx.x / p.splits;
     const int G = p.nq / p.nkv;
-    const int q_len = p.seq_qlen[seq], q_start = p.seq_start[seq], pos0 = p.seq_pos0[seq];
-    const int n_rows = q_len * G;
     const int r0 = tile * ROWS_CTA;
-    if (r0 >= n_rows) return;
-    const bool live = p.seq_live == nullptr || p.seq_live[q_start] >= 0;
-
-    // Range of key blocks for this CTA.
-    const int t_first = r0 / G, t_last = min((r0 + ROWS_CTA - 1) / G, q_len - 1);
-    const int pos_hi = pos0 + t_last;                 // the farthest key any row of the CTA may see
-    const int lo_min = p.window > 0 ? max(0, pos0 + t_first - p.window + 1) : 0;
-    int kb_begin = lo_min / BLOCK_N, kb_end = pos_hi / BLOCK_N;     // inclusive
-    if (p.splits > 1) {
-        const int n = kb_end - kb_begin + 1, per = (n + p.splits - 1) / p.splits;
-        kb_begin += split * per;
-        kb_end = min(kb_begin + per - 1, kb_end);
-    }
-    if (!live) kb_end = kb_begin - 1;                 // nothing to read: the output is zero
-
     const int* table = p.block_table + (size_t)seq * p.table_width;
     const size_t kv_row = (size_t)p.nkv * HD;         // elements between consecutive keys of a page
-
-    auto load_q = [&]() {
-        for (int c = tid; c < ROWS_CTA * CHUNKS; c += WARPS * 32) {
-            const int r = c / CHUNKS, ch = c - r * CHUNKS;
-            const int rr = r0 + r;
-            const bool ok = rr < n_rows;
-            const int t = ok ? rr / G : 0, g = ok ? rr - t * G : 0;
-            const bf16* src = p.q + (size_t)(q_start + t) * p.q_stride + (size_t)(kvh * G + g) * HD + ch * 8;
-            cp_async16((uint32_t)__cvta_generic_to_shared(s_q + r * ROW_BYTES + ch * 16), src, ok ? 16 : 0);
-        }
-    };
     // Which pieces of a K/V block this thread copies is the same for every block: row, source offset and
     // destination offset are worked out once.
     constexpr int PIECES = BLOCK_N * CHUNKS / (WARPS * 32);
@@ -164,11 +133,47 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
         piece_dst[j] = r * ROW_BYTES + ch * 16;
     }
     const uint32_t k_smem = (uint32_t)__cvta_generic_to_shared(s_k), v_smem = (uint32_t)__cvta_generic_to_shared(s_v);
+    // The step's geometry (rows, positions, which sequences have ended) is written before the step's first kernel
+    // starts, by copies from the host or by the step before, and every step begins with kernels that wait for
+    // their predecessor before they let a dependent launch (common.cuh): it, too, is read ahead of the wait.
+    const int q_len = p.seq_qlen[seq], q_start = p.seq_start[seq], pos0 = p.seq_pos0[seq];
+    const int n_rows = q_len * G;
+    const bool live = p.seq_live == nullptr || p.seq_live[q_start] >= 0;
+    __syncthreads();                                   // s_pages
+
+    fr_pdl_wait();
+    fr_pdl_launch();
+    mark(p, 1);
+    if (r0 >= n_rows) return;
+
+    // Range of key blocks for this CTA.
+    const int t_first = r0 / G, t_last = min((r0 + ROWS_CTA - 1) / G, q_len - 1);
+    const int pos_hi = pos0 + t_last;                 // the farthest key any row of the CTA may see
+    const int lo_min = p.window > 0 ? max(0, pos0 + t_first - p.window + 1) : 0;
+    int kb_begin = lo_min / BLOCK_N, kb_end = pos_hi / BLOCK_N;     // inclusive
+    if (p.splits > 1) {
+        const int n = kb_end - kb_begin + 1, per = (n + p.splits - 1) / p.splits;
+        kb_begin += split * per;
+        kb_end = min(kb_begin + per - 1, kb_end);
+    }
+    if (!live) kb_end = kb_begin - 1;                 // nothing to read: the output is zero
+
+    auto load_q = [&]() {
+        for (int c = tid; c < ROWS_CTA * CHUNKS; c += WARPS * 32) {
+            const int r = c / CHUNKS, ch = c - r * CHUNKS;
+            const int rr = r0 + r;
+            const bool ok = rr < n_rows;
+            const int t = ok ? rr / G : 0, g = ok ? rr - t * G : 0;
+            const bf16* src = p.q + (size_t)(q_start + t) * p.q_stride + (size_t)(kvh * G + g) * HD + ch * 8;
+            cp_async16((uint32_t)__cvta_generic_to_shared(s_q + r * ROW_BYTES + ch * 16), src, ok ? 16 : 0);
+        }
+    };
     auto load_kv = [&](int kb, int buf) {
         const int page = kb < WARPS * 32 ? s_pages[kb] : table[kb];
         const bf16* kbase = p.k_pool + ((size_t)page * BLOCK_N) * kv_row + (size_t)kvh * HD;
         const bf16* vbase = p.v_pool + ((size_t)page * BLOCK_N) * kv_row + (size_t)kvh * HD;
-        const int valid = pos_hi - kb * BLOCK_N + 1;                        // rows of the block that are needed
+        // rows of the block that are needed; none of a page that the table does not name (a sequence that has ended)
+        const int valid = page >= 0 ? pos_hi - kb * BLOCK_N + 1 : 0;
 #pragma unroll
         for (int j = 0; j < PIECES; ++j) {
             const bool ok = piece_row[j] < valid;                           // beyond the last needed key: zeros
@@ -203,7 +208,6 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
         for (int e = 0; e < 4; ++e) o[d][e] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
-    __syncthreads();                                   // s_pages
     load_q();
 #pragma unroll
     for (int st = 0; st < NS - 1; ++st) {

@@ -86,6 +86,12 @@ __device__ __forceinline__ float fr_warp_max(float v) {
 // may write or read; fr_pdl_launch() once the next kernel may be scheduled.  A kernel that
 // follows one of these in a stream but was launched the ordinary way is fully serialised,
 // as always.  FRIDAY_PDL=0 in the environment switches the launch attribute off.
+//
+// What may be read ahead of the wait: memory that only copies from the host write (page tables), and the
+// geometry of the step (rows, positions, ended sequences), which is final before the step's first kernel
+// starts.  The latter holds because the row-wise kernels that open every step (embedding, the first norm)
+// wait before they let their dependents launch: whatever runs after them was launched after the step before
+// had finished.  Kernels that let dependents launch before their own wait (the products) never open a step.
 __device__ __forceinline__ void fr_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void fr_pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

@@ -489,8 +489,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             if (et == 0) mark(p, 6);
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + a * BN;
-            // partial tiles are laid out [chunk of 16 columns][row][16]: a warp's 32 rows are 2 KB in one piece
-            float* part = item.nseg > 1 ? p.ws + (size_t)item.part * TILE_P * BN + (size_t)i_local * 16 : nullptr;
+            // partial tiles are laid out [chunk of 16 columns][quarter of the chunk][row][4]: what a warp stores or
+            // loads at a time is 512 bytes in one piece
+            float* part = item.nseg > 1 ? p.ws + (size_t)item.part * TILE_P * BN + (size_t)i_local * 4 : nullptr;
 #pragma unroll 1
             for (int c = 0; c < BN / 16; ++c) {
                 uint32_t r[16];
@@ -506,8 +507,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 } else {
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
-                        ((float4*)(part + (size_t)c * TILE_P * 16))[j] =
-                            make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                        *(float4*)(part + ((size_t)c * 4 + j) * TILE_P * 4) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
                 }
             }
             tc_fence_before();
@@ -530,7 +530,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (flags[0]) {
                     if (et == 0) mark(p, 8);
-                    const float* mine = p.ws + (size_t)i_local * 16;
+                    const float* mine = p.ws + (size_t)i_local * 4;
 #pragma unroll 1
                     for (int c = 0; c < BN / 16; ++c) {
                         float v[16];
@@ -542,10 +542,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
 #pragma unroll
                             for (int s = 0; s < 8; ++s) {
                                 if (s0 + s < item.nseg) {
-                                    const float4* src = (const float4*)(mine + (size_t)work.contributor(item, s0 + s) * TILE_P * BN +
-                                                                        (size_t)c * TILE_P * 16);
+                                    const float* src = mine + (size_t)work.contributor(item, s0 + s) * TILE_P * BN + (size_t)c * TILE_P * 16;
 #pragma unroll
-                                    for (int j = 0; j < 4; ++j) x[s][j] = __ldcg(src + j);
+                                    for (int j = 0; j < 4; ++j) x[s][j] = __ldcg((const float4*)(src + (size_t)j * TILE_P * 4));
                                 }
                             }
 #pragma unroll
@@ -656,12 +655,14 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmParams& p, in
 // and plan[4] = counters needed.  bn / splits / swap < 0 let the heuristics decide.
 FR_EXPORT int gemm_tc_plan(int m, int n, int k, int sm_count, int swap, int bn, int splits, long long* plan) {
     // Measured on B200 at the sizes of a 7B model (k = 3584 or 18944, n from 3584 to 152064):
-    //  * up to 16 rows: weights on the M side, the rows as a 16-wide N tile; k split until the SMs are busy;
-    //  * 17 to 128 rows: rows on the M side (one tile, partly empty) and narrow weight tiles, so that about a
+    //  * up to 64 rows: weights on the M side, the rows as an N tile of 16, 32 or 64; k split until the SMs are
+    //    busy (at 64 rows: 16 / 15 / 35 us for the qkv, output and down products against 21 / 20 / 40 us the other
+    //    way round; at 32 rows 13 / 12 / 31 against 21 / 20 / 39);
+    //  * 65 to 128 rows: rows on the M side (one tile, partly empty) and narrow weight tiles, so that about a
     //    hundred CTAs stream weights without splitting k; very long k is split four ways over wide tiles instead;
     //  * more rows: 128 x 256 tiles.
     const int kb_total = (k + TILE_K - 1) / TILE_K;
-    if (swap < 0) swap = m <= 16 ? 1 : 0;
+    if (swap < 0) swap = m <= 64 ? 1 : 0;
     const int q_rows = swap ? m : n, p_rows = swap ? n : m;
     const bool skinny = !swap && m <= TILE_P;
     if (bn <= 0) {

@@ -173,10 +173,10 @@ class CudaOps:
         fusion.in_width, fusion.in_eps = float(deferred.scaled.shape[1]), deferred.eps
         return fusion
 
-    def _few_rows_tile_ok(self, x, weight, out, residual):
+    def _few_rows_tile_ok(self, x, weight, out, residual, max_rows):
         """What the fused epilogues of the tensor-core product need: a one-token step's few rows, bf16, whole
         tiles of 128 output columns."""
-        return (fusion_enabled() and out.dtype == torch.bfloat16 and x.shape[0] <= 16 and weight.shape[0] % 128 == 0
+        return (fusion_enabled() and out.dtype == torch.bfloat16 and x.shape[0] <= max_rows and weight.shape[0] % 128 == 0
                 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0
                 and (residual is None or residual.data_ptr() % 16 == 0)
                 and self.tensor_core_ok(x, weight, out, residual))
@@ -191,7 +191,7 @@ class CudaOps:
         rows, n = xt.shape[0], weight.shape[0]
         if xt.dim() == 2 and weight.dim() == 2 and xt.shape[1] == weight.shape[1] and norm_weight.numel() == n:
             out = torch.empty((rows, n), dtype=xt.dtype, device=xt.device)
-            if self._few_rows_tile_ok(xt, weight, out, residual) and norm_weight.is_contiguous():
+            if self._few_rows_tile_ok(xt, weight, out, residual, 64) and norm_weight.is_contiguous():
                 if residual is not None:
                     assert residual.shape == out.shape and residual.dtype == out.dtype and residual.stride() == out.stride()
                 scaled = torch.empty_like(out)
@@ -216,7 +216,7 @@ class CudaOps:
                 and head_dim % 8 == 0 and n == (n_heads + 2 * n_kv_heads) * head_dim \
                 and (denom is None or rotary_dim % 16 == 0):
             out = torch.empty((xt.shape[0], n), dtype=xt.dtype, device=xt.device)
-            if self._few_rows_tile_ok(xt, weight, out, None) and (not write or k_pool.dtype == torch.bfloat16):
+            if self._few_rows_tile_ok(xt, weight, out, None, 16) and (not write or k_pool.dtype == torch.bfloat16):
                 _need_cuda(xt, weight, bias, row_seq, row_pos, denom, k_pool, v_pool, block_table)
                 fusion = self._fusion_in(deferred, lib.GemmFusion())
                 fusion.row_seq, fusion.row_pos, fusion.denom = _ptr(row_seq), _ptr(row_pos), _ptr(denom)

@@ -456,7 +456,8 @@ def test_gemm_with_rotation_and_cache_write_in_its_epilogue(m, nq, nkv, hd, rot,
     assert torch.equal(qkv, ops.linear(x, w, bias=b))
 
 
-@pytest.mark.parametrize("m,n,k,k2", [(1, 128, 64, 64), (8, 3584, 3584, 1024), (16, 256, 18944, 512), (7, 640, 200, 136)])
+@pytest.mark.parametrize("m,n,k,k2", [(1, 128, 64, 64), (8, 3584, 3584, 1024), (16, 256, 18944, 512), (7, 640, 200, 136),
+                                      (33, 384, 1024, 192), (64, 3584, 512, 64)])
 def test_gemm_begins_a_norm_that_the_next_gemm_finishes(m, n, k, k2, monkeypatch):
     x, w = rnd((m, k), torch.bfloat16, 80, 0.5), rnd((n, k), torch.bfloat16, 81, 0.05)
     res = rnd((m, n), torch.bfloat16, 82, 2.0)
@@ -486,7 +487,7 @@ def test_gemm_begins_a_norm_that_the_next_gemm_finishes(m, n, k, k2, monkeypatch
     # here: fp32 weights) gets the rows from the norm's own kernel
     close(ops.linear(h, w2.float()), ref, torch.bfloat16, "consumer on the CUDA cores")
     # many rows: the norm's own kernel runs and a tensor comes back
-    xs = rnd((40, k), torch.bfloat16, 87, 0.5)
+    xs = rnd((80, k), torch.bfloat16, 87, 0.5)
     out3, h3 = ops.linear_norm(xs, w, g, eps)
     assert torch.is_tensor(h3)
     close(h3, pm.rms_norm(f64(out3), f64(g), eps), torch.bfloat16, "unfused norm")
