@@ -203,6 +203,75 @@ def timeline(eng, batch):
     return 0
 
 
+def cta_trace(eng, batch):
+    """Where the CTAs of a decode step's products and attention kernels spend their time: %globaltimer stamps that
+    the kernels write when given a trace buffer (csrc/gemm_tc_fusion.h part 4, attention_mma_set_trace), read after
+    one replay of the captured step.  Times in us from the step's first stamp; min / median / max over CTAs."""
+    import numpy as np
+    import torch
+    from friday_inference_engine_b200 import ops
+    from friday_inference_engine_b200.ops import lib
+    layers = len(eng.model.layers)
+    prompts = random_prompts(batch, PROMPT, eng.vocab_size, 1)
+    slots = [eng.alloc_slot() for _ in prompts]
+    for lo in range(0, batch, 8):
+        eng.step(slots[lo:lo + 8], prompts[lo:lo + 8], [[]] * len(slots[lo:lo + 8]))
+    dec = eng.decoder(slots, [p[-1] for p in prompts])
+    dec.step()                                                # eager: sizes scratch, builds libraries
+    be = ops.backend()
+    n_gemm = 4 * layers + 1
+    be.trace = torch.zeros((n_gemm, 148, 16), dtype=torch.int64, device="cuda:0")
+    be.trace_next = 0
+    attn = torch.zeros((8192, 8), dtype=torch.int64, device="cuda:0")
+    set_trace = lib.family("attention_mma").declare("attention_mma_set_trace", [lib.P])
+    set_trace(attn.data_ptr())
+    dec.step()                                                # captured with the trace pointers in place
+    for _ in range(5):
+        dec.step()
+    torch.cuda.synchronize()
+    be.trace.zero_()
+    attn.zero_()
+    dec.step()
+    torch.cuda.synchronize()
+    set_trace(None)
+    g = be.trace.cpu().numpy().astype(np.float64)
+    a = attn.cpu().numpy().astype(np.float64)
+    be.trace = None
+    g[g == 0] = np.nan
+    a[a == 0] = np.nan
+    t0 = np.nanmin(g)
+
+    def stats(col):
+        col = (col - t0) / 1000.0
+        return "%6.1f %6.1f %6.1f" % (np.nanmin(col), np.nanmedian(col), np.nanmax(col))
+
+    names = ["qkv", "o", "gate_up", "down"]
+    print("products: CTAs | set-up done | predecessor finished | first operands landed | last accumulator complete | "
+          "last tile done   (min median max, us)")
+    for i in range(n_gemm):
+        name = names[i % 4] + " %d" % (i // 4) if i < 4 * layers else "head"
+        print("%-10s %4d | %s | %s | %s | %s | %s" % (name, int(np.sum(~np.isnan(g[i, :, 0]))), stats(g[i, :, 1]),
+                                                      stats(g[i, :, 3]), stats(g[i, :, 4]), stats(g[i, :, 6]), stats(g[i, :, 7])))
+    print("CTAs that sum a tile's split-k partial tiles, us after their own last accumulator: knows it is last | "
+          "partial tiles summed | tile transposed | tile written   (median, max)")
+    for i in range(n_gemm):
+        sel = ~np.isnan(g[i, :, 8])
+        if sel.any():
+            rel = (g[i, sel][:, [8, 10, 11, 12]] - g[i, sel][:, [6]]) / 1000.0
+            print("%-10s %4d | " % (names[i % 4] + " %d" % (i // 4), sel.sum())
+                  + " | ".join("%5.2f %5.2f" % (np.nanmedian(rel[:, j]), np.nanmax(rel[:, j])) for j in range(4)))
+    # the attention launch that wrote last is the last layer's; its predecessor is that layer's qkv product
+    done = np.nanmax(g[4 * (layers - 1), :, 7])
+    live = ~np.isnan(a[:, 0])
+    print("attention of the last layer: %d CTAs; us after the qkv product's last tile (min median max); the o product's "
+          "predecessor finished at %.1f" % (live.sum(), (np.nanmin(g[4 * (layers - 1) + 1, :, 3]) - done) / 1000.0))
+    for j, what in enumerate(["kernel entry", "predecessor finished", "loads issued", "first block landed", "blocks done",
+                              "warps merged", "cluster barrier passed", "splits merged"]):
+        col = (a[live, j] - done) / 1000.0
+        print("  %-24s %6.1f %6.1f %6.1f" % (what, np.nanmin(col), np.nanmedian(col), np.nanmax(col)))
+    return 0
+
+
 def reference_arm():
     why = ("the reference is a C++/CMake program with no Python packaging (pip install of its tree fails: "
            "no setup.py or pyproject.toml), has no bf16 or batched path and targets sm_86 with GGUF k-quant weights")
@@ -221,6 +290,8 @@ def main():
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64, prefill and e2e")
     ap.add_argument("--prefill-only", action="store_true", help="time the 2,048-token prompt only (for profiling)")
     ap.add_argument("--slots", type=int, default=64, help="sequences the cache is sized for (smaller for profiling)")
+    ap.add_argument("--cta-trace", action="store_true",
+                    help="print when the CTAs of a decode step's products and attention reach the points they stamp")
     ap.add_argument("--timeline", action="store_true",
                     help="print the kernels of one decode step as they run inside the captured graph (torch profiler)")
     args = ap.parse_args()
@@ -247,6 +318,8 @@ def main():
 
     if args.timeline:
         return timeline(eng, args.batch)
+    if args.cta_trace:
+        return cta_trace(eng, args.batch)
     if args.prefill_only:
         ms_pre = time_prefill(eng, max(1, args.warmup - 2), max(1, args.steps))
         print(json.dumps({"prefill_ms": round(ms_pre, 3), "layers_run": layers}))

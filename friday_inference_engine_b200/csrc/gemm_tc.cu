@@ -67,6 +67,7 @@ struct GemmParams {
     int* counters;      // [tiles], zero between launches
     int* status;        // 0, or a code when a wait gave up
     int p_rows, q_rows, ldo, out_dtype, bias_dtype, swapped;
+    int bn;             // rows of Q per tile: the kernel's BN, or any multiple of 16 below it in the widest instance
     int act;            // 1: the product's columns are (gate, up) pairs; out gets silu(gate) * up, half as wide
     int tiles_p, tiles_q, splits, kb_total, kb_per;
     // Work decomposition.  The first dp_tiles tiles are cut into `splits` equal k ranges each and dealt out round
@@ -136,6 +137,9 @@ template <int BN, int STAGES>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                const GemmParams p) {
+    // The widest instance takes any tile width up to its own (a multiple of 16): strides in shared and tensor memory
+    // stay those of the full width, the boxes of the loads, the instruction and the loops follow p.bn.
+    const int bn = BN == 256 ? p.bn : BN;
     constexpr int Q_BYTES = BN * TILE_K * 2;
     constexpr int STAGE_BYTES = P_BYTES + Q_BYTES;
     constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
@@ -216,6 +220,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             };
             // The weights do not depend on the kernel before this one; the activations do.  Fill the ring with
             // weight slices first, then wait for the predecessor, then add the activation slices.
+            const uint32_t stage_tx = P_BYTES + bn * TILE_K * 2;       // bytes that land in a stage
             const CUtensorMap* map_w = p.swapped ? &map_p : &map_q;
             const CUtensorMap* map_x = p.swapped ? &map_q : &map_p;
             const uint32_t off_w = p.swapped ? 0 : P_BYTES, off_x = p.swapped ? P_BYTES : 0;
@@ -223,9 +228,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             Walk ahead(p, blockIdx.x, gridDim.x);
             int early = 0;
             for (; early < STAGES && ahead.live; ++early, ahead.step(p)) {
-                mbar_expect_tx(full0 + 8 * early, STAGE_BYTES);
+                mbar_expect_tx(full0 + 8 * early, stage_tx);
                 tma_load_2d(smem_u32(smem + early * STAGE_BYTES) + off_w, map_w, ahead.kb * TILE_K,
-                            p.swapped ? ahead.p_blk * TILE_P : ahead.q_blk * BN, full0 + 8 * early);
+                            p.swapped ? ahead.p_blk * TILE_P : ahead.q_blk * bn, full0 + 8 * early);
             }
             mark(p, 2);
             fr_pdl_wait();
@@ -239,11 +244,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                     --early;                                 // the weight slice of this stage is already on its way
                 } else {
                     if (!(ok = mbar_wait(empty0 + 8 * stage, phase ^ 1, p.status, 1))) break;
-                    mbar_expect_tx(full0 + 8 * stage, STAGE_BYTES);
-                    tma_load_2d(dst + off_w, map_w, head.kb * TILE_K, p.swapped ? head.p_blk * TILE_P : head.q_blk * BN,
+                    mbar_expect_tx(full0 + 8 * stage, stage_tx);
+                    tma_load_2d(dst + off_w, map_w, head.kb * TILE_K, p.swapped ? head.p_blk * TILE_P : head.q_blk * bn,
                                 full0 + 8 * stage);
                 }
-                tma_load_2d(dst + off_x, map_x, head.kb * TILE_K, p.swapped ? head.q_blk * BN : head.p_blk * TILE_P,
+                tma_load_2d(dst + off_x, map_x, head.kb * TILE_K, p.swapped ? head.q_blk * bn : head.p_blk * TILE_P,
                             full0 + 8 * stage);
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
@@ -251,7 +256,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     } else if (warp == 1) {
         if (lane == 0) {
             fr_pdl_wait();
-            constexpr uint32_t idesc = instr_desc(TILE_P, BN);
+            const uint32_t idesc = instr_desc(TILE_P, bn);
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -307,7 +312,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         // sequence, position and cache row, and the rotation's cosines and sines.  What remains after the last product
         // is one trip to memory for split-k's partial sums, arithmetic, and stores.
         auto prefetch_tile = [&](int p_blk, int q_blk) {
-            const int nt = min(BN, p.q_rows - q_blk * BN);
+            const int nt = min(bn, p.q_rows - q_blk * bn);
             s_bias[et] = p.bias != nullptr ? bias_at(p, p_blk * TILE_P + et) : 0.f;
             if (f.norm_out != nullptr)
                 s_g[et] = f.norm_w_dtype == FR_F32 ? ((const float*)f.norm_w)[p_blk * TILE_P + et]
@@ -317,12 +322,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 for (int k = 0; k < ITEMS; ++k) {
                     const int idx = et + 128 * k;
                     if (idx < nt * 16)
-                        res[k] = __ldcg((const uint4*)((const __nv_bfloat16*)p.residual + (size_t)(q_blk * BN + (idx >> 4)) * p.ldo +
+                        res[k] = __ldcg((const uint4*)((const __nv_bfloat16*)p.residual + (size_t)(q_blk * bn + (idx >> 4)) * p.ldo +
                                                        (size_t)p_blk * TILE_P + (idx & 15) * 8));
                 }
             }
             if (rope && et < nt) {
-                const int row = q_blk * BN + et;
+                const int row = q_blk * bn + et;
                 const int seq = f.row_seq[row], pos = f.row_pos[row];
                 s_seq[et] = seq;
                 s_pos[et] = pos;
@@ -362,14 +367,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             return w;
         };
         auto finish_rows = [&](int p_blk, int q_blk) {
-            const int nt = min(BN, p.q_rows - q_blk * BN);
+            const int nt = min(bn, p.q_rows - q_blk * bn);
             const int half = f.rot >> 1;
 #pragma unroll
             for (int k = 0; k < ITEMS; ++k) {
                 if (k * 128 >= nt * 16) break;
                 const int idx = k * 128 + et, token = idx >> 4, f0 = (idx & 15) * 8;
                 const bool active = idx < nt * 16;
-                const int row = q_blk * BN + token, col = p_blk * TILE_P + f0;
+                const int row = q_blk * bn + token, col = p_blk * TILE_P + f0;
                 float ss = 0.f;
                 if (active) {
                     float x[8];
@@ -454,7 +459,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         auto load_scale = [&](int blk) {
             if (f.in_ssq == nullptr || blk == scale_blk) return;
             asm volatile("bar.sync 1, 128;" ::: "memory");
-            const int rows = p.swapped ? p.q_rows : p.p_rows, per = p.swapped ? BN : TILE_P;
+            const int rows = p.swapped ? p.q_rows : p.p_rows, per = p.swapped ? bn : TILE_P;
             if (et < per) {
                 const int row = blk * per + et;
                 float ss = 0.f;
@@ -491,9 +496,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + a * BN;
             // partial tiles are laid out [chunk of 16 columns][quarter of the chunk][row][4]: what a warp stores or
             // loads at a time is 512 bytes in one piece
-            float* part = item.nseg > 1 ? p.ws + (size_t)item.part * TILE_P * BN + (size_t)i_local * 4 : nullptr;
+            float* part = item.nseg > 1 ? p.ws + (size_t)item.part * TILE_P * bn + (size_t)i_local * 4 : nullptr;
 #pragma unroll 1
-            for (int c = 0; c < BN / 16; ++c) {
+            for (int c = 0; c < bn / 16; ++c) {
                 uint32_t r[16];
                 tc_ld16(taddr + c * 16, r);
                 tc_ld_wait();
@@ -503,7 +508,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 if (part == nullptr) {
                     scale16(c, v);
                     if (staged) put16(c, v);
-                    else finish16(p, gi, q_blk * BN + c * 16, v);
+                    else finish16(p, gi, q_blk * bn + c * 16, v);
                 } else {
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
@@ -532,7 +537,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                     if (et == 0) mark(p, 8);
                     const float* mine = p.ws + (size_t)i_local * 4;
 #pragma unroll 1
-                    for (int c = 0; c < BN / 16; ++c) {
+                    for (int c = 0; c < bn / 16; ++c) {
                         float v[16];
 #pragma unroll
                         for (int j = 0; j < 16; ++j) v[j] = 0.f;
@@ -542,7 +547,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
 #pragma unroll
                             for (int s = 0; s < 8; ++s) {
                                 if (s0 + s < item.nseg) {
-                                    const float* src = mine + (size_t)work.contributor(item, s0 + s) * TILE_P * BN + (size_t)c * TILE_P * 16;
+                                    const float* src = mine + (size_t)work.contributor(item, s0 + s) * TILE_P * bn + (size_t)c * TILE_P * 16;
 #pragma unroll
                                     for (int j = 0; j < 4; ++j) x[s][j] = __ldcg((const float4*)(src + (size_t)j * TILE_P * 4));
                                 }
@@ -561,7 +566,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                         if (et == 0) mark(p, 10);
                         scale16(c, v);
                         if (staged) put16(c, v);
-                        else finish16(p, gi, q_blk * BN + c * 16, v);
+                        else finish16(p, gi, q_blk * bn + c * 16, v);
                     }
                     if (staged) {
                         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -667,7 +672,18 @@ FR_EXPORT int gemm_tc_plan(int m, int n, int k, int sm_count, int swap, int bn, 
     const bool skinny = !swap && m <= TILE_P;
     if (bn <= 0) {
         if (swap) bn = q_rows <= 16 ? 16 : q_rows <= 32 ? 32 : 64;
-        else if (!skinny) bn = q_rows >= 256 ? 256 : q_rows > 64 ? 128 : 64;
+        else if (!skinny && q_rows >= 256) {
+            // Many rows: 128 x bn tiles, bn a multiple of 16 from 128 to 256, chosen so that the tiles fill whole
+            // waves of the SMs.  A tile costs about bn + 16 (its products, and an epilogue that is mostly hidden);
+            // 2048 x 3584: 14 column tiles of 256 are 224 tiles, two waves at 76 %; 18 of 208 are 288, two at 97 %.
+            const long long tiles_p = (p_rows + TILE_P - 1) / TILE_P;
+            long long best = -1;
+            for (int cand = 256; cand >= 128; cand -= 16) {
+                const long long tiles = tiles_p * ((q_rows + cand - 1) / cand);
+                const long long cost = ((tiles + sm_count - 1) / sm_count) * (cand + 16);
+                if (best < 0 || cost < best) { best = cost; bn = cand; }
+            }
+        } else if (!skinny) bn = q_rows > 64 ? 128 : 64;
         else if (q_rows >= 8192 || kb_total >= 128) bn = 128;
         else bn = (q_rows + 31) / 32 <= sm_count ? 32 : 64;
     }
@@ -732,7 +748,7 @@ FR_EXPORT int gemm_tc_fused(const void* x, const void* w, void* out, int out_dty
     long long plan[5];
     gemm_tc_plan(m, n, k, sm_count, swap, bn, splits, plan);
     swap = (int)plan[0]; bn = (int)plan[1]; splits = (int)plan[2];
-    if (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256) FR_REFUSE("gemm_tc: tile width %d", bn);
+    if (bn != 16 && bn != 32 && bn != 64 && !(bn >= 128 && bn <= 256 && bn % 16 == 0)) FR_REFUSE("gemm_tc: tile width %d", bn);
     if (plan[3] > scratch_floats || plan[4] > n_counters)
         FR_REFUSE("gemm_tc: split-k needs %lld scratch floats and %lld counters, given %lld and %d", plan[3], plan[4],
                   scratch_floats, n_counters);
@@ -769,6 +785,7 @@ FR_EXPORT int gemm_tc_fused(const void* x, const void* w, void* out, int out_dty
     p.out = out; p.bias = bias; p.residual = residual; p.ws = scratch; p.counters = counters; p.status = status;
     p.p_rows = swap ? n : m; p.q_rows = swap ? m : n; p.ldo = ldo; p.out_dtype = out_dtype; p.bias_dtype = bias_dtype;
     p.swapped = swap;
+    p.bn = bn;
     p.act = act;
     p.tiles_p = (p.p_rows + TILE_P - 1) / TILE_P; p.tiles_q = (p.q_rows + bn - 1) / bn;
     p.splits = splits; p.kb_total = (k + TILE_K - 1) / TILE_K; p.kb_per = (p.kb_total + splits - 1) / splits;
@@ -797,7 +814,7 @@ FR_EXPORT int gemm_tc_fused(const void* x, const void* w, void* out, int out_dty
         case 32: return launch<32, 10>(mp, mq, p, grid, stream);
         case 64: return launch<64, 7>(mp, mq, p, grid, stream);
         case 128: return launch<128, 6>(mp, mq, p, grid, stream);
-        default: return launch<256, 4>(mp, mq, p, grid, stream);
+        default: return launch<256, 4>(mp, mq, p, grid, stream);       // any width from 144 to 256
     }
 }
 

@@ -263,7 +263,8 @@ def test_gemm_tensor_core(m, n, k):
 @pytest.mark.parametrize("m,n,k,swap,bn,splits", [
     (8, 512, 1024, 1, 16, 1), (8, 512, 1024, 1, 16, 4), (8, 512, 1024, 1, 64, 16), (40, 300, 2048, 1, 64, 3),
     (40, 300, 2048, 0, 64, 1), (300, 300, 2048, 0, 128, 2), (300, 700, 2048, 0, 256, 5), (128, 256, 4096, 0, 256, 64),
-    (100, 100, 64, 0, 128, 1), (5, 130, 72, 0, 256, 1), (300, 40, 2048, 1, 32, 1)])
+    (100, 100, 64, 0, 128, 1), (5, 130, 72, 0, 256, 1), (300, 40, 2048, 1, 32, 1),
+    (300, 1000, 256, 0, 208, 1), (2048, 3584, 512, 0, 208, 1), (256, 700, 128, 0, 144, 3), (130, 1001, 328, 0, 240, 1)])
 def test_gemm_tensor_core_every_tiling(m, n, k, swap, bn, splits):
     """Orientation, tile width and split-k are choices of the launcher; each must give the same product."""
     dt = torch.bfloat16
@@ -375,7 +376,7 @@ def test_gemm_tensor_core_gated_epilogue(m, inner, k):
     ref = pm.swiglu(pm.linear(f64(x), f64(wg)), pm.linear(f64(x), f64(wu)))
     close(ops.linear_swiglu(x, pairs), ref, dt, "product with silu(gate) * up in the epilogue", bf16_rel=0.01)
     be = ops.backend()
-    for swap, bn, splits in ((1, 64, 3), (0, 128, 2), (0, 256, 1)):
+    for swap, bn, splits in ((1, 64, 3), (0, 128, 2), (0, 256, 1), (0, 176, 1)):
         if (swap and m > 64) or 2 * inner * max(m, 128) > 2000000:     # forced tilings only where their scratch fits
             continue
         out = torch.empty((m, inner), dtype=dt, device=DEV)
