@@ -1,0 +1,423 @@
+// Causal grouped-query attention for prompts on the 5th-generation tensor cores (sm_100a): both products of
+// flash attention are tcgen05.mma with their results in tensor memory.
+//
+// A CTA owns up to 128 rows of one sequence and kv head; row r stands for (token r / G, group head r % G),
+// G = heads / kv heads, so a block of keys and values is read once for all heads that share it (as the reference's
+// R = tq*G + g rows: attention_kernels.cu:493-499).  Blocks of 128 keys are two pages of the cache.
+//
+//   warp 0      TMA producer: the queries (a 4-d box [64 dims][G heads][1][T tokens] per 64-dim slice lands as
+//               rows t*G + g, 128-byte swizzle), then per block K and V pages into a ring of two stages.  A page
+//               that the block does not need, or that the table does not name, is loaded from beyond the pool's
+//               last row, which fills zeros.
+//   warp 1      allocates tensor memory; one lane issues S = Q K^T (M = 128 rows, N = 128 keys, both operands
+//               K-major) into one of two S buffers, and O_blk = P V (A = P from shared memory, K-major; B = V as it
+//               lies in the cache, [keys][dims] = MN-major) into the O buffer.
+//   warps 2-5   one thread per row (its TMEM lane): reads its row of S twice (maximum, then exponentials), keeps the
+//               running maximum and sum, writes P (bf16) into shared memory in the swizzled layout the tensor core
+//               reads, then adds O_blk, rescaled, to the row's output which it holds in registers.
+//
+// QK^T of block i+1 is issued before the softmax of block i is waited for, so the tensor core works while the
+// rows are exponentiated.  Scores, softmax and sums are fp32; P is rounded to bf16 for the second product, as the
+// mma.sync kernel does.  Rows of V past the last key that any row of the CTA may see are zeroed in shared memory
+// before the product (their P is zero, but zero times a stale NaN is not); stale K only reaches scores that the
+// mask replaces.  Every wait on an mbarrier is bounded (two seconds), then a code goes to `status` and all roles
+// leave their loops.
+//
+// Head sizes: multiples of 16 up to 128.  One-token steps keep the mma.sync kernel (attention_mma.cu), whose rows
+// of a CTA share a token.
+#include <cuda.h>
+#include <math.h>
+
+#include "common.cuh"
+#include "tc_common.cuh"
+
+FR_EXPORT const char* attention_tc_last_error() { return fr_error_text; }
+
+namespace {
+
+using namespace tc;
+typedef __nv_bfloat16 bf16;
+constexpr int THREADS = 192;
+constexpr int ROWS = 128;                 // rows of a CTA = M of the instruction
+constexpr int KEYS = 128;                 // keys of a block = two cache pages
+constexpr int PAGE = 64;
+constexpr int SLICE = ROWS * 128;         // bytes of 128 rows of 64 bf16 (one 128-byte swizzle row each)
+constexpr int STAGES = 2;
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct TcArgs {
+    bf16* out;                // [rows][nq * hd]
+    const int* block_table;   // [seqs][table_width]
+    const int* seq_start;     // first row of each sequence
+    const int* seq_qlen;      // rows (tokens) of each sequence in this step
+    const int* seq_pos0;      // position of its first row
+    const int* seq_live;      // may be null; < 0 at seq_start[s]: the sequence has ended
+    int* status;
+    int table_width, nq, nkv, hd, window, pool_rows;
+    float scale_log2;         // softmax scale times log2(e)
+};
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3,
+                                            uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+        : "memory");
+}
+// Descriptor of an MN-major operand (the contiguous dimension is N): 8 consecutive k form a 1024-byte swizzle atom
+// of 64 n; `sbo` is the distance between atoms along k, `lbo` between atoms along n.
+__device__ __forceinline__ uint64_t smem_desc_mn(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                    const __grid_constant__ CUtensorMap map_v, const TcArgs p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* s_q = smem;                              // [2 slices][128 rows][128 B]
+    uint8_t* s_k = s_q + 2 * SLICE;                   // [STAGES][2 slices][128 keys][128 B]
+    uint8_t* s_v = s_k + STAGES * 2 * SLICE;          // [STAGES][2 slices of 64 dims][128 keys][128 B]
+    uint8_t* s_p = s_v + STAGES * 2 * SLICE;          // [2 slices of 64 keys][128 rows][128 B]
+    uint64_t* bars = (uint64_t*)(s_p + 2 * SLICE);
+    // bars: q_full, kv_full[2], kv_empty[2], s_full[2], p_full, o_full, o_empty
+    uint32_t* tmem_slot = (uint32_t*)(bars + 10);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t q_full = smem_u32(bars), kv_full0 = smem_u32(bars + 1), kv_empty0 = smem_u32(bars + 3);
+    const uint32_t s_full0 = smem_u32(bars + 5), p_full = smem_u32(bars + 7), o_full = smem_u32(bars + 8);
+    const uint32_t o_empty = smem_u32(bars + 9);
+
+    // The CTA's rows and its range of key blocks.  The step's geometry is final before the step's first kernel
+    // starts (common.cuh), so it is read ahead of the wait.
+    const int seq = blockIdx.z, kvh = blockIdx.y, tile = blockIdx.x;
+    const int G = p.nq / p.nkv, T = ROWS / G;         // T tokens of G heads each fill the tile's rows
+    const int q_len = p.seq_qlen[seq], q_start = p.seq_start[seq], pos0 = p.seq_pos0[seq];
+    const int t0 = tile * T;
+    if (t0 >= q_len) return;
+    if (p.seq_live != nullptr && p.seq_live[q_start] < 0) return;     // an ended sequence's rows are not written
+    const int t_end = min(t0 + T, q_len);             // tokens t0 .. t_end-1
+    const int pos_hi = pos0 + t_end - 1;              // the farthest key any row of the CTA may see
+    const int lo_min = p.window > 0 ? max(0, pos0 + t0 - p.window + 1) : 0;
+    const int kb_begin = lo_min / KEYS, kb_end = pos_hi / KEYS;       // inclusive
+    const int n_blocks = kb_end - kb_begin + 1;
+    const int slices = (p.hd + 63) / 64;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(kv_full0 + 8 * s, 1);
+            mbar_init(kv_empty0 + 8 * s, 1);
+            mbar_init(s_full0 + 8 * s, 1);
+        }
+        mbar_init(p_full, 128);
+        mbar_init(o_full, 1);
+        mbar_init(o_empty, 128);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(512u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * KEYS;   // columns: S0 | S1 | O
+    fr_pdl_wait();
+    if (threadIdx.x == 0) fr_pdl_launch();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+            mbar_expect_tx(q_full, (uint32_t)slices * 64 * G * T * 2);
+            for (int s = 0; s < slices; ++s)
+                tma_load_4d(smem_u32(s_q + s * SLICE), &map_q, s * 64, 0, kvh, q_start + t0, q_full);
+            const int* table = p.block_table + (size_t)seq * p.table_width;
+            bool ok = true;
+            for (int i = 0; i < n_blocks && ok; ++i) {
+                const int kb = kb_begin + i, stage = i & 1;
+                if (!(ok = mbar_wait(kv_empty0 + 8 * stage, ((i >> 1) & 1) ^ 1, p.status, 1))) break;
+                mbar_expect_tx(kv_full0 + 8 * stage, (uint32_t)slices * 2 * 2 * PAGE * 128);
+                for (int h = 0; h < 2; ++h) {
+                    const int lp = kb * 2 + h;
+                    int row = p.pool_rows;                                   // beyond the pool: the box is filled with zeros
+                    if (lp * PAGE <= pos_hi && lp < p.table_width) {
+                        const int page = table[lp];
+                        if (page >= 0) row = page * PAGE;
+                    }
+                    for (int s = 0; s < slices; ++s) {
+                        const uint32_t off = (uint32_t)((stage * 2 + s) * SLICE + h * PAGE * 128);
+                        tma_load_3d(smem_u32(s_k) + off, &map_k, s * 64, kvh, row, kv_full0 + 8 * stage);
+                        tma_load_3d(smem_u32(s_v) + off, &map_v, s * 64, kvh, row, kv_full0 + 8 * stage);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc_qk = instr_desc(ROWS, KEYS);
+            const uint32_t idesc_pv = instr_desc(ROWS, p.hd) | (1u << 16);   // B is MN-major
+            const int k_steps = p.hd / 16;                                   // of the first product
+            auto issue_qk = [&](int i) {
+                const int stage = i & 1;
+                const uint32_t d = tmem_s + (uint32_t)(i & 1) * KEYS;
+                for (int ks = 0; ks < k_steps; ++ks) {
+                    const int s = ks >> 2, k = ks & 3;
+                    const uint64_t da = smem_desc(smem_u32(s_q + s * SLICE)) + 2 * k;
+                    const uint64_t db = smem_desc(smem_u32(s_k + (stage * 2 + s) * SLICE)) + 2 * k;
+                    tc_mma(d, da, db, idesc_qk, ks > 0 ? 1u : 0u);
+                }
+                tc_commit(s_full0 + 8 * (i & 1));
+            };
+            bool ok = mbar_wait(q_full, 0, p.status, 2);
+            if (ok) ok = mbar_wait(kv_full0, 0, p.status, 3);
+            if (ok) {
+                tc_fence_after();
+                issue_qk(0);
+            }
+            for (int i = 0; i < n_blocks && ok; ++i) {
+                const int stage = i & 1;
+                if (i + 1 < n_blocks) {
+                    // S of block i+1 goes to the other buffer, which the rows have read (p_full of block i-1 was
+                    // waited for in the round before)
+                    if (!(ok = mbar_wait(kv_full0 + 8 * ((i + 1) & 1), ((i + 1) >> 1) & 1, p.status, 3))) break;
+                    tc_fence_after();
+                    issue_qk(i + 1);
+                }
+                if (!(ok = mbar_wait(p_full, i & 1, p.status, 4))) break;
+                if (i > 0 && !(ok = mbar_wait(o_empty, (i - 1) & 1, p.status, 5))) break;
+                tc_fence_after();
+                // keys of this block that some row may see, in steps of 16
+                const int keys_here = min(KEYS, pos_hi - (kb_begin + i) * KEYS + 1);
+                const int pv_steps = (keys_here + 15) / 16;
+                for (int ks = 0; ks < pv_steps; ++ks) {
+                    const uint64_t da = smem_desc(smem_u32(s_p + (ks >> 2) * SLICE)) + 2 * (ks & 3);
+                    const uint64_t db = smem_desc_mn(smem_u32(s_v + stage * 2 * SLICE) + ks * 16 * 128, SLICE, 1024);
+                    tc_mma(tmem_o, da, db, idesc_pv, ks > 0 ? 1u : 0u);
+                }
+                tc_commit(o_full);
+                tc_commit(kv_empty0 + 8 * stage);
+            }
+        }
+    } else {
+        const int quarter = warp & 3;                      // TMEM lanes this warp may read: 32*quarter ..
+        const int r = quarter * 32 + lane;                 // this thread's row of the tile
+        const int t = r / G, g = r - t * G;
+        const bool valid = r < T * G && t0 + t < q_len;
+        const int pos_r = valid ? pos0 + t0 + t : -1;      // -1: every key is masked
+        const int lo_r = (valid && p.window > 0) ? max(0, pos_r - p.window + 1) : 0;
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        float o[128];
+#pragma unroll
+        for (int i = 0; i < 128; ++i) o[i] = 0.f;
+        float m_run = -INFINITY, l_run = 0.f;
+        bool ok = true;
+        for (int i = 0; i < n_blocks && ok; ++i) {
+            const int kb = kb_begin + i, stage = i & 1;
+            const int j0 = kb * KEYS;
+            if (!(ok = mbar_wait(s_full0 + 8 * (i & 1), (i >> 1) & 1, p.status, 6))) break;
+            tc_fence_after();
+            const uint32_t s_addr = tmem_s + lane_addr + (uint32_t)(i & 1) * KEYS;
+            const bool need_mask = j0 + KEYS - 1 > pos0 + t0 || (p.window > 0 && j0 < pos_hi - p.window + 1) || !valid;
+            // the row's maximum over the block
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < KEYS / 16; ++c) {
+                uint32_t raw[16];
+                tc_ld16(s_addr + c * 16, raw);
+                tc_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    float v = __uint_as_float(raw[j]) * p.scale_log2;
+                    if (need_mask) {
+                        const int key = j0 + c * 16 + j;
+                        if (key > pos_r || key < lo_r) v = -INFINITY;
+                    }
+                    mx = fmaxf(mx, v);
+                }
+            }
+            const float m_new = fmaxf(m_run, mx);
+            const float m_use = m_new == -INFINITY ? 0.f : m_new;
+            const float alpha = exp2f(m_run - m_use);          // 0 while the row has seen no key
+            m_run = m_new;
+            // exponentials: P into shared memory (bf16, the swizzled K-major layout), their sum into l
+            float sum = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < KEYS / 16; ++c) {
+                uint32_t raw[16];
+                tc_ld16(s_addr + c * 16, raw);
+                tc_ld_wait();
+                float pe[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    float v = __uint_as_float(raw[j]) * p.scale_log2;
+                    if (need_mask) {
+                        const int key = j0 + c * 16 + j;
+                        if (key > pos_r || key < lo_r) v = -INFINITY;
+                    }
+                    pe[j] = exp2f(v - m_use);
+                    sum += pe[j];
+                }
+                // 16 keys = two 16-byte chunks of the row's 128-byte line in slice c / 4
+                uint8_t* line = s_p + (c >> 2) * SLICE + r * 128;
+                const int ch = (c & 3) * 2;
+                *(uint4*)(line + ((ch ^ (r & 7)) << 4)) =
+                    make_uint4(pack2(pe[0], pe[1]), pack2(pe[2], pe[3]), pack2(pe[4], pe[5]), pack2(pe[6], pe[7]));
+                *(uint4*)(line + (((ch + 1) ^ (r & 7)) << 4)) =
+                    make_uint4(pack2(pe[8], pe[9]), pack2(pe[10], pe[11]), pack2(pe[12], pe[13]), pack2(pe[14], pe[15]));
+            }
+            l_run = l_run * alpha + sum;
+            if (kb == kb_end) {
+                // keys past the last one that any row may see: their V rows may hold anything; zero them
+                const int key = j0 + r;
+                if (key > pos_hi) {
+                    if (!(ok = mbar_wait(kv_full0 + 8 * stage, (i >> 1) & 1, p.status, 7))) break;
+                    for (int s = 0; s < slices; ++s) {
+                        uint4* line = (uint4*)(s_v + (stage * 2 + s) * SLICE + r * 128);
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) line[q] = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                }
+            }
+            tc_fence_before();
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(p_full);
+            // O_blk = P V of this block, added to the row
+            if (!(ok = mbar_wait(o_full, i & 1, p.status, 8))) break;
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                if (c * 16 < p.hd) {
+                    uint32_t raw[16];
+                    tc_ld16(tmem_o + lane_addr + c * 16, raw);
+                    tc_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) o[c * 16 + j] = o[c * 16 + j] * alpha + __uint_as_float(raw[j]);
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(o_empty);
+        }
+        if (ok && valid) {
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            bf16* dst = p.out + ((size_t)(q_start + t0 + t) * p.nq + (size_t)kvh * G + g) * p.hd;
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                if (c * 8 < p.hd)
+                    *(uint4*)(dst + c * 8) = make_uint4(pack2(o[c * 8] * inv, o[c * 8 + 1] * inv), pack2(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv),
+                                                        pack2(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv), pack2(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv));
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+    static EncodeTiled fn = nullptr;
+    if (fn == nullptr) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)ptr;
+    }
+    return fn;
+}
+
+int encode(CUtensorMap* map, const void* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides,
+           const cuuint32_t* box, const char* what) {
+    EncodeTiled enc = encode_fn();
+    if (enc == nullptr) FR_REFUSE("attention_tc: the driver does not offer cuTensorMapEncodeTiled");
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), dims, strides, box,
+                           estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) FR_REFUSE("attention_tc: cuTensorMapEncodeTiled failed with %d for %s", (int)r, what);
+    return FR_OK;
+}
+
+constexpr int SMEM_BYTES = (2 + 2 * STAGES * 2 + 2) * SLICE + 1024 + 256;
+
+}  // namespace
+
+// What the kernel takes: bf16, head sizes in steps of 16 up to 128, 64-token pages, at most 128 heads per kv head,
+// query rows that start on 16-byte boundaries.
+FR_EXPORT int attention_tc_supports(int hd, int page, int nq, int nkv, int q_stride) {
+    return hd % 16 == 0 && hd >= 16 && hd <= 128 && page == PAGE && nkv > 0 && nq % nkv == 0 && nq / nkv <= ROWS &&
+           q_stride % 8 == 0;
+}
+
+// q: rows of q_stride bf16 (head h at h * hd), total_rows of them; out [rows][nq * hd]; pools [pool_pages][64][nkv][hd]
+// bf16.  seq_start / seq_qlen / seq_pos0: per sequence, its first row, its rows in this step, the position of its
+// first row; seq_live (may be null): indexed by a sequence's first row, negative marks an ended sequence, whose rows
+// are left alone.  max_q_len: the longest seq_qlen (sizes the grid).  status: a device word for a wait that gave up.
+FR_EXPORT int attention_tc(const void* q, int q_stride, int total_rows, void* out, const void* k_pool, const void* v_pool,
+                           int pool_pages, const int* block_table, int table_width, const int* seq_start,
+                           const int* seq_qlen, const int* seq_pos0, const int* seq_live, int n_seqs, int max_q_len,
+                           int nq, int nkv, int hd, int window, float scale, int* status, cudaStream_t stream) {
+    if (n_seqs <= 0 || total_rows <= 0 || max_q_len <= 0) return FR_OK;
+    if (!attention_tc_supports(hd, PAGE, nq, nkv, q_stride))
+        FR_REFUSE("attention_tc: head size %d, %d heads on %d kv heads, row stride %d: not for this kernel", hd, nq, nkv, q_stride);
+    if (((uintptr_t)q & 15) || ((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15) || ((uintptr_t)out & 15))
+        FR_REFUSE("attention_tc: buffers must be 16-byte aligned");
+    if (status == nullptr) FR_REFUSE("attention_tc: a status word is needed");
+    if (n_seqs > 65535 || nkv > 65535) FR_REFUSE("attention_tc: %d sequences x %d kv heads exceed the grid", n_seqs, nkv);
+    const int G = nq / nkv, T = ROWS / G;
+    CUtensorMap mq, mk, mv;
+    {
+        const cuuint64_t dims[4] = {(cuuint64_t)hd, (cuuint64_t)G, (cuuint64_t)nkv, (cuuint64_t)total_rows};
+        const cuuint64_t strides[3] = {(cuuint64_t)hd * 2, (cuuint64_t)G * hd * 2, (cuuint64_t)q_stride * 2};
+        const cuuint32_t box[4] = {64, (cuuint32_t)G, 1, (cuuint32_t)T};
+        const int rc = encode(&mq, q, 4, dims, strides, box, "the queries");
+        if (rc) return rc;
+    }
+    {
+        const cuuint64_t dims[3] = {(cuuint64_t)hd, (cuuint64_t)nkv, (cuuint64_t)pool_pages * PAGE};
+        const cuuint64_t strides[2] = {(cuuint64_t)hd * 2, (cuuint64_t)nkv * hd * 2};
+        const cuuint32_t box[3] = {64, 1, PAGE};
+        int rc = encode(&mk, k_pool, 3, dims, strides, box, "the keys");
+        if (rc) return rc;
+        rc = encode(&mv, v_pool, 3, dims, strides, box, "the values");
+        if (rc) return rc;
+    }
+    TcArgs p;
+    p.out = (bf16*)out; p.block_table = block_table; p.seq_start = seq_start; p.seq_qlen = seq_qlen;
+    p.seq_pos0 = seq_pos0; p.seq_live = seq_live; p.status = status; p.table_width = table_width; p.nq = nq;
+    p.nkv = nkv; p.hd = hd; p.window = window; p.pool_rows = pool_pages * PAGE; p.scale_log2 = scale * LOG2E;
+    static bool configured = false;
+    if (!configured) {
+        FR_CUDA(cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        configured = true;
+    }
+    const dim3 grid((max_q_len + T - 1) / T, nkv, n_seqs);
+    FR_CUDA(fr_launch(attention_tc_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, mq, mk, mv, p));
+    FR_CHECK_LAUNCH("attention_tc");
+    return FR_OK;
+}

@@ -301,8 +301,8 @@ class CudaOps:
             code = int(bufs[2][0].item())
             if code:
                 bufs[2].zero_()
-                raise KernelError("a tensor-core kernel on %s gave up waiting (code %d: 1 producer, 2 accumulator, "
-                                  "3 operands, 4 epilogue); its results are not valid" % (device, code))
+                raise KernelError("a tensor-core kernel on %s gave up waiting (code %d: which of its bounded waits, "
+                                  "see gemm_tc.cu and attention_tc.cu); its results are not valid" % (device, code))
 
     def _linear_simt(self, x, weight, bias, residual, out):
         """The CUDA-core product: true fp32, and the fallback of bf16 for sizes the tensor-core kernel refuses."""
@@ -327,6 +327,12 @@ class CudaOps:
         """
         _need_cuda(q, out, k_pool, v_pool, block_table, row_seq, row_pos)
         if (out.dtype == torch.bfloat16 and getattr(geometry, "seq_start", None) is not None
+                and not geometry.decode and self.attention_tc_supports(head_dim, page_size, n_heads, n_kv_heads, q_stride)
+                and k_pool.dim() == 4 and k_pool.is_contiguous() and v_pool.is_contiguous()):
+            return self.attention_tc(q, q_stride, out, k_pool, v_pool, block_table, geometry.seq_start,
+                                     geometry.seq_qlen, geometry.seq_pos0, row_seq, geometry.n_seqs,
+                                     geometry.max_q_len, n_heads, n_kv_heads, head_dim, window, scale)
+        if (out.dtype == torch.bfloat16 and getattr(geometry, "seq_start", None) is not None
                 and self.attention_mma_supports(head_dim, page_size)):
             keys_mode = bool(geometry.decode)
             splits = 1
@@ -345,6 +351,24 @@ class CudaOps:
             "attention_simt", _ptr(q), q_stride, _ptr(out), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
             block_table.shape[1], page_size, _ptr(row_seq), _ptr(row_pos), rows, n_heads, n_kv_heads, head_dim,
             window or 0, float(scale), splits, _ptr(scratch), code_of(out.dtype), _stream())
+
+    def attention_tc_supports(self, head_dim, page_size, n_heads, n_kv_heads, q_stride):
+        """Prompts: both products of attention on tcgen05 (csrc/attention_tc.cu).  FRIDAY_ATTN_TC=0 keeps the
+        mma.sync kernel for them."""
+        import os
+        return (os.environ.get("FRIDAY_ATTN_TC", "1") != "0" and head_dim % 16 == 0 and 16 <= head_dim <= 128
+                and page_size == 64 and n_kv_heads > 0 and n_heads % n_kv_heads == 0 and n_heads // n_kv_heads <= 128
+                and q_stride % 8 == 0)
+
+    def attention_tc(self, q, q_stride, out, k_pool, v_pool, block_table, seq_start, seq_qlen, seq_pos0, seq_live,
+                     n_seqs, max_q_len, n_heads, n_kv_heads, head_dim, window, scale):
+        """Causal attention of whole prompts (or their continuation) over the paged cache: up to 128 rows of
+        (token, group head) pairs per CTA, blocks of 128 keys."""
+        status = self._tc_buffers(q.device)[2]
+        lib.family("attention_tc").call(
+            "attention_tc", _ptr(q), q_stride, q.shape[0], _ptr(out), _ptr(k_pool), _ptr(v_pool), k_pool.shape[0],
+            _ptr(block_table), block_table.shape[1], _ptr(seq_start), _ptr(seq_qlen), _ptr(seq_pos0), _ptr(seq_live),
+            n_seqs, max_q_len, n_heads, n_kv_heads, head_dim, window or 0, float(scale), _ptr(status), _stream())
 
     def attention_mma_supports(self, head_dim, page_size):
         return head_dim % 16 == 0 and 16 <= head_dim <= 128 and page_size == 64

@@ -23,7 +23,8 @@ CSRC = os.path.join(os.path.dirname(_HERE), "csrc")
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC,-fvisibility=hidden",
               "--expt-relaxed-constexpr"]
-FAMILIES = ("rowwise", "gemm_simt", "attention_simt", "sampling", "gemm_tc", "attention_mma", "decode_layer")
+FAMILIES = ("rowwise", "gemm_simt", "attention_simt", "sampling", "gemm_tc", "attention_mma", "attention_tc",
+            "decode_layer")
 # libraries other than the runtime that a family links
 EXTRA_LIBS = {}
 

@@ -46,6 +46,10 @@ _SIGNATURES = {
         "attention_mma_supports": [I, I],
         "attention_mma_clusters_at_once": [I, I],
     },
+    "attention_tc": {
+        "attention_tc": [P, I, I, P, P, P, I, P, I, P, P, P, P, I, I, I, I, I, I, F, P, P],
+        "attention_tc_supports": [I, I, I, I, I],
+    },
     "sampling": {
         "sampling_sample": [P, I, I, I, P, P, P, c_ulonglong, P, P, P],
     },

@@ -294,10 +294,11 @@ class SeqGeo(Geo):
     pass
 
 
-def mma_case(seqs, nq, nkv, hd, window, keys_mode, splits, seed=30):
+def mma_case(seqs, nq, nkv, hd, window, keys_mode, splits, seed=30, tcgen05=False):
     """seqs: list of (tokens held before the step, tokens in the step).  Builds a paged cache that holds
     every sequence's keys and values (shuffled pages, NaN elsewhere), runs the tensor-core kernel on the
-    step's rows and compares with the plain attention of each whole sequence."""
+    step's rows (the mma.sync one, or with tcgen05 the one for prompts) and compares with the plain attention
+    of each whole sequence."""
     dt = torch.bfloat16
     n_pages_each = [(a + q + PAGE - 1) // PAGE for a, q in seqs]
     total_pages = sum(n_pages_each) + 3
@@ -326,10 +327,17 @@ def mma_case(seqs, nq, nkv, hd, window, keys_mode, splits, seed=30):
     i32 = dict(dtype=torch.int32, device=DEV)
     geo = Geo(max(a + q for a, q in seqs))
     out = torch.full((rows, nq * hd), float("nan"), dtype=dt, device=DEV)
-    ops.backend().attention_mma(
-        qbuf, qbuf.stride(0), out, kp, vp, table.to(DEV), torch.tensor(starts, **i32),
-        torch.tensor([q for _, q in seqs], **i32), torch.tensor([a for a, _ in seqs], **i32), None, len(seqs),
-        max(q for _, q in seqs), nq, nkv, hd, window, hd ** -0.5, keys_mode, splits, geo)
+    if tcgen05:
+        ops.backend().attention_tc(
+            qbuf, qbuf.stride(0), out, kp, vp, table.to(DEV), torch.tensor(starts, **i32),
+            torch.tensor([q for _, q in seqs], **i32), torch.tensor([a for a, _ in seqs], **i32), None, len(seqs),
+            max(q for _, q in seqs), nq, nkv, hd, window, hd ** -0.5)
+        ops.backend().check_status()
+    else:
+        ops.backend().attention_mma(
+            qbuf, qbuf.stride(0), out, kp, vp, table.to(DEV), torch.tensor(starts, **i32),
+            torch.tensor([q for _, q in seqs], **i32), torch.tensor([a for a, _ in seqs], **i32), None, len(seqs),
+            max(q for _, q in seqs), nq, nkv, hd, window, hd ** -0.5, keys_mode, splits, geo)
     close(out, np.concatenate(refs, axis=0), dt, "tensor-core attention", bf16_rel=0.02)
 
 
@@ -341,6 +349,17 @@ def test_attention_mma_prompts_of_unequal_lengths(nq, nkv, hd, window):
     mma_case([(0, 37), (0, 130), (70, 65), (0, 1), (63, 2), (0, 64)], nq, nkv, hd, window, False, 1)
 
 
+@pytest.mark.parametrize("nq,nkv,hd,window", [
+    (4, 2, 16, None), (3, 1, 32, 24), (28, 4, 128, None), (6, 2, 48, 80), (8, 1, 112, 64), (14, 2, 64, None),
+    (5, 5, 80, None), (9, 3, 96, 100), (32, 1, 64, None), (40, 8, 128, 300), (128, 1, 16, None), (3, 3, 128, 128)])
+def test_attention_tcgen05_prompts_of_unequal_lengths(nq, nkv, hd, window):
+    """The kernel for prompts with both products on tcgen05: the same cases as the mma.sync kernel (stale pages
+    hold NaN), lengths around its 128-key blocks, 128 heads on one kv head (one token per tile), and a window
+    that is exactly one block."""
+    mma_case([(0, 37), (0, 130), (70, 65), (0, 1), (63, 2), (0, 64)], nq, nkv, hd, window, False, 1, tcgen05=True)
+    mma_case([(0, 128), (0, 129), (127, 2), (255, 258), (0, 700)], nq, nkv, hd, window, False, 1, seed=77, tcgen05=True)
+
+
 @pytest.mark.parametrize("nq,nkv,hd,window,splits", [
     (4, 2, 16, None, 1), (3, 1, 32, 24, 2), (28, 4, 128, None, 5), (28, 4, 128, None, 1), (6, 2, 48, 80, 3),
     (8, 1, 112, 64, 4), (40, 8, 128, None, 7), (32, 1, 64, None, 2), (5, 5, 80, 130, 16)])
@@ -350,6 +369,7 @@ def test_attention_mma_one_token_steps(nq, nkv, hd, window, splits):
 
 def test_attention_mma_long_prompt_sizes_of_the_7b_shape():
     mma_case([(0, 700), (300, 500)], 28, 4, 128, None, False, 1)
+    mma_case([(0, 2048), (1000, 1100)], 28, 4, 128, None, False, 1, tcgen05=True)
 
 
 def test_attention_mma_dead_rows_give_zero():
