@@ -10,23 +10,28 @@
 //               that the block does not need, or that the table does not name, is loaded from beyond the pool's
 //               last row, which fills zeros.
 //   warp 1      allocates tensor memory; one lane issues S = Q K^T (M = 128 rows, N = 128 keys, both operands
-//               K-major) into one of two S buffers, and O_blk = P V (A = P from shared memory, K-major; B = V as it
-//               lies in the cache, [keys][dims] = MN-major) into the O buffer.
-//   warps 2-5   one thread per row (its TMEM lane): reads its row of S twice (maximum, then exponentials), keeps the
-//               running maximum and sum, writes P (bf16) into shared memory in the swizzled layout the tensor core
-//               reads, then adds O_blk, rescaled, to the row's output which it holds in registers.
+//               K-major) into one of two S buffers, and O += P V (A = P from shared memory, K-major; B = V as it
+//               lies in the cache, [keys][dims] = MN-major) into the O columns, which stay in tensor memory for
+//               the whole CTA.
+//   warps 2-5   one thread per row (its TMEM lane): reads its row of S once into registers, keeps the running
+//               maximum and sum, writes P (bf16) into one of two shared-memory buffers in the swizzled layout the
+//               tensor core reads.  The maximum that P is taken against only moves when a row's true maximum has
+//               grown by more than 8 (in log2 units; P then stays below 2^8 and the sums remain exact for that
+//               reference); only then is O rescaled, in tensor memory.  At the end the row's O is divided by its sum.
 //
-// QK^T of block i+1 is issued before the softmax of block i is waited for, so the tensor core works while the
-// rows are exponentiated.  Scores, softmax and sums are fp32; P is rounded to bf16 for the second product, as the
-// mma.sync kernel does.  Rows of V past the last key that any row of the CTA may see are zeroed in shared memory
-// before the product (their P is zero, but zero times a stale NaN is not); stale K only reaches scores that the
-// mask replaces.  Every wait on an mbarrier is bounded (two seconds), then a code goes to `status` and all roles
-// leave their loops.
+// QK^T of block i+1 and P V of block i-1 run while the rows of block i are exponentiated.  Scores, softmax and sums
+// are fp32; P is rounded to bf16 for the second product, as the mma.sync kernel does.  Rows of V past the last key
+// that any row of the CTA may see are zeroed in shared memory before the product (their P is zero, but zero times a
+// stale NaN is not); stale K only reaches scores that the mask replaces.  Long tiles (late tokens) are launched
+// first.  Every wait on an mbarrier is bounded (two seconds), then a code goes to `status` and all roles leave their
+// loops.
 //
 // Head sizes: multiples of 16 up to 128.  One-token steps keep the mma.sync kernel (attention_mma.cu), whose rows
 // of a CTA share a token.
 #include <cuda.h>
 #include <math.h>
+
+#include <type_traits>
 
 #include "common.cuh"
 #include "tc_common.cuh"
@@ -55,6 +60,9 @@ struct TcArgs {
     int* status;
     int table_width, nq, nkv, hd, window, pool_rows;
     float scale_log2;         // softmax scale times log2(e)
+    unsigned long long* trace;   // for measurements (may be null): [cta][8] sums of time (ns) that row 0's thread spent
+                                 // waiting for S, reading it, writing P, rescaling O, waiting for the last product;
+                                 // then blocks, total time, start
 };
 
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
@@ -76,6 +84,32 @@ __device__ __forceinline__ uint64_t smem_desc_mn(uint32_t addr, uint32_t lbo, ui
     return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) |
            ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
+// 32 consecutive columns of this thread's TMEM lane
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, "
+        "%24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, "
+        "%25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tc_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&v);
@@ -89,19 +123,19 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     uint8_t* s_q = smem;                              // [2 slices][128 rows][128 B]
     uint8_t* s_k = s_q + 2 * SLICE;                   // [STAGES][2 slices][128 keys][128 B]
     uint8_t* s_v = s_k + STAGES * 2 * SLICE;          // [STAGES][2 slices of 64 dims][128 keys][128 B]
-    uint8_t* s_p = s_v + STAGES * 2 * SLICE;          // [2 slices of 64 keys][128 rows][128 B]
-    uint64_t* bars = (uint64_t*)(s_p + 2 * SLICE);
-    // bars: q_full, kv_full[2], kv_empty[2], s_full[2], p_full, o_full, o_empty
-    uint32_t* tmem_slot = (uint32_t*)(bars + 10);
+    uint8_t* s_p = s_v + STAGES * 2 * SLICE;          // [2 buffers][2 slices of 64 keys][128 rows][128 B]
+    uint64_t* bars = (uint64_t*)(s_p + 2 * 2 * SLICE);
+    // bars: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], pv_done[2]
+    uint32_t* tmem_slot = (uint32_t*)(bars + 15);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t q_full = smem_u32(bars), kv_full0 = smem_u32(bars + 1), kv_empty0 = smem_u32(bars + 3);
-    const uint32_t s_full0 = smem_u32(bars + 5), p_full = smem_u32(bars + 7), o_full = smem_u32(bars + 8);
-    const uint32_t o_empty = smem_u32(bars + 9);
+    const uint32_t q_full = smem_u32(bars), k_full0 = smem_u32(bars + 1), k_empty0 = smem_u32(bars + 3);
+    const uint32_t v_full0 = smem_u32(bars + 5), v_empty0 = smem_u32(bars + 7);
+    const uint32_t s_full0 = smem_u32(bars + 9), p_full0 = smem_u32(bars + 11), pv_done0 = smem_u32(bars + 13);
 
     // The CTA's rows and its range of key blocks.  The step's geometry is final before the step's first kernel
     // starts (common.cuh), so it is read ahead of the wait.
-    const int seq = blockIdx.z, kvh = blockIdx.y, tile = blockIdx.x;
+    const int seq = blockIdx.z, kvh = blockIdx.y, tile = gridDim.x - 1 - blockIdx.x;     // long tiles first
     const int G = p.nq / p.nkv, T = ROWS / G;         // T tokens of G heads each fill the tile's rows
     const int q_len = p.seq_qlen[seq], q_start = p.seq_start[seq], pos0 = p.seq_pos0[seq];
     const int t0 = tile * T;
@@ -117,13 +151,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(kv_full0 + 8 * s, 1);
-            mbar_init(kv_empty0 + 8 * s, 1);
+            mbar_init(k_full0 + 8 * s, 1);
+            mbar_init(k_empty0 + 8 * s, 1);
+            mbar_init(v_full0 + 8 * s, 1);
+            mbar_init(v_empty0 + 8 * s, 1);
             mbar_init(s_full0 + 8 * s, 1);
+            mbar_init(p_full0 + 8 * s, 128);
+            mbar_init(pv_done0 + 8 * s, 1);
         }
-        mbar_init(p_full, 128);
-        mbar_init(o_full, 1);
-        mbar_init(o_empty, 128);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -153,21 +188,28 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             bool ok = true;
             for (int i = 0; i < n_blocks && ok; ++i) {
                 const int kb = kb_begin + i, stage = i & 1;
-                if (!(ok = mbar_wait(kv_empty0 + 8 * stage, ((i >> 1) & 1) ^ 1, p.status, 1))) break;
-                mbar_expect_tx(kv_full0 + 8 * stage, (uint32_t)slices * 2 * 2 * PAGE * 128);
+                int rows[2];
                 for (int h = 0; h < 2; ++h) {
                     const int lp = kb * 2 + h;
-                    int row = p.pool_rows;                                   // beyond the pool: the box is filled with zeros
+                    rows[h] = p.pool_rows;                                   // beyond the pool: the box is filled with zeros
                     if (lp * PAGE <= pos_hi && lp < p.table_width) {
                         const int page = table[lp];
-                        if (page >= 0) row = page * PAGE;
-                    }
-                    for (int s = 0; s < slices; ++s) {
-                        const uint32_t off = (uint32_t)((stage * 2 + s) * SLICE + h * PAGE * 128);
-                        tma_load_3d(smem_u32(s_k) + off, &map_k, s * 64, kvh, row, kv_full0 + 8 * stage);
-                        tma_load_3d(smem_u32(s_v) + off, &map_v, s * 64, kvh, row, kv_full0 + 8 * stage);
+                        if (page >= 0) rows[h] = page * PAGE;
                     }
                 }
+                // K is free again as soon as its scores are done, V only after the second product: rings of their own
+                if (!(ok = mbar_wait(k_empty0 + 8 * stage, ((i >> 1) & 1) ^ 1, p.status, 1))) break;
+                mbar_expect_tx(k_full0 + 8 * stage, (uint32_t)slices * 2 * PAGE * 128);
+                for (int h = 0; h < 2; ++h)
+                    for (int s = 0; s < slices; ++s)
+                        tma_load_3d(smem_u32(s_k) + (uint32_t)((stage * 2 + s) * SLICE + h * PAGE * 128), &map_k, s * 64, kvh,
+                                    rows[h], k_full0 + 8 * stage);
+                if (!(ok = mbar_wait(v_empty0 + 8 * stage, ((i >> 1) & 1) ^ 1, p.status, 1))) break;
+                mbar_expect_tx(v_full0 + 8 * stage, (uint32_t)slices * 2 * PAGE * 128);
+                for (int h = 0; h < 2; ++h)
+                    for (int s = 0; s < slices; ++s)
+                        tma_load_3d(smem_u32(s_v) + (uint32_t)((stage * 2 + s) * SLICE + h * PAGE * 128), &map_v, s * 64, kvh,
+                                    rows[h], v_full0 + 8 * stage);
             }
         }
     } else if (warp == 1) {
@@ -175,8 +217,20 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const uint32_t idesc_qk = instr_desc(ROWS, KEYS);
             const uint32_t idesc_pv = instr_desc(ROWS, p.hd) | (1u << 16);   // B is MN-major
             const int k_steps = p.hd / 16;                                   // of the first product
+            bool ok = mbar_wait(q_full, 0, p.status, 2);
+            unsigned long long m_spent[5] = {0, 0, 0, 0, 0}, m_mark = p.trace != nullptr ? global_ns() : 0;
+            auto mlap = [&](int which) {
+                if (p.trace != nullptr) {
+                    const unsigned long long now = global_ns();
+                    m_spent[which] += now - m_mark;
+                    m_mark = now;
+                }
+            };
             auto issue_qk = [&](int i) {
                 const int stage = i & 1;
+                if (!(ok = mbar_wait(k_full0 + 8 * stage, (i >> 1) & 1, p.status, 3))) return;
+                mlap(0);
+                tc_fence_after();
                 const uint32_t d = tmem_s + (uint32_t)(i & 1) * KEYS;
                 for (int ks = 0; ks < k_steps; ++ks) {
                     const int s = ks >> 2, k = ks & 3;
@@ -185,35 +239,36 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     tc_mma(d, da, db, idesc_qk, ks > 0 ? 1u : 0u);
                 }
                 tc_commit(s_full0 + 8 * (i & 1));
+                tc_commit(k_empty0 + 8 * stage);
+                mlap(1);
             };
-            bool ok = mbar_wait(q_full, 0, p.status, 2);
-            if (ok) ok = mbar_wait(kv_full0, 0, p.status, 3);
-            if (ok) {
-                tc_fence_after();
-                issue_qk(0);
-            }
+            if (ok) issue_qk(0);
             for (int i = 0; i < n_blocks && ok; ++i) {
                 const int stage = i & 1;
-                if (i + 1 < n_blocks) {
-                    // S of block i+1 goes to the other buffer, which the rows have read (p_full of block i-1 was
-                    // waited for in the round before)
-                    if (!(ok = mbar_wait(kv_full0 + 8 * ((i + 1) & 1), ((i + 1) >> 1) & 1, p.status, 3))) break;
-                    tc_fence_after();
-                    issue_qk(i + 1);
-                }
-                if (!(ok = mbar_wait(p_full, i & 1, p.status, 4))) break;
-                if (i > 0 && !(ok = mbar_wait(o_empty, (i - 1) & 1, p.status, 5))) break;
+                // S of block i+1 goes to the other buffer, which the rows have read (p_full of block i-1 was waited
+                // for in the round before)
+                if (i + 1 < n_blocks) issue_qk(i + 1);
+                if (!ok) break;
+                if (!(ok = mbar_wait(v_full0 + 8 * stage, (i >> 1) & 1, p.status, 3))) break;
+                mlap(2);
+                if (!(ok = mbar_wait(p_full0 + 8 * (i & 1), (i >> 1) & 1, p.status, 4))) break;
+                mlap(3);
                 tc_fence_after();
                 // keys of this block that some row may see, in steps of 16
                 const int keys_here = min(KEYS, pos_hi - (kb_begin + i) * KEYS + 1);
                 const int pv_steps = (keys_here + 15) / 16;
                 for (int ks = 0; ks < pv_steps; ++ks) {
-                    const uint64_t da = smem_desc(smem_u32(s_p + (ks >> 2) * SLICE)) + 2 * (ks & 3);
+                    const uint64_t da = smem_desc(smem_u32(s_p + ((i & 1) * 2 + (ks >> 2)) * SLICE)) + 2 * (ks & 3);
                     const uint64_t db = smem_desc_mn(smem_u32(s_v + stage * 2 * SLICE) + ks * 16 * 128, SLICE, 1024);
-                    tc_mma(tmem_o, da, db, idesc_pv, ks > 0 ? 1u : 0u);
+                    tc_mma(tmem_o, da, db, idesc_pv, (i > 0 || ks > 0) ? 1u : 0u);
                 }
-                tc_commit(o_full);
-                tc_commit(kv_empty0 + 8 * stage);
+                tc_commit(pv_done0 + 8 * (i & 1));
+                tc_commit(v_empty0 + 8 * stage);
+                mlap(4);
+            }
+            if (p.trace != nullptr) {
+                unsigned long long* at = p.trace + ((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 + 8;
+                for (int k = 0; k < 5; ++k) at[k] = m_spent[k];
             }
         }
     } else {
@@ -224,71 +279,119 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         const int pos_r = valid ? pos0 + t0 + t : -1;      // -1: every key is masked
         const int lo_r = (valid && p.window > 0) ? max(0, pos_r - p.window + 1) : 0;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-        float o[128];
-#pragma unroll
-        for (int i = 0; i < 128; ++i) o[i] = 0.f;
-        float m_run = -INFINITY, l_run = 0.f;
+        float m_run = -INFINITY, l_run = 0.f;              // the maximum that P is taken against, and the sum of P
         bool ok = true;
+        unsigned long long spent[5] = {0, 0, 0, 0, 0};
+        const bool tracing = p.trace != nullptr && r == 0;
+        unsigned long long t_mark = tracing ? global_ns() : 0, t_begin = t_mark;
+        auto lap = [&](int which) {
+            if (tracing) {
+                const unsigned long long now = global_ns();
+                spent[which] += now - t_mark;
+                t_mark = now;
+            }
+        };
         for (int i = 0; i < n_blocks && ok; ++i) {
             const int kb = kb_begin + i, stage = i & 1;
             const int j0 = kb * KEYS;
             if (!(ok = mbar_wait(s_full0 + 8 * (i & 1), (i >> 1) & 1, p.status, 6))) break;
             tc_fence_after();
+            lap(0);
+            // Two passes over the row of S in tensor memory, 32 columns at a time, as compact loops (the fully
+            // unrolled form, with the row held in 128 registers, ran three times slower: it does not fit the
+            // instruction cache).  Masked and unmasked blocks have loops of their own; most blocks need no mask.
             const uint32_t s_addr = tmem_s + lane_addr + (uint32_t)(i & 1) * KEYS;
-            const bool need_mask = j0 + KEYS - 1 > pos0 + t0 || (p.window > 0 && j0 < pos_hi - p.window + 1) || !valid;
-            // the row's maximum over the block
+            // (the choice must be the same for a whole warp: the loads from tensor memory are warp-wide instructions)
+            const bool need_mask = __any_sync(0xffffffffu, j0 + KEYS - 1 > pos0 + t0 ||
+                                                               (p.window > 0 && j0 < pos_hi - p.window + 1) || !valid);
             float mx = -INFINITY;
+            auto max_pass = [&](auto masked) {
 #pragma unroll 1
-            for (int c = 0; c < KEYS / 16; ++c) {
-                uint32_t raw[16];
-                tc_ld16(s_addr + c * 16, raw);
-                tc_ld_wait();
+                for (int c = 0; c < KEYS / 32; ++c) {
+                    uint32_t raw[32];
+                    tc_ld32(s_addr + c * 32, raw);
+                    tc_ld_wait();
+                    const int hi = pos_r - (j0 + c * 32), lo = lo_r - (j0 + c * 32);    // columns hi < j or j < lo are masked
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    float v = __uint_as_float(raw[j]) * p.scale_log2;
-                    if (need_mask) {
-                        const int key = j0 + c * 16 + j;
-                        if (key > pos_r || key < lo_r) v = -INFINITY;
+                    for (int j = 0; j < 32; ++j) {
+                        float v = __uint_as_float(raw[j]) * p.scale_log2;
+                        if (decltype(masked)::value && (j > hi || j < lo)) v = -INFINITY;
+                        mx = fmaxf(mx, v);
                     }
-                    mx = fmaxf(mx, v);
+                }
+            };
+            if (need_mask) max_pass(std::true_type{});
+            else max_pass(std::false_type{});
+            lap(1);
+            // The reference maximum moves only when the true one has grown by more than 8; O is rescaled then.
+            // tcgen05.ld and .st are warp-wide, so a warp rescales if any of its rows must.
+            const bool grow = mx > m_run + 8.f;            // also the first finite maximum (m_run = -inf)
+            if (__any_sync(0xffffffffu, grow)) {
+                const float alpha = grow ? exp2f(m_run - mx) : 1.f;      // 0 for a row that had seen no key
+                if (grow) {
+                    m_run = mx;
+                    l_run *= alpha;
+                }
+                if (i > 0) {
+                    // every product into O so far must be done
+                    if (!(ok = mbar_wait(pv_done0 + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1, p.status, 8))) break;
+                    tc_fence_after();
+#pragma unroll 1
+                    for (int c = 0; c < 4; ++c) {
+                        if (c * 32 < p.hd) {
+                            uint32_t raw[32];
+                            tc_ld32(tmem_o + lane_addr + c * 32, raw);
+                            tc_ld_wait();
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) raw[j] = __float_as_uint(__uint_as_float(raw[j]) * alpha);
+                            tc_st32(tmem_o + lane_addr + c * 32, raw);
+                        }
+                    }
+                    tc_st_wait();
                 }
             }
-            const float m_new = fmaxf(m_run, mx);
-            const float m_use = m_new == -INFINITY ? 0.f : m_new;
-            const float alpha = exp2f(m_run - m_use);          // 0 while the row has seen no key
-            m_run = m_new;
-            // exponentials: P into shared memory (bf16, the swizzled K-major layout), their sum into l
+            lap(3);
+            // P buffer i & 1 was read by the product of block i - 2
+            if (i >= 2 && !(ok = mbar_wait(pv_done0 + 8 * (i & 1), ((i - 2) >> 1) & 1, p.status, 5))) break;
+            const float m_use = m_run == -INFINITY ? 0.f : m_run;
             float sum = 0.f;
+            uint8_t* p_line = s_p + (i & 1) * 2 * SLICE + r * 128;
+            auto exp_pass = [&](auto masked) {
 #pragma unroll 1
-            for (int c = 0; c < KEYS / 16; ++c) {
-                uint32_t raw[16];
-                tc_ld16(s_addr + c * 16, raw);
-                tc_ld_wait();
-                float pe[16];
+                for (int c = 0; c < KEYS / 32; ++c) {
+                    uint32_t raw[32];
+                    tc_ld32(s_addr + c * 32, raw);
+                    tc_ld_wait();
+                    const int hi = pos_r - (j0 + c * 32), lo = lo_r - (j0 + c * 32);
+                    uint32_t packed[16];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    float v = __uint_as_float(raw[j]) * p.scale_log2;
-                    if (need_mask) {
-                        const int key = j0 + c * 16 + j;
-                        if (key > pos_r || key < lo_r) v = -INFINITY;
+                    for (int j = 0; j < 32; j += 2) {
+                        float v0 = __uint_as_float(raw[j]) * p.scale_log2, v1 = __uint_as_float(raw[j + 1]) * p.scale_log2;
+                        if (decltype(masked)::value) {
+                            if (j > hi || j < lo) v0 = -INFINITY;
+                            if (j + 1 > hi || j + 1 < lo) v1 = -INFINITY;
+                        }
+                        const float e0 = exp2f(v0 - m_use), e1 = exp2f(v1 - m_use);
+                        sum += e0;
+                        sum += e1;
+                        packed[j >> 1] = pack2(e0, e1);
                     }
-                    pe[j] = exp2f(v - m_use);
-                    sum += pe[j];
+                    // 32 keys = four 16-byte chunks of the row's 128-byte line in slice c / 2
+                    uint8_t* line = p_line + (c >> 1) * SLICE;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        *(uint4*)(line + (((((c & 1) << 2) + q) ^ (r & 7)) << 4)) =
+                            make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
                 }
-                // 16 keys = two 16-byte chunks of the row's 128-byte line in slice c / 4
-                uint8_t* line = s_p + (c >> 2) * SLICE + r * 128;
-                const int ch = (c & 3) * 2;
-                *(uint4*)(line + ((ch ^ (r & 7)) << 4)) =
-                    make_uint4(pack2(pe[0], pe[1]), pack2(pe[2], pe[3]), pack2(pe[4], pe[5]), pack2(pe[6], pe[7]));
-                *(uint4*)(line + (((ch + 1) ^ (r & 7)) << 4)) =
-                    make_uint4(pack2(pe[8], pe[9]), pack2(pe[10], pe[11]), pack2(pe[12], pe[13]), pack2(pe[14], pe[15]));
-            }
-            l_run = l_run * alpha + sum;
+            };
+            if (need_mask) exp_pass(std::true_type{});
+            else exp_pass(std::false_type{});
+            l_run += sum;
             if (kb == kb_end) {
                 // keys past the last one that any row may see: their V rows may hold anything; zero them
                 const int key = j0 + r;
                 if (key > pos_hi) {
-                    if (!(ok = mbar_wait(kv_full0 + 8 * stage, (i >> 1) & 1, p.status, 7))) break;
+                    if (!(ok = mbar_wait(v_full0 + 8 * stage, (i >> 1) & 1, p.status, 7))) break;
                     for (int s = 0; s < slices; ++s) {
                         uint4* line = (uint4*)(s_v + (stage * 2 + s) * SLICE + r * 128);
 #pragma unroll
@@ -298,32 +401,43 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             }
             tc_fence_before();
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_arrive(p_full);
-            // O_blk = P V of this block, added to the row
-            if (!(ok = mbar_wait(o_full, i & 1, p.status, 8))) break;
-            tc_fence_after();
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                if (c * 16 < p.hd) {
-                    uint32_t raw[16];
-                    tc_ld16(tmem_o + lane_addr + c * 16, raw);
-                    tc_ld_wait();
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) o[c * 16 + j] = o[c * 16 + j] * alpha + __uint_as_float(raw[j]);
-                }
-            }
-            tc_fence_before();
-            mbar_arrive(o_empty);
+            mbar_arrive(p_full0 + 8 * (i & 1));
+            lap(2);
         }
-        if (ok && valid) {
+        // the last product; then the row's output
+        if (ok) ok = mbar_wait(pv_done0 + 8 * ((n_blocks - 1) & 1), ((n_blocks - 1) >> 1) & 1, p.status, 8);
+        tc_fence_after();
+        lap(4);
+        if (ok) {
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             bf16* dst = p.out + ((size_t)(q_start + t0 + t) * p.nq + (size_t)kvh * G + g) * p.hd;
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
-                if (c * 8 < p.hd)
-                    *(uint4*)(dst + c * 8) = make_uint4(pack2(o[c * 8] * inv, o[c * 8 + 1] * inv), pack2(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv),
-                                                        pack2(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv), pack2(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv));
+            for (int c = 0; c < 4; ++c) {
+                if (c * 32 < p.hd) {                                   // uniform: the load is warp-wide
+                    uint32_t raw[32];
+                    tc_ld32(tmem_o + lane_addr + c * 32, raw);
+                    tc_ld_wait();
+                    if (valid) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            if (c * 32 + q * 8 < p.hd) {
+                                float x[8];
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) x[j] = __uint_as_float(raw[q * 8 + j]) * inv;
+                                *(uint4*)(dst + c * 32 + q * 8) =
+                                    make_uint4(pack2(x[0], x[1]), pack2(x[2], x[3]), pack2(x[4], x[5]), pack2(x[6], x[7]));
+                            }
+                        }
+                    }
+                }
             }
+        }
+        if (tracing) {
+            unsigned long long* at = p.trace + ((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16;
+            for (int k = 0; k < 5; ++k) at[k] = spent[k];
+            at[5] = (unsigned long long)n_blocks;
+            at[6] = global_ns() - t_begin;
+            at[7] = t_begin;
         }
     }
     tc_fence_before();
@@ -363,9 +477,16 @@ int encode(CUtensorMap* map, const void* base, int rank, const cuuint64_t* dims,
     return FR_OK;
 }
 
-constexpr int SMEM_BYTES = (2 + 2 * STAGES * 2 + 2) * SLICE + 1024 + 256;
+constexpr int SMEM_BYTES = (2 + 2 * STAGES * 2 + 2 * 2) * SLICE + 1024 + 256;
 
 }  // namespace
+
+// For measurements: launches after this call record per CTA where the thread of its first row spent its time.
+static unsigned long long* attention_tc_trace = nullptr;
+FR_EXPORT int attention_tc_set_trace(unsigned long long* trace) {
+    attention_tc_trace = trace;
+    return FR_OK;
+}
 
 // What the kernel takes: bf16, head sizes in steps of 16 up to 128, 64-token pages, at most 128 heads per kv head,
 // query rows that start on 16-byte boundaries.
@@ -411,6 +532,7 @@ FR_EXPORT int attention_tc(const void* q, int q_stride, int total_rows, void* ou
     p.out = (bf16*)out; p.block_table = block_table; p.seq_start = seq_start; p.seq_qlen = seq_qlen;
     p.seq_pos0 = seq_pos0; p.seq_live = seq_live; p.status = status; p.table_width = table_width; p.nq = nq;
     p.nkv = nkv; p.hd = hd; p.window = window; p.pool_rows = pool_pages * PAGE; p.scale_log2 = scale * LOG2E;
+    p.trace = attention_tc_trace;
     static bool configured = false;
     if (!configured) {
         FR_CUDA(cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
