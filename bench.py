@@ -269,6 +269,34 @@ def cta_trace(eng, batch):
                               "warps merged", "cluster barrier passed", "splits merged"]):
         col = (a[live, j] - done) / 1000.0
         print("  %-24s %6.1f %6.1f %6.1f" % (what, np.nanmin(col), np.nanmedian(col), np.nanmax(col)))
+    dec.close()
+    for s in slots:
+        eng.free_slot(s)
+
+    # the prompt attention of the last layer: where the thread of a CTA's first row and the thread that issues the
+    # products spend the time of a block of 128 keys
+    (p,) = random_prompts(1, PREFILL_TOKENS, eng.vocab_size, 99)
+    for _ in range(2):
+        s = eng.alloc_slot()
+        eng.step([s], [p], [[PREFILL_TOKENS - 1]])
+        eng.free_slot(s)
+    tc = torch.zeros((4096, 16), dtype=torch.int64, device="cuda:0")
+    set_tc = lib.family("attention_tc").declare("attention_tc_set_trace", [lib.P])
+    set_tc(tc.data_ptr())
+    s = eng.alloc_slot()
+    eng.step([s], [p], [[PREFILL_TOKENS - 1]])
+    torch.cuda.synchronize()
+    set_tc(None)
+    eng.free_slot(s)
+    t = tc.cpu().numpy().astype(np.float64)
+    t = t[t[:, 5] > 0]
+    blocks = t[:, 5].sum()
+    print("prompt attention, %d tokens: %d CTAs, %d blocks of 128 keys; us per block: " % (PREFILL_TOKENS, len(t), blocks)
+          + ", ".join("%s %.2f" % (what, t[:, k].sum() / blocks / 1000.0) for k, what in
+                      ((0, "row waits for S"), (1, "reads S, maximum"), (2, "exponentials and P"), (3, "rescales O"),
+                       (4, "waits for the last product"), (8, "issuer waits for K"), (9, "issues Q K^T"),
+                       (10, "waits for V"), (11, "waits for P"), (12, "issues P V")))
+          + "; kernel %.1f us" % (((t[:, 7] + t[:, 6]).max() - t[:, 7].min()) / 1000.0))
     return 0
 
 
