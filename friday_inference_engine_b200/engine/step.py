@@ -20,8 +20,6 @@ Host-side layout of a pass (int32, sent to the device in one copy):
 import numpy as np
 import torch
 
-from ..cache import CacheError
-
 
 class StepError(ValueError):
     """A step that cannot be run: unknown token id, a sequence too long, a bad request."""
