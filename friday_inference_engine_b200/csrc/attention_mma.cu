@@ -141,11 +141,6 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
     const bool live = p.seq_live == nullptr || p.seq_live[q_start] >= 0;
     __syncthreads();                                   // s_pages
 
-    fr_pdl_wait();
-    fr_pdl_launch();
-    mark(p, 1);
-    if (r0 >= n_rows) return;
-
     // Range of key blocks for this CTA.
     const int t_first = r0 / G, t_last = min((r0 + ROWS_CTA - 1) / G, q_len - 1);
     const int pos_hi = pos0 + t_last;                 // the farthest key any row of the CTA may see
@@ -156,7 +151,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
         kb_begin += split * per;
         kb_end = min(kb_begin + per - 1, kb_end);
     }
-    if (!live) kb_end = kb_begin - 1;                 // nothing to read: the output is zero
+    if (!live || r0 >= n_rows) kb_end = kb_begin - 1;  // nothing to read: the output is zero (or there is none)
 
     auto load_q = [&]() {
         for (int c = tid; c < ROWS_CTA * CHUNKS; c += WARPS * 32) {
@@ -184,6 +179,26 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
         }
     };
 
+    // Keys and values of earlier steps are final before this step's first kernel starts; only the blocks from the
+    // step's own first position on are written by the kernel before this one.  One-token steps therefore request
+    // their first blocks ahead of the wait, where they can; the queries and the rest follow it.
+    const int first_fresh = pos0 / BLOCK_N;            // blocks from here on hold rows of this step
+    bool early[NS - 1];
+#pragma unroll
+    for (int st = 0; st < NS - 1; ++st) {
+        early[st] = KEYS_MODE && kb_begin + st <= kb_end && kb_begin + st < first_fresh;
+        if (early[st]) load_kv(kb_begin + st, st);
+    }
+    cp_commit();                                       // group A: what could be asked for ahead
+
+    fr_pdl_wait();
+    fr_pdl_launch();
+    mark(p, 1);
+    if (r0 >= n_rows) {
+        cp_wait<0>();
+        return;
+    }
+
     // This thread's two rows (fragment layout of mma: rows lane/4 and lane/4 + 8 of the warp's 16).
     const int row_base = KEYS_MODE ? 0 : warp * 16;
     const int key_base = KEYS_MODE ? warp * 16 : 0;
@@ -210,10 +225,9 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
 
     load_q();
 #pragma unroll
-    for (int st = 0; st < NS - 1; ++st) {
-        if (kb_begin + st <= kb_end) load_kv(kb_begin + st, st);
-        cp_commit();                                   // group st holds block st (and the queries, in group 0)
-    }
+    for (int st = 0; st < NS - 1; ++st)
+        if (!early[st] && kb_begin + st <= kb_end) load_kv(kb_begin + st, st);
+    cp_commit();                                       // group B: the queries and the rest of the first blocks
 
     mark(p, 2);
     const uint32_t q_addr = (uint32_t)__cvta_generic_to_shared(s_q);
@@ -225,7 +239,10 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
             const int ahead = buf + NS - 1 >= NS ? buf - 1 : buf + NS - 1;      // the buffer used one block ago
             if (kb + NS - 1 <= kb_end) load_kv(kb + NS - 1, ahead);
             cp_commit();
-            cp_wait<NS - 1>();                         // everything but the newest NS-1 groups: block kb is here
+            // all but the newest groups: block kb is here (the first blocks and the queries sit in groups A and B,
+            // which only this round's group follows; later blocks have a group each)
+            if (kb == kb_begin) cp_wait<1>();
+            else cp_wait<NS - 1>();
         }
         __syncthreads();
         if (kb == kb_begin) mark(p, 3);
