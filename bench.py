@@ -139,8 +139,17 @@ def time_decode(eng, batch, steps, warmup, seed):
     return ms / steps, launches, mean_len
 
 
+E2E_SETTLE_STEPS = 32
+
+
 def time_e2e(eng, batch, steps, seed):
-    """Engine.generate with host tokens in and out; decode steps timed from the first drawn token on."""
+    """Engine.generate with host tokens in and out: every decode step copies its token ids in from pinned memory and
+    the chosen ids out.  Returns tokens/s over the last `steps` decode steps and over the first `steps` ones.
+
+    The first decode steps after the prompts run slower than the rest: 8 x 1,024 prompt tokens drive the GPU into its
+    power cap, and the SM clock needs some 15 steps of the much lighter decoding to come back (4.1 ms a step, then
+    3.16 ms).  The device-timed value does not see this (graph capture sits between its prompts and its timed steps),
+    so the headline figure skips E2E_SETTLE_STEPS steps; the figure from the first token on is reported beside it."""
     import torch
     prompts = random_prompts(batch, PROMPT, eng.vocab_size, seed)
     marks = []
@@ -151,9 +160,10 @@ def time_e2e(eng, batch, steps, seed):
     eng.generate(prompts, max_new_tokens=4, temperature=0.0, ignore_eos=True)       # warm-up: captures the step
     marks.clear()
     torch.cuda.synchronize()
-    out = eng.generate(prompts, max_new_tokens=steps + 1, temperature=0.0, ignore_eos=True, on_step=on_step)
-    assert all(len(g.tokens) == steps + 1 for g in out)
-    return batch * steps / (marks[-1] - marks[0])
+    total = E2E_SETTLE_STEPS + steps
+    out = eng.generate(prompts, max_new_tokens=total + 1, temperature=0.0, ignore_eos=True, on_step=on_step)
+    assert all(len(g.tokens) == total + 1 for g in out)
+    return batch * steps / (marks[-1] - marks[-1 - steps]), batch * steps / (marks[steps] - marks[0])
 
 
 def time_prefill(eng, warmup, reps):
@@ -388,10 +398,11 @@ def main():
         flops += layers * 4.0 * qd * PREFILL_TOKENS * PREFILL_TOKENS / 2.0
         line["prefill"] = {"value": round(PREFILL_TOKENS * 1000.0 / ms_pre, 1), "tokens": PREFILL_TOKENS,
                            "ms": round(ms_pre, 3), "frac": round(flops / (ms_pre * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
-        e2e = time_e2e(eng, args.batch, min(args.steps, 64), seed=1)
+        e2e, e2e_from_first = time_e2e(eng, args.batch, min(args.steps, 64), seed=1)
         # every decode step of generate() copies the step's token ids in from pinned memory and the chosen ids out
         line["e2e"] = {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": 4 * args.batch,
-                       "d2h_bytes_per_step": 4 * args.batch}
+                       "d2h_bytes_per_step": 4 * args.batch, "settle_steps": E2E_SETTLE_STEPS,
+                       "from_first_token": round(e2e_from_first, 1)}
     print(json.dumps(line))
     return 0
 
