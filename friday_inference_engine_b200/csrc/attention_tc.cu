@@ -6,25 +6,27 @@
 // R = tq*G + g rows: attention_kernels.cu:493-499).  Blocks of 128 keys are two pages of the cache.
 //
 //   warp 0      TMA producer: the queries (a 4-d box [64 dims][G heads][1][T tokens] per 64-dim slice lands as
-//               rows t*G + g, 128-byte swizzle), then per block K and V pages into a ring of two stages.  A page
-//               that the block does not need, or that the table does not name, is loaded from beyond the pool's
-//               last row, which fills zeros.
-//   warp 1      allocates tensor memory; one lane issues S = Q K^T (M = 128 rows, N = 128 keys, both operands
-//               K-major) into one of two S buffers, and O += P V (A = P from shared memory, K-major; B = V as it
-//               lies in the cache, [keys][dims] = MN-major) into the O columns, which stay in tensor memory for
-//               the whole CTA.
-//   warps 2-5   one thread per row (its TMEM lane): reads its row of S once into registers, keeps the running
-//               maximum and sum, writes P (bf16) into one of two shared-memory buffers in the swizzled layout the
-//               tensor core reads.  The maximum that P is taken against only moves when a row's true maximum has
-//               grown by more than 8 (in log2 units; P then stays below 2^8 and the sums remain exact for that
-//               reference); only then is O rescaled, in tensor memory.  At the end the row's O is divided by its sum.
+//               rows t*G + g, 128-byte swizzle), then per block the two K pages and the two V pages.  K's buffer is
+//               free again once the scores are done, V's after the second product.  A page that the block does
+//               not need, or that the table does not name, is loaded from beyond the pool's last row, which fills
+//               zeros.
+//   warp 1      allocates tensor memory (256 columns: S, and O); one lane issues S = Q K^T (M = 128 rows, N = 128
+//               keys, both operands K-major from shared memory) and O += P V (A = P from tensor memory, where it
+//               lies over the first half of S's columns; B = V as it lies in the cache, [keys][dims] = MN-major).
+//   warps 2-5   one thread per row (its TMEM lane): reads its row of S twice from tensor memory (maximum, then
+//               exponentials), keeps the running maximum and sum, and writes P (bf16, two to a column) back into
+//               tensor memory behind its reading.  The maximum that P is taken against only moves when a row's true
+//               maximum has grown by more than 8 (in log2 units; P then stays below 2^8 and the sums remain exact
+//               for that reference); only then is O rescaled, in tensor memory.  At the end the row's O is divided
+//               by its sum.
 //
-// QK^T of block i+1 and P V of block i-1 run while the rows of block i are exponentiated.  Scores, softmax and sums
-// are fp32; P is rounded to bf16 for the second product, as the mma.sync kernel does.  Rows of V past the last key
-// that any row of the CTA may see are zeroed in shared memory before the product (their P is zero, but zero times a
-// stale NaN is not); stale K only reaches scores that the mask replaces.  Long tiles (late tokens) are launched
-// first.  Every wait on an mbarrier is bounded (two seconds), then a code goes to `status` and all roles leave their
-// loops.
+// Neither P nor O ever leaves tensor memory before the output is written.  A CTA needs 97 KB of shared memory and
+// half the tensor memory, so two share an SM: while the rows of one exponentiate, the products of the other run.
+// Scores, softmax and sums are fp32; P is rounded to bf16 for the second product, as the mma.sync kernel does.
+// Rows of V past the last key that any row of the CTA may see are zeroed in shared memory before the product (their
+// P is zero, but zero times a stale NaN is not); stale K only reaches scores that the mask replaces.  Long tiles (late
+// tokens) are launched first.  Every wait on an mbarrier is bounded (two seconds), then a code goes to `status` and
+// all roles leave their loops.
 //
 // Head sizes: multiples of 16 up to 128.  One-token steps keep the mma.sync kernel (attention_mma.cu), whose rows
 // of a CTA share a token.
@@ -47,7 +49,7 @@ constexpr int ROWS = 128;                 // rows of a CTA = M of the instructio
 constexpr int KEYS = 128;                 // keys of a block = two cache pages
 constexpr int PAGE = 64;
 constexpr int SLICE = ROWS * 128;         // bytes of 128 rows of 64 bf16 (one 128-byte swizzle row each)
-constexpr int STAGES = 2;
+constexpr int TMEM_COLS = 256;           // S (and P over it) | O
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct TcArgs {
@@ -115,23 +117,41 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-__global__ void __launch_bounds__(THREADS, 1)
+// 16 consecutive columns of this thread's TMEM lane, written
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand lies in tensor memory (lane = row, two bf16 per 32-bit column)
+__device__ __forceinline__ void tc_mma_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__global__ void __launch_bounds__(THREADS, 2)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, const TcArgs p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* s_q = smem;                              // [2 slices][128 rows][128 B]
-    uint8_t* s_k = s_q + 2 * SLICE;                   // [STAGES][2 slices][128 keys][128 B]
-    uint8_t* s_v = s_k + STAGES * 2 * SLICE;          // [STAGES][2 slices of 64 dims][128 keys][128 B]
-    uint8_t* s_p = s_v + STAGES * 2 * SLICE;          // [2 buffers][2 slices of 64 keys][128 rows][128 B]
-    uint64_t* bars = (uint64_t*)(s_p + 2 * 2 * SLICE);
-    // bars: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], pv_done[2]
-    uint32_t* tmem_slot = (uint32_t*)(bars + 15);
+    uint8_t* s_k = s_q + 2 * SLICE;                   // [2 slices][128 keys][128 B]
+    uint8_t* s_v = s_k + 2 * SLICE;                   // [2 slices of 64 dims][128 keys][128 B]
+    uint64_t* bars = (uint64_t*)(s_v + 2 * SLICE);
+    // bars: q_full, k_full, k_empty, v_full, v_empty, s_full, p_full, pv_done
+    uint32_t* tmem_slot = (uint32_t*)(bars + 8);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t q_full = smem_u32(bars), k_full0 = smem_u32(bars + 1), k_empty0 = smem_u32(bars + 3);
-    const uint32_t v_full0 = smem_u32(bars + 5), v_empty0 = smem_u32(bars + 7);
-    const uint32_t s_full0 = smem_u32(bars + 9), p_full0 = smem_u32(bars + 11), pv_done0 = smem_u32(bars + 13);
+    const uint32_t q_full = smem_u32(bars), k_full = smem_u32(bars + 1), k_empty = smem_u32(bars + 2);
+    const uint32_t v_full = smem_u32(bars + 3), v_empty = smem_u32(bars + 4);
+    const uint32_t s_full = smem_u32(bars + 5), p_full = smem_u32(bars + 6), pv_done = smem_u32(bars + 7);
 
     // The CTA's rows and its range of key blocks.  The step's geometry is final before the step's first kernel
     // starts (common.cuh), so it is read ahead of the wait.
@@ -150,21 +170,19 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(k_full0 + 8 * s, 1);
-            mbar_init(k_empty0 + 8 * s, 1);
-            mbar_init(v_full0 + 8 * s, 1);
-            mbar_init(v_empty0 + 8 * s, 1);
-            mbar_init(s_full0 + 8 * s, 1);
-            mbar_init(p_full0 + 8 * s, 128);
-            mbar_init(pv_done0 + 8 * s, 1);
-        }
+        mbar_init(k_full, 1);
+        mbar_init(k_empty, 1);
+        mbar_init(v_full, 1);
+        mbar_init(v_empty, 1);
+        mbar_init(s_full, 1);
+        mbar_init(p_full, 128);
+        mbar_init(pv_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                     "r"(512u)
+                     "r"((uint32_t)TMEM_COLS)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -172,7 +190,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * KEYS;   // columns: S0 | S1 | O
+    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + KEYS;      // columns: S (P over its first half) | O
     fr_pdl_wait();
     if (threadIdx.x == 0) fr_pdl_launch();
 
@@ -187,7 +205,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const int* table = p.block_table + (size_t)seq * p.table_width;
             bool ok = true;
             for (int i = 0; i < n_blocks && ok; ++i) {
-                const int kb = kb_begin + i, stage = i & 1;
+                const int kb = kb_begin + i;
                 int rows[2];
                 for (int h = 0; h < 2; ++h) {
                     const int lp = kb * 2 + h;
@@ -197,19 +215,17 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                         if (page >= 0) rows[h] = page * PAGE;
                     }
                 }
-                // K is free again as soon as its scores are done, V only after the second product: rings of their own
-                if (!(ok = mbar_wait(k_empty0 + 8 * stage, ((i >> 1) & 1) ^ 1, p.status, 1))) break;
-                mbar_expect_tx(k_full0 + 8 * stage, (uint32_t)slices * 2 * PAGE * 128);
+                // K is free again as soon as its scores are done, V after the second product
+                if (!(ok = mbar_wait(k_empty, (i & 1) ^ 1, p.status, 1))) break;
+                mbar_expect_tx(k_full, (uint32_t)slices * 2 * PAGE * 128);
                 for (int h = 0; h < 2; ++h)
                     for (int s = 0; s < slices; ++s)
-                        tma_load_3d(smem_u32(s_k) + (uint32_t)((stage * 2 + s) * SLICE + h * PAGE * 128), &map_k, s * 64, kvh,
-                                    rows[h], k_full0 + 8 * stage);
-                if (!(ok = mbar_wait(v_empty0 + 8 * stage, ((i >> 1) & 1) ^ 1, p.status, 1))) break;
-                mbar_expect_tx(v_full0 + 8 * stage, (uint32_t)slices * 2 * PAGE * 128);
+                        tma_load_3d(smem_u32(s_k) + (uint32_t)(s * SLICE + h * PAGE * 128), &map_k, s * 64, kvh, rows[h], k_full);
+                if (!(ok = mbar_wait(v_empty, (i & 1) ^ 1, p.status, 1))) break;
+                mbar_expect_tx(v_full, (uint32_t)slices * 2 * PAGE * 128);
                 for (int h = 0; h < 2; ++h)
                     for (int s = 0; s < slices; ++s)
-                        tma_load_3d(smem_u32(s_v) + (uint32_t)((stage * 2 + s) * SLICE + h * PAGE * 128), &map_v, s * 64, kvh,
-                                    rows[h], v_full0 + 8 * stage);
+                        tma_load_3d(smem_u32(s_v) + (uint32_t)(s * SLICE + h * PAGE * 128), &map_v, s * 64, kvh, rows[h], v_full);
             }
         }
     } else if (warp == 1) {
@@ -226,44 +242,35 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     m_mark = now;
                 }
             };
-            auto issue_qk = [&](int i) {
-                const int stage = i & 1;
-                if (!(ok = mbar_wait(k_full0 + 8 * stage, (i >> 1) & 1, p.status, 3))) return;
+            for (int i = 0; i < n_blocks && ok; ++i) {
+                // S = Q K^T.  The tensor core takes its instructions in order, so the S columns (and P over them)
+                // are free: the product of P V of the block before was issued earlier.
+                if (!(ok = mbar_wait(k_full, i & 1, p.status, 3))) break;
                 mlap(0);
                 tc_fence_after();
-                const uint32_t d = tmem_s + (uint32_t)(i & 1) * KEYS;
                 for (int ks = 0; ks < k_steps; ++ks) {
                     const int s = ks >> 2, k = ks & 3;
                     const uint64_t da = smem_desc(smem_u32(s_q + s * SLICE)) + 2 * k;
-                    const uint64_t db = smem_desc(smem_u32(s_k + (stage * 2 + s) * SLICE)) + 2 * k;
-                    tc_mma(d, da, db, idesc_qk, ks > 0 ? 1u : 0u);
+                    const uint64_t db = smem_desc(smem_u32(s_k + s * SLICE)) + 2 * k;
+                    tc_mma(tmem_s, da, db, idesc_qk, ks > 0 ? 1u : 0u);
                 }
-                tc_commit(s_full0 + 8 * (i & 1));
-                tc_commit(k_empty0 + 8 * stage);
+                tc_commit(s_full);
+                tc_commit(k_empty);
                 mlap(1);
-            };
-            if (ok) issue_qk(0);
-            for (int i = 0; i < n_blocks && ok; ++i) {
-                const int stage = i & 1;
-                // S of block i+1 goes to the other buffer, which the rows have read (p_full of block i-1 was waited
-                // for in the round before)
-                if (i + 1 < n_blocks) issue_qk(i + 1);
-                if (!ok) break;
-                if (!(ok = mbar_wait(v_full0 + 8 * stage, (i >> 1) & 1, p.status, 3))) break;
+                if (!(ok = mbar_wait(v_full, i & 1, p.status, 3))) break;
                 mlap(2);
-                if (!(ok = mbar_wait(p_full0 + 8 * (i & 1), (i >> 1) & 1, p.status, 4))) break;
+                if (!(ok = mbar_wait(p_full, i & 1, p.status, 4))) break;
                 mlap(3);
                 tc_fence_after();
-                // keys of this block that some row may see, in steps of 16
+                // O += P V over the keys of this block that some row may see, in steps of 16; P from tensor memory
                 const int keys_here = min(KEYS, pos_hi - (kb_begin + i) * KEYS + 1);
                 const int pv_steps = (keys_here + 15) / 16;
                 for (int ks = 0; ks < pv_steps; ++ks) {
-                    const uint64_t da = smem_desc(smem_u32(s_p + ((i & 1) * 2 + (ks >> 2)) * SLICE)) + 2 * (ks & 3);
-                    const uint64_t db = smem_desc_mn(smem_u32(s_v + stage * 2 * SLICE) + ks * 16 * 128, SLICE, 1024);
-                    tc_mma(tmem_o, da, db, idesc_pv, (i > 0 || ks > 0) ? 1u : 0u);
+                    const uint64_t db = smem_desc_mn(smem_u32(s_v) + ks * 16 * 128, SLICE, 1024);
+                    tc_mma_ta(tmem_o, tmem_s + 8 * ks, db, idesc_pv, (i > 0 || ks > 0) ? 1u : 0u);
                 }
-                tc_commit(pv_done0 + 8 * (i & 1));
-                tc_commit(v_empty0 + 8 * stage);
+                tc_commit(pv_done);
+                tc_commit(v_empty);
                 mlap(4);
             }
             if (p.trace != nullptr) {
@@ -292,16 +299,16 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             }
         };
         for (int i = 0; i < n_blocks && ok; ++i) {
-            const int kb = kb_begin + i, stage = i & 1;
+            const int kb = kb_begin + i;
             const int j0 = kb * KEYS;
-            if (!(ok = mbar_wait(s_full0 + 8 * (i & 1), (i >> 1) & 1, p.status, 6))) break;
+            if (!(ok = mbar_wait(s_full, i & 1, p.status, 6))) break;
             tc_fence_after();
             lap(0);
             // Two passes over the row of S in tensor memory, 32 columns at a time, as compact loops (the fully
             // unrolled form, with the row held in 128 registers, ran three times slower: it does not fit the
-            // instruction cache).  Masked and unmasked blocks have loops of their own; most blocks need no mask.
-            const uint32_t s_addr = tmem_s + lane_addr + (uint32_t)(i & 1) * KEYS;
-            // (the choice must be the same for a whole warp: the loads from tensor memory are warp-wide instructions)
+            // instruction cache).  Masked and unmasked blocks have loops of their own; most blocks need no mask
+            // (the choice must be the same for a whole warp: the loads from tensor memory are warp-wide instructions).
+            const uint32_t s_addr = tmem_s + lane_addr;
             const bool need_mask = __any_sync(0xffffffffu, j0 + KEYS - 1 > pos0 + t0 ||
                                                                (p.window > 0 && j0 < pos_hi - p.window + 1) || !valid);
             float mx = -INFINITY;
@@ -334,7 +341,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 }
                 if (i > 0) {
                     // every product into O so far must be done
-                    if (!(ok = mbar_wait(pv_done0 + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1, p.status, 8))) break;
+                    if (!(ok = mbar_wait(pv_done, (i - 1) & 1, p.status, 8))) break;
                     tc_fence_after();
 #pragma unroll 1
                     for (int c = 0; c < 4; ++c) {
@@ -351,11 +358,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 }
             }
             lap(3);
-            // P buffer i & 1 was read by the product of block i - 2
-            if (i >= 2 && !(ok = mbar_wait(pv_done0 + 8 * (i & 1), ((i - 2) >> 1) & 1, p.status, 5))) break;
+            // Exponentials; P (bf16, two to a column) goes over the columns of S that this pass has already read:
+            // 32 scores in, 16 columns out, always behind the reading.
             const float m_use = m_run == -INFINITY ? 0.f : m_run;
             float sum = 0.f;
-            uint8_t* p_line = s_p + (i & 1) * 2 * SLICE + r * 128;
             auto exp_pass = [&](auto masked) {
 #pragma unroll 1
                 for (int c = 0; c < KEYS / 32; ++c) {
@@ -376,42 +382,38 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                         sum += e1;
                         packed[j >> 1] = pack2(e0, e1);
                     }
-                    // 32 keys = four 16-byte chunks of the row's 128-byte line in slice c / 2
-                    uint8_t* line = p_line + (c >> 1) * SLICE;
-#pragma unroll
-                    for (int q = 0; q < 4; ++q)
-                        *(uint4*)(line + (((((c & 1) << 2) + q) ^ (r & 7)) << 4)) =
-                            make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                    tc_st16(s_addr + c * 16, packed);
                 }
             };
             if (need_mask) exp_pass(std::true_type{});
             else exp_pass(std::false_type{});
+            tc_st_wait();
             l_run += sum;
             if (kb == kb_end) {
                 // keys past the last one that any row may see: their V rows may hold anything; zero them
                 const int key = j0 + r;
                 if (key > pos_hi) {
-                    if (!(ok = mbar_wait(v_full0 + 8 * stage, (i >> 1) & 1, p.status, 7))) break;
+                    if (!(ok = mbar_wait(v_full, i & 1, p.status, 7))) break;
                     for (int s = 0; s < slices; ++s) {
-                        uint4* line = (uint4*)(s_v + (stage * 2 + s) * SLICE + r * 128);
+                        uint4* line = (uint4*)(s_v + s * SLICE + r * 128);
 #pragma unroll
                         for (int q = 0; q < 8; ++q) line[q] = make_uint4(0u, 0u, 0u, 0u);
                     }
                 }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
             tc_fence_before();
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_arrive(p_full0 + 8 * (i & 1));
+            mbar_arrive(p_full);
             lap(2);
         }
         // the last product; then the row's output
-        if (ok) ok = mbar_wait(pv_done0 + 8 * ((n_blocks - 1) & 1), ((n_blocks - 1) >> 1) & 1, p.status, 8);
+        if (ok) ok = mbar_wait(pv_done, (n_blocks - 1) & 1, p.status, 8);
         tc_fence_after();
         lap(4);
         if (ok) {
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             bf16* dst = p.out + ((size_t)(q_start + t0 + t) * p.nq + (size_t)kvh * G + g) * p.hd;
-#pragma unroll
+#pragma unroll 1
             for (int c = 0; c < 4; ++c) {
                 if (c * 32 < p.hd) {                                   // uniform: the load is warp-wide
                     uint32_t raw[32];
@@ -444,7 +446,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
     }
 }
 
@@ -477,7 +479,7 @@ int encode(CUtensorMap* map, const void* base, int rank, const cuuint64_t* dims,
     return FR_OK;
 }
 
-constexpr int SMEM_BYTES = (2 + 2 * STAGES * 2 + 2 * 2) * SLICE + 1024 + 256;
+constexpr int SMEM_BYTES = 6 * SLICE + 1024 + 256;      // Q, K, V: two 64-dim slices each; two CTAs share an SM
 
 }  // namespace
 
