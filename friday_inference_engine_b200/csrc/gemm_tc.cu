@@ -19,10 +19,19 @@
 //
 // The operand that feeds the M side of the instruction ("P", tiles of 128 rows) and the
 // one that feeds its N side ("Q", tiles of BN rows) are chosen by the launcher:
-//   many rows (prompts):   P = x, Q = w, BN = 128 or 256;
-//   few rows (decoding):   P = w, Q = x, BN = 16/32/64 >= rows: every weight is streamed
-//                          once at full width, the handful of activations ride along, and
-//                          the epilogue writes the tile transposed.
+//   many rows (prompts):   P = x, Q = w, BN = 128 ... 256 in steps of 16 (the widest
+//                          kernel instance takes the width as a number), chosen so that
+//                          the tiles fill whole waves of the SMs;
+//   few rows (decoding):   P = w, Q = x, BN = 16/32/64 >= rows (up to 64 rows): every
+//                          weight is streamed once at full width, the handful of
+//                          activations ride along, and the epilogue writes the tile
+//                          transposed: the sums go through shared memory as
+//                          [rows][128 columns] floats, then every thread finishes pieces
+//                          of 8 consecutive columns of one row with 16-byte accesses.
+// In that transposed epilogue more can ride along (gemm_tc_fusion.h): the RMSNorm of
+// the input finished (a factor per row), the RMSNorm of the output begun, and rotary
+// encoding with the write of keys and values into the cache.  What it reads besides
+// the sums is fetched while the products run.
 // When a shape has fewer tiles than the GPU has SMs (decoding against a [4608 x 3584]
 // matrix is 36 tiles), k is cut into `splits` ranges; each CTA writes its partial tile to
 // a scratch buffer, and the CTA that arrives last for a tile (a counter per tile) sums
