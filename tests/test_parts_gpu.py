@@ -196,12 +196,39 @@ class AdditivePosition(Part):
         v[:, : n_heads + n_kv_heads, 0] += (ctx.row_pos.float() / 100.0).to(qkv.dtype)[:, None]
 
 
+@register_part("feed_forward", "toy_top1")
+class Top1Experts(Part):
+    """A feed-forward with routing: a router picks one of a few small ReLU experts per row; the expert's output is
+    weighted with the router's probability for it.  Rows are flat, so routing is a matter of row indices."""
+    category = "feed_forward"
+
+    def __init__(self, env, experts, inner):
+        super().__init__(env)
+        self.experts, self.inner = int(experts), int(inner)
+        self.declare("router.weight", (self.experts, env.width))
+        self.declare("experts.up", (self.experts, self.inner, env.width))
+        self.declare("experts.down", (self.experts, env.width, self.inner))
+
+    def forward(self, h, residual, ctx):
+        t = self.tensors
+        probs = torch.softmax(h.float() @ t["router.weight"].float().t(), dim=-1)      # router logits in 32-bit
+        choice = probs.argmax(dim=-1)
+        out = residual.clone()
+        for e in range(self.experts):
+            rows = (choice == e).nonzero(as_tuple=True)[0]
+            if rows.numel():
+                y = torch.relu(h[rows].float() @ t["experts.up"][e].float().t()) @ t["experts.down"][e].float().t()
+                out[rows] += (y * probs[rows, e][:, None]).to(out.dtype)
+        return out
+
+
 def toy_spec(cfg):
     spec = qwen2_spec(cfg)
     layers = list(spec.layers)
     # layer 1: the toy mixer instead of attention; layer 2: attention with the toy position encoding
     p1 = dict(layers[1].params)
     p1["mixer"] = PartSpec("toy_running_mean", {}, prefix="toy.")
+    p1["feed_forward"] = PartSpec("toy_top1", {"experts": 3, "inner": 40}, prefix="moe.")     # and routed experts
     layers[1] = PartSpec("prenorm", p1, prefix=layers[1].prefix)
     p2 = dict(layers[2].params)
     mp = dict(p2["mixer"].params)
@@ -249,7 +276,13 @@ def toy_plain_logits(t, cfg, tokens):
     n = pm.rms_norm(x, t["model.layers.1.input_layernorm.weight"], m.eps)
     mean = np.cumsum(n, axis=0) / np.arange(1, T + 1)[:, None]
     x = x + pm.linear(mean, t["model.layers.1.toy.mix.weight"])
-    x = pm.mlp_block(m, 1, x)
+    n = pm.rms_norm(x, t["model.layers.1.post_attention_layernorm.weight"], m.eps)
+    logits = n @ t["model.layers.1.moe.router.weight"].T
+    probs = np.exp(logits - logits.max(-1, keepdims=True))
+    probs /= probs.sum(-1, keepdims=True)
+    for row, e in enumerate(probs.argmax(-1)):
+        y = np.maximum(n[row] @ t["model.layers.1.moe.experts.up"][e].T, 0.0) @ t["model.layers.1.moe.experts.down"][e].T
+        x[row] = x[row] + y * probs[row, e]
     x, kv2 = attn(2, x, False)
     x = pm.mlp_block(m, 2, x)
     x, _ = attn(0, x, True)
@@ -267,6 +300,8 @@ def test_toy_architecture_is_registered_built_and_stepped(tmp_path):
     harness.sharpen(d, 4.0)
     tensors = pm.read_safetensors(d + "/model.safetensors")
     assert "model.layers.1.toy.mix.weight" in tensors and "model.layers.1.self_attn.q_proj.weight" not in tensors
+    assert tensors["model.layers.1.moe.experts.up"].shape == (3, 40, cfg["hidden_size"]) and \
+        "model.layers.1.mlp.gate_proj.weight" not in tensors and "model.layers.0.mlp.gate_proj.weight" in tensors
     eng = Engine(model_path=d, dtype="float32", max_ctx=256, max_batch=3, prefill_chunk=40)
     assert len(eng.cache.groups) == 1 and eng.cache.groups[0].entries == [0, 2, 3] and list(eng.cache.states) == [1]
     prompts = tiny_configs.random_prompts([70, 9, 33], cfg["vocab_size"], 6)
