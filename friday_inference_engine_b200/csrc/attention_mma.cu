@@ -8,24 +8,32 @@
 // does the same with CUDA cores: decodeAttentionGqaKernel, attention_kernels.cu:267-411,
 // and its R = tq*G + g rows for prompts, :493-499).
 //
-// Blocks of 64 keys are exactly the cache's pages, so a block is one page lookup.  K and
-// V blocks go global -> shared with cp.async (two buffers: the next block loads while this
-// one is used; rows past a sequence's last needed key are zero-filled, so stale pages
-// never reach the arithmetic), fragments come from ldmatrix, products are
-// mma.sync.m16n8k16 with the online softmax of flash attention between them.
+// Blocks of 64 keys are exactly the cache's pages, so a block is one page lookup.  Fragments come from ldmatrix,
+// products are mma.sync.m16n8k16 with the online softmax of flash attention between them.  How K and V blocks
+// get from global to shared memory differs:
+//   prompts          cp.async by the computing warps into padded rows, two buffers; rows past a sequence's last
+//                    needed key are zero-filled;
+//   one-token steps  a fifth warp issues TMA loads of whole pages (64 keys x 64 dims a box, 128-byte swizzle) into a
+//                    ring of three blocks with an mbarrier per buffer; ldmatrix addresses undo the swizzle; the
+//                    computing warps issue no copies and meet no block-wide barrier in the loop.  Blocks of earlier
+//                    steps are requested before the wait for the kernel before this one.  V rows past the last
+//                    needed key are zeroed in shared memory (a zero weight times a stale NaN is a NaN); scores of
+//                    such keys are replaced by the mask.
 //
 // Two shapes of the same kernel:
 //   rows mode (prompts): a CTA owns 64 rows; each of its 4 warps owns 16 rows and walks
 //       all 64 keys of a block;
 //   keys mode (decoding): a CTA owns 16 rows (one token's G heads, padded) and a range of
 //       blocks (`splits` CTAs share a sequence's keys); each warp takes 16 of a block's 64
-//       keys; warps merge through shared memory, splits through the scratch buffer and
-//       the merge kernel.
+//       keys; warps merge through shared memory; the splits of a tile form a thread-block
+//       cluster and merge through each other's shared memory (more than 8 splits: through
+//       a scratch buffer, the last CTA to arrive merging).
 // Head sizes: multiples of 16 up to 128.  Others are served by the CUDA-core kernel.
 #include <math.h>
 
 #include "attention_merge.cuh"
 #include "common.cuh"
+#include "tc_common.cuh"
 
 FR_EXPORT const char* attention_mma_last_error() { return fr_error_text; }
 
@@ -53,6 +61,8 @@ struct MmaArgs {
                               // each other's shared memory (no scratch, no counters)
     int q_stride, table_width, nq, nkv, window, splits;
     float scale_log2;         // softmax scale times log2(e)
+    int pool_rows;            // rows of a pool (pages x 64): a load from there on is filled with zeros
+    int* status;              // a word that receives a code when a bounded wait of the one-token kernel gave up
     unsigned long long* trace;  // for measurements (may be null): [cta][8] timestamps of a one-token step's CTAs
 };
 
@@ -91,24 +101,50 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// One-token steps have a fifth warp that only copies: it keeps the ring of K/V blocks full with TMA loads of whole
+// pages (one instruction per 64 keys x 64 dims, 128-byte swizzle, completion on an mbarrier), so the four computing
+// warps issue no copy instructions and meet no block-wide barrier inside the loop.  (Bulk copies of single rows, one
+// instruction per 256 bytes, were three times slower than the cp.async of the computing warps.)
+__device__ __forceinline__ void tma_page(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+        : "memory");
+}
+
 template <int HD, bool KEYS_MODE>
-__global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs p) {
+__global__ void __launch_bounds__(KEYS_MODE ? (WARPS + 1) * 32 : WARPS * 32)
+attention_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const MmaArgs p) {
     constexpr int ROW_BYTES = HD * 2 + 16;            // padded: 8 consecutive rows hit 8 different bank groups
     constexpr int CHUNKS = HD / 8;                    // 16-byte pieces per row
     constexpr int ROWS_CTA = KEYS_MODE ? 16 : 64;
     constexpr int KPW = KEYS_MODE ? 16 : 64;          // keys of a block per warp
     constexpr int NT = KPW / 8;                       // score tiles (8 keys each) per warp
     constexpr int DT = HD / 8;                        // output tiles (8 dims each)
-    constexpr int KV_BYTES = BLOCK_N * ROW_BYTES;
     // Buffers of the K/V ring.  One-token steps do almost no arithmetic per block, so what bounds them is how many
     // blocks are on their way from memory: three buffers keep two in flight; prompts are bound by arithmetic.
     constexpr int NS = KEYS_MODE ? 3 : 2;
-    extern __shared__ __align__(16) uint8_t smem[];
-    uint8_t* s_q = smem;                              // [ROWS_CTA][ROW_BYTES]
-    uint8_t* s_k = s_q + ROWS_CTA * ROW_BYTES;        // [NS][64][ROW_BYTES]
-    uint8_t* s_v = s_k + NS * KV_BYTES;               // [NS][64][ROW_BYTES]
+    // One-token steps: a block's keys (and values) lie as SL slices of 64 dims, each [64 keys][128 bytes] with the
+    // 16-byte pieces of a row exchanged by the row's number (TMA's 128-byte swizzle), behind a 1 KB boundary.
+    constexpr int SL = (HD + 63) / 64;
+    constexpr int KV_BYTES = KEYS_MODE ? SL * BLOCK_N * 128 : BLOCK_N * ROW_BYTES;
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    uint8_t* smem = KEYS_MODE ? (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023) : smem_raw;
+    uint8_t* s_k = smem;                              // [NS] blocks
+    uint8_t* s_v = s_k + NS * KV_BYTES;               // [NS] blocks
+    uint8_t* s_q = s_v + NS * KV_BYTES;               // [ROWS_CTA][ROW_BYTES]
 
     __shared__ int s_pages[WARPS * 32];               // the sequence's first pages, read before anything depends on them
+    __shared__ uint64_t s_bars[2 * NS];               // one-token steps: full[NS], empty[NS]
+    const uint32_t full0 = tc::smem_u32(s_bars), empty0 = tc::smem_u32(s_bars + NS);
+    if (KEYS_MODE && threadIdx.x == 0) {
+        for (int b = 0; b < NS; ++b) {
+            tc::mbar_init(full0 + 8 * b, 1);
+            tc::mbar_init(empty0 + 8 * b, WARPS);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
     mark(p, 0);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int seq = blockIdx.z, kvh = blockIdx.y;
@@ -180,24 +216,40 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
     };
 
     // Keys and values of earlier steps are final before this step's first kernel starts; only the blocks from the
-    // step's own first position on are written by the kernel before this one.  One-token steps therefore request
-    // their first blocks ahead of the wait, where they can; the queries and the rest follow it.
+    // step's own first position on are written by the kernel before this one.  The copying warp of a one-token step
+    // therefore starts at once and waits for the kernel before only when it reaches such a block.
     const int first_fresh = pos0 / BLOCK_N;            // blocks from here on hold rows of this step
-    bool early[NS - 1];
-#pragma unroll
-    for (int st = 0; st < NS - 1; ++st) {
-        early[st] = KEYS_MODE && kb_begin + st <= kb_end && kb_begin + st < first_fresh;
-        if (early[st]) load_kv(kb_begin + st, st);
+    const bool producer = KEYS_MODE && warp == WARPS;
+    if (producer) {
+        bool waited = false, ok = true;
+        int j = 0;
+        for (int kb = kb_begin; kb <= kb_end && ok; ++kb, ++j) {
+            const int b = j % NS;
+            if (kb >= first_fresh && !waited) {
+                fr_pdl_wait();
+                waited = true;
+            }
+            if (!(ok = tc::mbar_wait(empty0 + 8 * b, ((j / NS) & 1) ^ 1, p.status, 21))) break;
+            const int page = kb < WARPS * 32 ? s_pages[kb] : table[kb];
+            if (lane == 0) {
+                // a page that the table does not name is loaded from beyond the pool's last row: zeros
+                const int row = page >= 0 ? page * BLOCK_N : p.pool_rows;
+                tc::mbar_expect_tx(full0 + 8 * b, (uint32_t)(2 * SL * BLOCK_N * 128));
+                for (int sl = 0; sl < SL; ++sl) {
+                    tma_page(k_smem + b * KV_BYTES + sl * BLOCK_N * 128, &map_k, sl * 64, kvh, row, full0 + 8 * b);
+                    tma_page(v_smem + b * KV_BYTES + sl * BLOCK_N * 128, &map_v, sl * 64, kvh, row, full0 + 8 * b);
+                }
+            }
+            __syncwarp();
+        }
+        if (!waited) fr_pdl_wait();
+        fr_pdl_launch();
+    } else {
+        fr_pdl_wait();
+        fr_pdl_launch();
     }
-    cp_commit();                                       // group A: what could be asked for ahead
-
-    fr_pdl_wait();
-    fr_pdl_launch();
     mark(p, 1);
-    if (r0 >= n_rows) {
-        cp_wait<0>();
-        return;
-    }
+    if (r0 >= n_rows) return;
 
     // This thread's two rows (fragment layout of mma: rows lane/4 and lane/4 + 8 of the warp's 16).
     const int row_base = KEYS_MODE ? 0 : warp * 16;
@@ -223,28 +275,45 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
         for (int e = 0; e < 4; ++e) o[d][e] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
-    load_q();
+    if (!producer) load_q();
+    if (!KEYS_MODE) {
 #pragma unroll
-    for (int st = 0; st < NS - 1; ++st)
-        if (!early[st] && kb_begin + st <= kb_end) load_kv(kb_begin + st, st);
-    cp_commit();                                       // group B: the queries and the rest of the first blocks
+        for (int st = 0; st < NS - 1; ++st)
+            if (kb_begin + st <= kb_end) load_kv(kb_begin + st, st);
+    }
+    cp_commit();                                       // the queries (and for prompts the first blocks)
+    if (KEYS_MODE) {
+        cp_wait<0>();
+        if (!producer) asm volatile("bar.sync 1, %0;" ::"n"(WARPS * 32) : "memory");     // the queries are in place
+    }
 
     mark(p, 2);
     const uint32_t q_addr = (uint32_t)__cvta_generic_to_shared(s_q);
     uint32_t q_frag[KEYS_MODE ? HD / 16 : 1][4];       // one-token steps keep the queries in registers
     bool q_loaded = false;
     int buf = 0;
-    for (int kb = kb_begin; kb <= kb_end; ++kb, buf = buf + 1 == NS ? 0 : buf + 1) {
-        {
+    bool ring_ok = true;
+    int round = 0;                                     // how often the ring has gone round
+    for (int kb = producer ? kb_end + 1 : kb_begin; kb <= kb_end && ring_ok; ++kb) {
+        if (KEYS_MODE) {
+            if (!(ring_ok = tc::mbar_wait(full0 + 8 * buf, round & 1, p.status, 22))) break;
+            const int valid = pos_hi - kb * BLOCK_N + 1;
+            if (kb == kb_end && valid < BLOCK_N) {
+                // rows past the last needed key come with the page: what lies there may be anything, and a zero weight
+                // times a NaN is a NaN.  Zero those rows of V (scores of such keys are replaced by the mask).
+                for (int c = tid; c < (BLOCK_N - valid) * SL * 8; c += WARPS * 32) {
+                    const int r = valid + c / (SL * 8), rest = c % (SL * 8);
+                    *(uint4*)(s_v + buf * KV_BYTES + (rest >> 3) * BLOCK_N * 128 + r * 128 + (rest & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(WARPS * 32) : "memory");
+            }
+        } else {
             const int ahead = buf + NS - 1 >= NS ? buf - 1 : buf + NS - 1;      // the buffer used one block ago
             if (kb + NS - 1 <= kb_end) load_kv(kb + NS - 1, ahead);
             cp_commit();
-            // all but the newest groups: block kb is here (the first blocks and the queries sit in groups A and B,
-            // which only this round's group follows; later blocks have a group each)
-            if (kb == kb_begin) cp_wait<1>();
-            else cp_wait<NS - 1>();
+            cp_wait<NS - 1>();                         // everything but the newest NS-1 groups: block kb is here
+            __syncthreads();
         }
-        __syncthreads();
         if (kb == kb_begin) mark(p, 3);
         const uint32_t k_addr = (uint32_t)__cvta_generic_to_shared(s_k + buf * KV_BYTES);
         const uint32_t v_addr = (uint32_t)__cvta_generic_to_shared(s_v + buf * KV_BYTES);
@@ -271,8 +340,9 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
 #pragma unroll
             for (int np = 0; np < NT / 2; ++np) {
                 uint32_t b[4];
-                ldsm4(b, k_addr + (key_base + np * 16 + (lane & 7) + 8 * (lane >> 4)) * ROW_BYTES +
-                             (ks * 16 + 8 * ((lane >> 3) & 1)) * 2);
+                const int krow = key_base + np * 16 + (lane & 7) + 8 * (lane >> 4), kch = ks * 2 + ((lane >> 3) & 1);
+                ldsm4(b, KEYS_MODE ? k_addr + (kch >> 3) * BLOCK_N * 128 + krow * 128 + (((kch & 7) ^ (krow & 7)) << 4)
+                                   : k_addr + krow * ROW_BYTES + kch * 16);
                 mma16816(s[2 * np], a, b[0], b[1]);
                 mma16816(s[2 * np + 1], a, b[2], b[3]);
             }
@@ -334,13 +404,23 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
 #pragma unroll
             for (int dp = 0; dp < DT / 2; ++dp) {
                 uint32_t b[4];
-                ldsm4_t(b, v_addr + (key_base + kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * ROW_BYTES +
-                               (dp * 16 + 8 * (lane >> 4)) * 2);
+                const int vrow = key_base + kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), vch = dp * 2 + (lane >> 4);
+                ldsm4_t(b, KEYS_MODE ? v_addr + (vch >> 3) * BLOCK_N * 128 + vrow * 128 + (((vch & 7) ^ (vrow & 7)) << 4)
+                                     : v_addr + vrow * ROW_BYTES + vch * 16);
                 mma16816(o[2 * dp], a, b[0], b[1]);
                 mma16816(o[2 * dp + 1], a, b[2], b[3]);
             }
         }
-        __syncthreads();          // every warp is done with this buffer before it is loaded again
+        if (KEYS_MODE) {
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(empty0 + 8 * buf);      // this warp is done with the buffer
+        } else {
+            __syncthreads();      // every warp is done with this buffer before it is loaded again
+        }
+        if (++buf == NS) {
+            buf = 0;
+            ++round;
+        }
     }
     cp_wait<0>();
     mark(p, 4);
@@ -388,9 +468,11 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
         float* r_o = c_l + WARPS * 16;                              // [16][HD]: this CTA's merged rows (cluster path)
         float* r_m = r_o + 16 * HD;                                 // [16]
         float* r_l = r_m + 16;
+        __syncthreads();                              // every warp is done with the last K/V buffers
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const int r = (lane >> 2) + 8 * i;
+            if (producer) break;
 #pragma unroll
             for (int d = 0; d < DT; ++d) {
                 *reinterpret_cast<float2*>(c_o + (warp * 16 + r) * HDP + d * 8 + 2 * (lane & 3)) = make_float2(o[d][2 * i], o[d][2 * i + 1]);
@@ -401,8 +483,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
             }
         }
         __syncthreads();
-        const int r = tid >> 3;                       // 16 rows x 8 threads
-        const int rr = r0 + r;
+        const int r = tid >> 3;                       // 16 rows x 8 threads (the copying warp has none)
+        const int rr = producer ? n_rows : r0 + r;
         if (rr < n_rows) {
             float big = -INFINITY;
 #pragma unroll
@@ -445,7 +527,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(const MmaArgs
             const int rank = (int)fr_cluster_rank();
             const int rows_per = (16 + p.splits - 1) / p.splits;
             constexpr int VEC = HD / 4;                                 // float4 pieces per row
-            for (int idx = tid; idx < rows_per * VEC; idx += WARPS * 32) {
+            for (int idx = producer ? rows_per * VEC : tid; idx < rows_per * VEC; idx += WARPS * 32) {
                 const int r2 = rank * rows_per + idx / VEC, d4 = idx % VEC;
                 const int rr2 = r0 + r2;
                 if (r2 >= 16 || rr2 >= n_rows) continue;
@@ -550,20 +632,27 @@ bool use_clusters() {
     return v != 0;
 }
 
+// Dynamic shared memory: the K/V ring (one-token steps: 128-byte rows per 64-dim slice behind a 1 KB boundary;
+// prompts: padded rows) or, if larger, what the merge of a one-token step's warps needs; and the queries.
 template <int HD, bool KEYS_MODE>
-int launch(const MmaArgs& p, dim3 grid, cudaStream_t stream) {
+constexpr int smem_bytes() {
     constexpr int ROW_BYTES = HD * 2 + 16;
     constexpr int ROWS_CTA = KEYS_MODE ? 16 : 64;
-    constexpr int kv = 2 * (KEYS_MODE ? 3 : 2) * BLOCK_N * ROW_BYTES;
+    constexpr int kv = KEYS_MODE ? 2 * 3 * ((HD + 63) / 64) * BLOCK_N * 128 : 2 * 2 * BLOCK_N * ROW_BYTES;
     constexpr int merge = KEYS_MODE ? (WARPS * 16 * (HD + 4) + 2 * WARPS * 16 + 16 * HD + 32) * 4 : 0;
-    constexpr int smem = ROWS_CTA * ROW_BYTES + (kv > merge ? kv : merge);
+    return (KEYS_MODE ? 1024 : 0) + ROWS_CTA * ROW_BYTES + (kv > merge ? kv : merge);
+}
+
+template <int HD, bool KEYS_MODE>
+int launch(const CUtensorMap& mk, const CUtensorMap& mv, const MmaArgs& p, dim3 grid, cudaStream_t stream) {
+    constexpr int smem = smem_bytes<HD, KEYS_MODE>();
     static bool configured = false;
     if (!configured) {
         FR_CUDA(cudaFuncSetAttribute(attention_mma_kernel<HD, KEYS_MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         configured = true;
     }
-    FR_CUDA(fr_launch_cluster(attention_mma_kernel<HD, KEYS_MODE>, grid, dim3(WARPS * 32), smem, stream,
-                              p.cluster ? (unsigned)p.splits : 1u, p));
+    FR_CUDA(fr_launch_cluster(attention_mma_kernel<HD, KEYS_MODE>, grid, dim3(KEYS_MODE ? (WARPS + 1) * 32 : WARPS * 32), smem,
+                              stream, p.cluster ? (unsigned)p.splits : 1u, mk, mv, p));
     FR_CHECK_LAUNCH("attention_mma");
     return FR_OK;
 }
@@ -575,14 +664,11 @@ int clusters_at_once(int size) {
     if (size < 1 || size > 8) return 0;
     if (known[size] < 0) {
         known[size] = 0;
-        constexpr int ROW_BYTES = HD * 2 + 16;
-        constexpr int kv = 2 * 3 * BLOCK_N * ROW_BYTES;
-        constexpr int merge = (WARPS * 16 * (HD + 4) + 2 * WARPS * 16 + 16 * HD + 32) * 4;
-        constexpr int smem = 16 * ROW_BYTES + (kv > merge ? kv : merge);
+        constexpr int smem = smem_bytes<HD, true>();
         if (cudaFuncSetAttribute(attention_mma_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess) {
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3(size * 64);
-            cfg.blockDim = dim3(WARPS * 32);
+            cfg.blockDim = dim3((WARPS + 1) * 32);
             cfg.dynamicSmemBytes = smem;
             cudaLaunchAttribute attr[1];
             attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -600,18 +686,43 @@ int clusters_at_once(int size) {
 }
 
 template <bool KEYS_MODE>
-int launch_hd(int hd, const MmaArgs& p, dim3 grid, cudaStream_t stream) {
+int launch_hd(int hd, const CUtensorMap& mk, const CUtensorMap& mv, const MmaArgs& p, dim3 grid, cudaStream_t stream) {
     switch (hd) {
-        case 16: return launch<16, KEYS_MODE>(p, grid, stream);
-        case 32: return launch<32, KEYS_MODE>(p, grid, stream);
-        case 48: return launch<48, KEYS_MODE>(p, grid, stream);
-        case 64: return launch<64, KEYS_MODE>(p, grid, stream);
-        case 80: return launch<80, KEYS_MODE>(p, grid, stream);
-        case 96: return launch<96, KEYS_MODE>(p, grid, stream);
-        case 112: return launch<112, KEYS_MODE>(p, grid, stream);
-        case 128: return launch<128, KEYS_MODE>(p, grid, stream);
+        case 16: return launch<16, KEYS_MODE>(mk, mv, p, grid, stream);
+        case 32: return launch<32, KEYS_MODE>(mk, mv, p, grid, stream);
+        case 48: return launch<48, KEYS_MODE>(mk, mv, p, grid, stream);
+        case 64: return launch<64, KEYS_MODE>(mk, mv, p, grid, stream);
+        case 80: return launch<80, KEYS_MODE>(mk, mv, p, grid, stream);
+        case 96: return launch<96, KEYS_MODE>(mk, mv, p, grid, stream);
+        case 112: return launch<112, KEYS_MODE>(mk, mv, p, grid, stream);
+        case 128: return launch<128, KEYS_MODE>(mk, mv, p, grid, stream);
         default: FR_REFUSE("attention_mma: head size %d is not built (multiples of 16 up to 128)", hd);
     }
+}
+
+// A pool [pages][64][nkv][hd] as a 3-d tensor (dims, kv heads, rows); boxes of 64 dims x 64 rows, 128-byte swizzle.
+int pool_map(CUtensorMap* map, const void* pool, int pool_pages, int nkv, int hd) {
+    typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeTiled enc = nullptr;
+    if (enc == nullptr) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            enc = (EncodeTiled)ptr;
+    }
+    if (enc == nullptr) FR_REFUSE("attention_mma: the driver does not offer cuTensorMapEncodeTiled");
+    const cuuint64_t dims[3] = {(cuuint64_t)hd, (cuuint64_t)nkv, (cuuint64_t)pool_pages * BLOCK_N};
+    const cuuint64_t strides[2] = {(cuuint64_t)hd * 2, (cuuint64_t)nkv * hd * 2};
+    const cuuint32_t box[3] = {64, 1, BLOCK_N};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(pool), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) FR_REFUSE("attention_mma: cuTensorMapEncodeTiled failed with %d", (int)r);
+    return FR_OK;
 }
 
 }  // namespace
@@ -642,22 +753,24 @@ FR_EXPORT int attention_mma_clusters_at_once(int hd, int size) {
 
 FR_EXPORT int attention_mma_supports(int hd, int page) { return hd % 16 == 0 && hd >= 16 && hd <= 128 && page == BLOCK_N; }
 
-// q: rows of q_stride bf16 (head h at h * hd); out [rows][nq * hd]; pools [pages][64][nkv][hd] bf16.
+// q: rows of q_stride bf16 (head h at h * hd); out [rows][nq * hd]; pools [pool_pages][64][nkv][hd] bf16.
 // seq_start/seq_qlen/seq_pos0: per sequence, its first row, its rows in this step, the position of its first row.
 // seq_live (may be null): indexed by a sequence's first row; negative marks a sequence that has ended.
 // max_q_len: the longest seq_qlen (sizes the grid).  keys_mode: 1 for one-token steps.  splits > 1 needs
 // scratch of rows * nq * splits * (hd + 2) floats.  counters (may be null): n_counters zeroed ints; with them the
-// splits of a one-token step are merged inside the kernel, without them by a second kernel.
-FR_EXPORT int attention_mma(const void* q, int q_stride, void* out, const void* k_pool, const void* v_pool,
+// splits of a one-token step are merged inside the kernel, without them by a second kernel.  status: a device word
+// that receives a code (21 the copying warp, 22 a computing warp) if a bounded wait of a one-token step gives up.
+FR_EXPORT int attention_mma(const void* q, int q_stride, void* out, const void* k_pool, const void* v_pool, int pool_pages,
                             const int* block_table, int table_width, int page, const int* seq_start,
                             const int* seq_qlen, const int* seq_pos0, const int* seq_live, int n_seqs, int rows,
                             int max_q_len, int nq, int nkv, int hd, int window, float scale, int keys_mode, int splits,
-                            float* scratch, int* counters, int n_counters, cudaStream_t stream) {
+                            float* scratch, int* counters, int n_counters, int* status, cudaStream_t stream) {
     if (n_seqs <= 0 || rows <= 0) return FR_OK;
     if (!attention_mma_supports(hd, page)) FR_REFUSE("attention_mma: head size %d / page %d is not built", hd, page);
     if (nkv <= 0 || nq % nkv != 0) FR_REFUSE("attention: %d heads cannot share %d key/value heads", nq, nkv);
     if (splits < 1 || splits > 4096) FR_REFUSE("attention_mma: %d splits", splits);
     if (splits > 8 && scratch == nullptr) FR_REFUSE("attention_mma: more than 8 splits need a scratch buffer");
+    if (keys_mode && status == nullptr) FR_REFUSE("attention_mma: one-token steps need a status word");
     if (n_seqs > 65535 || nkv > 65535) FR_REFUSE("attention_mma: %d sequences x %d kv heads exceed the grid", n_seqs, nkv);
     MmaArgs p;
     p.q = (const bf16*)q; p.out = (bf16*)out; p.k_pool = (const bf16*)k_pool; p.v_pool = (const bf16*)v_pool;
@@ -667,13 +780,24 @@ FR_EXPORT int attention_mma(const void* q, int q_stride, void* out, const void* 
     p.q_stride = q_stride; p.table_width = table_width; p.nq = nq;
     p.nkv = nkv; p.window = window; p.splits = splits; p.scale_log2 = scale * LOG2E;
     p.trace = keys_mode ? attention_trace : nullptr;
+    p.status = status;
+    p.pool_rows = pool_pages * BLOCK_N;
     const int G = nq / nkv;
     const int rows_cta = keys_mode ? 16 : 64;
     const int tiles = (max_q_len * G + rows_cta - 1) / rows_cta;
     if (p.counters != nullptr && ((long long)n_seqs * nkv * tiles > n_counters || splits > 64))
         p.counters = nullptr;                          // the merge kernel instead
     dim3 grid(tiles * splits, nkv, n_seqs);
-    int rc = keys_mode ? launch_hd<true>(hd, p, grid, stream) : launch_hd<false>(hd, p, grid, stream);
+    CUtensorMap mk = {}, mv = {};
+    if (keys_mode) {
+        if (pool_pages <= 0 || ((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15))
+            FR_REFUSE("attention_mma: one-token steps need the pools' size and 16-byte aligned pools");
+        int rc_map = pool_map(&mk, k_pool, pool_pages, nkv, hd);
+        if (rc_map) return rc_map;
+        rc_map = pool_map(&mv, v_pool, pool_pages, nkv, hd);
+        if (rc_map) return rc_map;
+    }
+    int rc = keys_mode ? launch_hd<true>(hd, mk, mv, p, grid, stream) : launch_hd<false>(hd, mk, mv, p, grid, stream);
     if (rc) return rc;
     if (splits > 1 && p.counters == nullptr && !p.cluster) {
         MergeArgs mp{scratch, out, rows, nq, hd, splits};

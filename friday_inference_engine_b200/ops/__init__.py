@@ -383,10 +383,10 @@ class CudaOps:
             scratch = geometry.scratch(rows * n_heads * splits * (head_dim + 2), q.device)
         counters = self._attention_counters(q.device)
         lib.family("attention_mma").call(
-            "attention_mma", _ptr(q), q_stride, _ptr(out), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
+            "attention_mma", _ptr(q), q_stride, _ptr(out), _ptr(k_pool), _ptr(v_pool), k_pool.shape[0], _ptr(block_table),
             block_table.shape[1], 64, _ptr(seq_start), _ptr(seq_qlen), _ptr(seq_pos0), _ptr(seq_live), n_seqs, rows,
             max_q_len, n_heads, n_kv_heads, head_dim, window or 0, float(scale), 1 if keys_mode else 0, splits,
-            _ptr(scratch), _ptr(counters), counters.numel(), _stream())
+            _ptr(scratch), _ptr(counters), counters.numel(), _ptr(self._tc_buffers(q.device)[2]), _stream())
 
     def _attention_counters(self, device):
         """Zeroed ints, one per (sequence, kv head, row tile) of a one-token step; the kernel leaves them zero."""

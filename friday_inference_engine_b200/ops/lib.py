@@ -42,7 +42,7 @@ _SIGNATURES = {
         "attention_simt": [P, I, P, P, P, P, I, I, P, P, I, I, I, I, I, F, I, P, I, P],
     },
     "attention_mma": {
-        "attention_mma": [P, I, P, P, P, P, I, I, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, I, P],
+        "attention_mma": [P, I, P, P, P, I, P, I, I, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, I, P, P],
         "attention_mma_supports": [I, I],
         "attention_mma_clusters_at_once": [I, I],
     },
