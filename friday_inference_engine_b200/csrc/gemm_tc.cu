@@ -36,7 +36,9 @@
 // matrix is 36 tiles), k is cut into `splits` ranges; each CTA writes its partial tile to
 // a scratch buffer, and the CTA that arrives last for a tile (a counter per tile) sums
 // the partials in split order and runs the epilogue.  The sum order is fixed, so results
-// do not depend on which CTA came last.
+// do not depend on which CTA came last.  Tiles of 32 or 64 rows are finished by all the
+// CTAs of the tile instead, 16 rows each, once every partial tile is written (they wait
+// for the tile's counter, with a time limit): one CTA alone took 24 us for such a tile.
 //
 // Replaces the reference's int8 mma.sync GEMM (prefill_kernels.cu:173-327) and its dp4a
 // GEMVs (hpc_k_quants.cu:445-681), with the same epilogue contract (bias, then
@@ -83,6 +85,11 @@ struct GemmParams {
     // robin (splits = 1: whole tiles).  The remaining sk_tiles tiles ("stream-k"): their k blocks, laid end to end,
     // are cut into one contiguous run of sk_units per CTA, so that a last, partial wave of tiles keeps every SM busy.
     int dp_tiles, sk_tiles, sk_units;
+    // Tiles wider than 16 rows whose k is split: instead of the last CTA to arrive finishing the whole tile, every
+    // CTA of the tile waits until all partial tiles are written and finishes a share of the tile's rows (16 at a
+    // time).  Needs all CTAs of a tile on the device at once (grid = tiles * splits, no more than there are SMs), and a
+    // second counter per tile (at counters[tiles + tile]) that tells the last CTA to leave.
+    int shared_finish;
 };
 
 struct Item {
@@ -302,8 +309,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         fr_pdl_wait();
         bool ok = true;
         int it = 0;
-        Work work(p, blockIdx.x, gridDim.x);
-        Item item;
         const GemmFusion& f = p.f;
         // Narrow tiles of the swapped orientation are written transposed.  Their sums go through s_sum as
         // [rows of the step][128 columns] floats; then every thread finishes pieces of 8 consecutive columns of one
@@ -313,28 +318,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                                (((uintptr_t)p.out | (uintptr_t)p.residual) & 15) == 0 && (bf16_out || p.residual == nullptr);
         const bool rope = f.row_pos != nullptr;            // the launcher grants it to 16-wide tiles only
         float* s_sum = (float*)s_tile;
-        constexpr int ITEMS = BN <= 64 ? BN / 8 : 1;       // pieces per thread: BN * 16 pieces over 128 threads
-        uint4 res[ITEMS];                                  // this thread's pieces of the residual rows, fetched early
+        constexpr int ITEMS = 2;                           // pieces per thread of 16 rows: 16 * 16 pieces over 128 threads
+        uint4 res[ITEMS];                                  // this thread's pieces of the residual rows being finished
         if (rope && f.denom != nullptr && et < (f.rot >> 1)) s_den[et] = f.denom[et];
         // What a staged tile's epilogue reads besides the sums is fetched as soon as the tile is known, while the
         // products are still running: bias and norm weights of the tile's columns, the residual pieces, each row's
         // sequence, position and cache row, and the rotation's cosines and sines.  What remains after the last product
         // is one trip to memory for split-k's partial sums, arithmetic, and stores.
+        // this thread's pieces of the residual rows t_lo .. t_lo + t_cnt - 1 of the tile
+        auto load_res = [&](int p_blk, int q_blk, int t_lo, int t_cnt) {
+            if (p.residual == nullptr) return;
+#pragma unroll
+            for (int k = 0; k < ITEMS; ++k) {
+                const int idx = et + 128 * k;
+                if (idx < t_cnt * 16)
+                    res[k] = __ldcg((const uint4*)((const __nv_bfloat16*)p.residual + (size_t)(q_blk * bn + t_lo + (idx >> 4)) * p.ldo +
+                                                   (size_t)p_blk * TILE_P + (idx & 15) * 8));
+            }
+        };
         auto prefetch_tile = [&](int p_blk, int q_blk) {
             const int nt = min(bn, p.q_rows - q_blk * bn);
             s_bias[et] = p.bias != nullptr ? bias_at(p, p_blk * TILE_P + et) : 0.f;
             if (f.norm_out != nullptr)
                 s_g[et] = f.norm_w_dtype == FR_F32 ? ((const float*)f.norm_w)[p_blk * TILE_P + et]
                                                    : __bfloat162float(((const __nv_bfloat16*)f.norm_w)[p_blk * TILE_P + et]);
-            if (p.residual != nullptr) {
-#pragma unroll
-                for (int k = 0; k < ITEMS; ++k) {
-                    const int idx = et + 128 * k;
-                    if (idx < nt * 16)
-                        res[k] = __ldcg((const uint4*)((const __nv_bfloat16*)p.residual + (size_t)(q_blk * bn + (idx >> 4)) * p.ldo +
-                                                       (size_t)p_blk * TILE_P + (idx & 15) * 8));
-                }
-            }
+            if (BN == 16) load_res(p_blk, q_blk, 0, nt);       // wider tiles fetch them 16 rows at a time, when they finish them
             if (rope && et < nt) {
                 const int row = q_blk * bn + et;
                 const int seq = f.row_seq[row], pos = f.row_pos[row];
@@ -375,14 +383,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             w.x = pack2(x[0], x[1]); w.y = pack2(x[2], x[3]); w.z = pack2(x[4], x[5]); w.w = pack2(x[6], x[7]);
             return w;
         };
-        auto finish_rows = [&](int p_blk, int q_blk) {
-            const int nt = min(bn, p.q_rows - q_blk * bn);
+        auto finish_rows = [&](int p_blk, int q_blk, int t_lo, int t_cnt) {     // rows t_lo .. t_lo + t_cnt - 1 of the tile
             const int half = f.rot >> 1;
 #pragma unroll
             for (int k = 0; k < ITEMS; ++k) {
-                if (k * 128 >= nt * 16) break;
-                const int idx = k * 128 + et, token = idx >> 4, f0 = (idx & 15) * 8;
-                const bool active = idx < nt * 16;
+                if (k * 128 >= t_cnt * 16) break;
+                const int idx = k * 128 + et, token = t_lo + (idx >> 4), f0 = (idx & 15) * 8;
+                const bool active = idx < t_cnt * 16;
                 const int row = q_blk * bn + token, col = p_blk * TILE_P + f0;
                 float ss = 0.f;
                 if (active) {
@@ -490,6 +497,54 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 for (int j = 0; j < 16; ++j) v[j] *= r;
             }
         };
+        // Rows of a staged tile are finished 16 at a time (a chunk of the accumulator's columns): chunks c_begin,
+        // c_begin + c_step, ...  With `summed` the chunk's sums are first gathered from the tile's partial tiles in the
+        // scratch buffer (split-k); otherwise they lie in s_sum already.
+        Work work(p, blockIdx.x, gridDim.x);
+        Item item;
+        auto finish_chunks = [&](int p_blk, int q_blk, int c_begin, int c_step, bool summed) {
+            const int nt = min(bn, p.q_rows - q_blk * bn);
+            const float* mine = p.ws + (size_t)i_local * 4;
+#pragma unroll 1
+            for (int c = c_begin; c * 16 < nt; c += c_step) {
+                const int t_cnt = min(16, nt - c * 16);
+                if (BN > 16) load_res(p_blk, q_blk, c * 16, t_cnt);
+                if (summed) {
+                    float v[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] = 0.f;
+                    // five partial tiles at a time: all their loads are on their way before the first sum
+                    for (int s0 = 0; s0 < item.nseg; s0 += 5) {
+                        float4 x[5][4];
+#pragma unroll
+                        for (int s = 0; s < 5; ++s) {
+                            if (s0 + s < item.nseg) {
+                                const float* src = mine + (size_t)work.contributor(item, s0 + s) * TILE_P * bn + (size_t)c * TILE_P * 16;
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) x[s][j] = __ldcg((const float4*)(src + (size_t)j * TILE_P * 4));
+                            }
+                        }
+#pragma unroll
+                        for (int s = 0; s < 5; ++s) {
+                            if (s0 + s < item.nseg) {
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    v[4 * j] += x[s][j].x; v[4 * j + 1] += x[s][j].y;
+                                    v[4 * j + 2] += x[s][j].z; v[4 * j + 3] += x[s][j].w;
+                                }
+                            }
+                        }
+                    }
+                    if (et == 0) mark(p, 10);
+                    scale16(c, v);
+                    put16(c, v);
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (et == 0) mark(p, 11);
+                }
+                finish_rows(p_blk, q_blk, c * 16, t_cnt);
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+            }
+        };
         for (; ok && work.next(item); ++it) {
             const int tile = item.tile;
             const int q_blk = tile / p.tiles_p, p_blk = tile - q_blk * p.tiles_p;
@@ -529,10 +584,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             if (lane == 0) mbar_arrive(acce0 + 8 * a);     // the accumulator may be overwritten
             if (part == nullptr && staged) {
                 asm volatile("bar.sync 1, 128;" ::: "memory");
-                finish_rows(p_blk, q_blk);
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                finish_chunks(p_blk, q_blk, 0, 1, false);
             }
-            if (item.nseg > 1) {
+            if (item.nseg > 1 && p.shared_finish && staged) {
+                // The partial tile is written.  Tell the tile's other CTAs, wait for all of them (they all run: the
+                // launcher saw to that), then finish every nseg-th group of 16 rows of the tile.
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (et == 0) {
+                    __threadfence();
+                    atomicAdd(p.counters + tile, 1);
+                    const unsigned long long t_wait = global_ns();
+                    bool all = false;
+                    for (uint32_t spin = 1;; ++spin) {
+                        if (*(volatile int*)(p.counters + tile) >= item.nseg) { all = true; break; }
+                        if ((spin & 63u) == 0 && global_ns() - t_wait > WAIT_LIMIT_NS) break;
+                    }
+                    if (!all) atomicCAS(p.status, 0, 5);
+                    __threadfence();
+                    flags[0] = all;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (flags[0]) {
+                    if (et == 0) mark(p, 8);
+                    finish_chunks(p_blk, q_blk, item.part - tile * p.splits, item.nseg, true);
+                    if (et == 0) mark(p, 12);
+                }
+                // the last CTA to leave the tile makes its counters ready for the next launch
+                if (et == 0 && atomicAdd(p.counters + p.dp_tiles + tile, 1) == item.nseg - 1) {
+                    p.counters[tile] = 0;
+                    p.counters[p.dp_tiles + tile] = 0;
+                }
+            } else if (item.nseg > 1) {
                 // The partial tile is written; whoever adds the tile's last one sums them all (thread 0 of the epilogue
                 // publishes for the CTA: the barrier before it orders the other threads' stores before its fence).
                 asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -544,43 +626,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (flags[0]) {
                     if (et == 0) mark(p, 8);
-                    const float* mine = p.ws + (size_t)i_local * 4;
-#pragma unroll 1
-                    for (int c = 0; c < bn / 16; ++c) {
-                        float v[16];
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) v[j] = 0.f;
-                        // eight partial tiles at a time: all their loads are on their way before the first sum
-                        for (int s0 = 0; s0 < item.nseg; s0 += 8) {
-                            float4 x[8][4];
-#pragma unroll
-                            for (int s = 0; s < 8; ++s) {
-                                if (s0 + s < item.nseg) {
-                                    const float* src = mine + (size_t)work.contributor(item, s0 + s) * TILE_P * bn + (size_t)c * TILE_P * 16;
-#pragma unroll
-                                    for (int j = 0; j < 4; ++j) x[s][j] = __ldcg((const float4*)(src + (size_t)j * TILE_P * 4));
-                                }
-                            }
-#pragma unroll
-                            for (int s = 0; s < 8; ++s) {
-                                if (s0 + s < item.nseg) {
-#pragma unroll
-                                    for (int j = 0; j < 4; ++j) {
-                                        v[4 * j] += x[s][j].x; v[4 * j + 1] += x[s][j].y;
-                                        v[4 * j + 2] += x[s][j].z; v[4 * j + 3] += x[s][j].w;
-                                    }
-                                }
-                            }
-                        }
-                        if (et == 0) mark(p, 10);
-                        scale16(c, v);
-                        if (staged) put16(c, v);
-                        else finish16(p, gi, q_blk * bn + c * 16, v);
-                    }
                     if (staged) {
-                        asm volatile("bar.sync 1, 128;" ::: "memory");
-                        if (et == 0) mark(p, 11);
-                        finish_rows(p_blk, q_blk);
+                        finish_chunks(p_blk, q_blk, 0, 1, true);
+                    } else {
+                        const float* mine = p.ws + (size_t)i_local * 4;
+#pragma unroll 1
+                        for (int c = 0; c < bn / 16; ++c) {
+                            float v[16];
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) v[j] = 0.f;
+#pragma unroll 2
+                            for (int sp = 0; sp < item.nseg; ++sp) {
+                                const float* src = mine + (size_t)work.contributor(item, sp) * TILE_P * bn + (size_t)c * TILE_P * 16;
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    const float4 x = __ldcg((const float4*)(src + (size_t)j * TILE_P * 4));
+                                    v[4 * j] += x.x; v[4 * j + 1] += x.y; v[4 * j + 2] += x.z; v[4 * j + 3] += x.w;
+                                }
+                            }
+                            scale16(c, v);
+                            finish16(p, gi, q_blk * bn + c * 16, v);
+                        }
                     }
                     if (et == 0) mark(p, 12);
                     if (et == 0) p.counters[tile] = 0;     // ready for the next launch
@@ -639,6 +705,16 @@ bool use_stream_k() {
     if (v < 0) {
         const char* e = getenv("FRIDAY_STREAM_K");
         v = (e != nullptr && e[0] == '1') ? 1 : 0;
+    }
+    return v != 0;
+}
+
+// FRIDAY_GEMM_SHARED_FINISH=0: the last CTA of a tile to arrive always finishes the whole tile (for comparison).
+bool use_shared_finish() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("FRIDAY_GEMM_SHARED_FINISH");
+        v = (e != nullptr && e[0] == '0') ? 0 : 1;
     }
     return v != 0;
 }
@@ -813,6 +889,8 @@ FR_EXPORT int gemm_tc_fused(const void* x, const void* w, void* out, int out_dty
             grid = sm_count;
         }
     }
+    p.shared_finish = swap && splits > 1 && bn >= 32 && bn <= 64 && !act && grid == tiles * splits && grid <= sm_count &&
+                      2 * tiles <= n_counters && use_shared_finish();
     CUtensorMap mp, mq;
     int rc = swap ? make_map(&mp, w, n, k, ldw, TILE_P) : make_map(&mp, x, m, k, lda, TILE_P);
     if (rc) return rc;
