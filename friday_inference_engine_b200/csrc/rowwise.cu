@@ -311,23 +311,26 @@ FR_EXPORT int rowwise_rope_kv_write(void* qkv, const int* row_seq, const int* ro
 
 // ------------------------------------------------------------------ advance
 // After a decode step that stays on the device: the sampled token becomes the next
-// input, position and length of every live row grow by one.
+// input, position and length of every live row grow by one, and so does the number of
+// draws made for it (the sampler's step counter), if given.
 __global__ void advance_kernel(int* tokens, const int* __restrict__ sampled, int* row_pos, int* kv_len,
-                               const int* __restrict__ row_seq, int n) {
+                               const int* __restrict__ row_seq, int* draws, int n) {
     fr_pdl_wait();
     fr_pdl_launch();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n || row_seq[i] < 0) return;
+    if (i >= n) return;
+    if (draws != nullptr) draws[i] += 1;
+    if (row_seq[i] < 0) return;
     tokens[i] = sampled[i];
     row_pos[i] += 1;
     kv_len[i] += 1;
 }
 
-FR_EXPORT int rowwise_advance(int* tokens, const int* sampled, int* row_pos, int* kv_len, const int* row_seq, int n,
-                              cudaStream_t stream) {
+FR_EXPORT int rowwise_advance(int* tokens, const int* sampled, int* row_pos, int* kv_len, const int* row_seq, int* draws,
+                              int n, cudaStream_t stream) {
     if (n <= 0) return FR_OK;
     FR_CUDA(fr_launch(advance_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, tokens, sampled, row_pos, kv_len,
-                      row_seq, n));
+                      row_seq, draws, n));
     FR_CHECK_LAUNCH("advance");
     return FR_OK;
 }

@@ -132,8 +132,7 @@ class DeviceDecoder:
         self.logits = self.model.logits(x, normed=normed)
         ops.sample(self.logits, self.temperature, self.streams, self.draws, self.seed, row_live=self.row_seq,
                    out=self.sampled)
-        ops.advance(self.tokens, self.sampled, self.row_pos, self.kv_len, self.row_seq)
-        self.draws.add_(1)
+        ops.advance(self.tokens, self.sampled, self.row_pos, self.kv_len, self.row_seq, self.draws)
 
     def _sync_tables(self):
         slots = [s for s, alive in zip(self.slots, self.live) if alive]

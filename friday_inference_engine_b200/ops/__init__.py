@@ -134,9 +134,9 @@ class CudaOps:
             block_table.shape[1] if write else 0, page_size, 1 if write else 0, qkv.shape[0], code_of(qkv.dtype),
             _stream())
 
-    def advance(self, tokens, sampled, row_pos, kv_len, row_seq):
+    def advance(self, tokens, sampled, row_pos, kv_len, row_seq, draws=None):
         lib.family("rowwise").call("rowwise_advance", _ptr(tokens), _ptr(sampled), _ptr(row_pos), _ptr(kv_len),
-                                   _ptr(row_seq), tokens.numel(), _stream())
+                                   _ptr(row_seq), _ptr(draws), tokens.numel(), _stream())
 
     # -- matrix products --------------------------------------------------
     def linear(self, x, weight, bias=None, residual=None, out_dtype=None, out=None):

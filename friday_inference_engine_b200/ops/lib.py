@@ -27,7 +27,7 @@ _SIGNATURES = {
         "rowwise_rmsnorm": [P, P, I, P, I, I, F, I, P],
         "rowwise_swiglu": [P, P, I, I, I, P],
         "rowwise_rope_kv_write": [P, P, P, P, I, I, I, I, P, P, P, I, I, I, I, I, P],
-        "rowwise_advance": [P, P, P, P, P, I, P],
+        "rowwise_advance": [P, P, P, P, P, P, I, P],
     },
     "gemm_simt": {
         "gemm_simt": [P, I, P, I, P, I, P, I, P, I, I, I, I, I, I, P],

@@ -61,7 +61,9 @@ class TorchOps:
                 k_pool[page, pos % page_size] = v3[r, n_heads:n_heads + n_kv_heads]
                 v_pool[page, pos % page_size] = v3[r, n_heads + n_kv_heads:]
 
-    def advance(self, tokens, sampled, row_pos, kv_len, row_seq):
+    def advance(self, tokens, sampled, row_pos, kv_len, row_seq, draws=None):
+        if draws is not None:
+            draws += 1
         live = row_seq >= 0
         tokens[live] = sampled[live]
         row_pos[live] += 1
