@@ -66,7 +66,7 @@ constexpr int SIDE_BYTES = 3 * TILE_P * 4 + 3 * 64 * 4 + 64 * 8;      // row fac
 template <int BN, int STAGES>
 constexpr int smem_bytes() {
     return STAGES * (P_BYTES + BN * TILE_K * 2) + 1024 + (2 * STAGES + 4) * 8 + 64 + SIDE_BYTES +
-           (BN <= 64 ? BN * TILE_P * 4 : 0) + (BN == 16 ? 16 * 64 * 8 : 0);
+           (BN <= 64 ? BN * TILE_P * 4 : BN * 4) + (BN == 16 ? 16 * 64 * 8 : 0);
 }
 
 struct GemmParams {
@@ -180,6 +180,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     constexpr int T_BYTES = BN <= 64 ? BN * TILE_P * 4 : 0;
     uint8_t* s_tile = (uint8_t*)s_scale + SIDE_BYTES;
     float2* s_cs = (float2*)(s_tile + T_BYTES);                              // [16][64], 16-wide tiles only
+    float* s_gw = (float*)s_tile;                                            // [BN] norm weights of the columns of a tile with rows on M
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
     const uint32_t accf0 = smem_u32(bars + 2 * STAGES), acce0 = smem_u32(bars + 2 * STAGES + 2);
@@ -497,6 +498,42 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 for (int j = 0; j < 16; ++j) v[j] *= r;
             }
         };
+        // Rows-on-M orientation with the RMSNorm of the output begun: 16 whole columns of row gi (the launcher has seen
+        // to n % 16 == 0 and 16-byte aligned rows): bias, residual, rounding, store; then the rounded values' squares
+        // into ss and, times the norm's weights, into norm_out.
+        auto finish16_norm = [&](int q_blk, int gi, int gj0, float (&v)[16], float& ss) {
+            if (gi >= p.p_rows || gj0 >= p.q_rows) return;
+            const size_t base = (size_t)gi * p.ldo + gj0;
+            if (p.bias != nullptr)
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] += bias_at(p, gj0 + j);
+            if (p.residual != nullptr) {
+                const uint4* rp = (const uint4*)((const __nv_bfloat16*)p.residual + base);
+                const uint4 r0 = rp[0], r1 = rp[1];
+                const uint32_t rw[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    v[2 * j] += __uint_as_float(rw[j] << 16);
+                    v[2 * j + 1] += __uint_as_float(rw[j] & 0xffff0000u);
+                }
+            }
+            uint32_t w[8], h[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                w[j] = pack2(v[2 * j], v[2 * j + 1]);
+                const float x0 = __uint_as_float(w[j] << 16), x1 = __uint_as_float(w[j] & 0xffff0000u);
+                ss += x0 * x0;
+                ss += x1 * x1;
+                h[j] = pack2(x0 * s_gw[gj0 - q_blk * bn + 2 * j], x1 * s_gw[gj0 - q_blk * bn + 2 * j + 1]);
+            }
+            uint4* o = (uint4*)((__nv_bfloat16*)p.out + base);
+            o[0] = make_uint4(w[0], w[1], w[2], w[3]);
+            o[1] = make_uint4(w[4], w[5], w[6], w[7]);
+            uint4* ho = (uint4*)((__nv_bfloat16*)f.norm_out + base);
+            ho[0] = make_uint4(h[0], h[1], h[2], h[3]);
+            ho[1] = make_uint4(h[4], h[5], h[6], h[7]);
+        };
+        const bool norm_rows = f.norm_out != nullptr && !p.swapped;
         // Rows of a staged tile are finished 16 at a time (a chunk of the accumulator's columns): chunks c_begin,
         // c_begin + c_step, ...  With `summed` the chunk's sums are first gathered from the tile's partial tiles in the
         // scratch buffer (split-k); otherwise they lie in s_sum already.
@@ -554,6 +591,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             const bool staged = can_stage && (p_blk + 1) * TILE_P <= p.p_rows;
             load_scale(p.swapped ? q_blk : p_blk);
             if (staged) prefetch_tile(p_blk, q_blk);
+            float ss_row = 0.f;                            // rows-on-M with a norm begun: this row's sum of squares over the tile
+            if (norm_rows) {
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                for (int i = et; i < bn; i += 128) {
+                    const int col = q_blk * bn + i;
+                    s_gw[i] = col >= p.q_rows ? 0.f : f.norm_w_dtype == FR_F32 ? ((const float*)f.norm_w)[col]
+                                                                               : __bfloat162float(((const __nv_bfloat16*)f.norm_w)[col]);
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+            }
             if (!(ok = mbar_wait(accf0 + 8 * a, acc_phase, p.status, 4))) break;
             if (et == 0) mark(p, 6);
             tc_fence_after();
@@ -572,6 +619,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 if (part == nullptr) {
                     scale16(c, v);
                     if (staged) put16(c, v);
+                    else if (norm_rows) finish16_norm(q_blk, gi, q_blk * bn + c * 16, v, ss_row);
                     else finish16(p, gi, q_blk * bn + c * 16, v);
                 } else {
 #pragma unroll
@@ -645,7 +693,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                                 }
                             }
                             scale16(c, v);
-                            finish16(p, gi, q_blk * bn + c * 16, v);
+                            if (norm_rows) finish16_norm(q_blk, gi, q_blk * bn + c * 16, v, ss_row);
+                            else finish16(p, gi, q_blk * bn + c * 16, v);
                         }
                     }
                     if (et == 0) mark(p, 12);
@@ -653,6 +702,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");
             }
+            if (norm_rows && gi < p.p_rows && (item.nseg == 1 || flags[0])) f.out_ssq[(size_t)q_blk * p.p_rows + gi] = ss_row;
             if (et == 0) mark(p, 7);
         }
     }
@@ -845,12 +895,19 @@ FR_EXPORT int gemm_tc_fused(const void* x, const void* w, void* out, int out_dty
         const bool rope = f.row_pos != nullptr || f.row_seq != nullptr || f.denom != nullptr || f.k_pool != nullptr;
         if (f.in_ssq != nullptr && (f.in_parts <= 0 || !(f.in_width > 0.f) || (swap && bn > TILE_P)))
             FR_REFUSE("gemm_tc: a deferred norm of the input needs its partial sums, the width, and tiles of at most %d rows", TILE_P);
-        if (f.norm_out != nullptr || rope) {
+        if (rope || (f.norm_out != nullptr && swap)) {
             // both work on the staged tile of the swapped orientation: whole tiles of 128 columns, rows of 16-byte pieces
             if (!swap || act || out_dtype != FR_BF16 || bn > 64 || n % TILE_P || ldo % 8 ||
                 (((uintptr_t)out | (uintptr_t)residual | (uintptr_t)f.norm_out) & 15))
                 FR_REFUSE("gemm_tc: a fused norm or rotation needs few rows (swapped tiles up to 64 wide), bf16 output "
                           "without activation, n a multiple of %d and 16-byte aligned rows", TILE_P);
+        }
+        if (f.norm_out != nullptr && !swap) {
+            // rows on the M side: every thread finishes whole groups of 16 columns of its row
+            if (act || out_dtype != FR_BF16 || n % 16 || ldo % 8 || 
+                (((uintptr_t)out | (uintptr_t)residual | (uintptr_t)f.norm_out) & 15))
+                FR_REFUSE("gemm_tc: a fused norm needs bf16 output without activation, n a multiple of 16 and 16-byte "
+                          "aligned rows");
         }
         if (f.norm_out != nullptr && (f.norm_w == nullptr || f.out_ssq == nullptr))
             FR_REFUSE("gemm_tc: a fused norm needs its weight and a buffer for the sums of squares");

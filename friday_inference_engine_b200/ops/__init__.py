@@ -8,6 +8,7 @@ kernel library that cannot be built or loaded is an error.
 exists so that tests of the code *around* the kernels (cache, step function, loop) can
 run where there is no GPU, with a stand-in defined in the tests.
 """
+import numpy as np
 import torch
 
 from . import lib
@@ -173,10 +174,10 @@ class CudaOps:
         fusion.in_width, fusion.in_eps = float(deferred.scaled.shape[1]), deferred.eps
         return fusion
 
-    def _few_rows_tile_ok(self, x, weight, out, residual, max_rows):
-        """What the fused epilogues of the tensor-core product need: a one-token step's few rows, bf16, whole
-        tiles of 128 output columns."""
-        return (fusion_enabled() and out.dtype == torch.bfloat16 and x.shape[0] <= max_rows and weight.shape[0] % 128 == 0
+    def _few_rows_tile_ok(self, x, weight, out, residual, max_rows, columns=128):
+        """What the fused epilogues of the tensor-core product need: no more rows than max_rows, bf16, whole
+        groups of `columns` output columns (128: the tiles of a one-token step's few rows)."""
+        return (fusion_enabled() and out.dtype == torch.bfloat16 and x.shape[0] <= max_rows and weight.shape[0] % columns == 0
                 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0
                 and (residual is None or residual.data_ptr() % 16 == 0)
                 and self.tensor_core_ok(x, weight, out, residual))
@@ -201,6 +202,22 @@ class CudaOps:
                 fusion.norm_out, fusion.out_ssq = _ptr(scaled), _ptr(ssq)
                 self._linear_tc(xt, weight, bias, residual, out, fusion=fusion)
                 return out, DeferredNorm(scaled, ssq, eps, out, norm_weight)
+            if rows > 64 and n % 16 == 0 and self._few_rows_tile_ok(xt, weight, out, residual, rows, 16) \
+                    and norm_weight.is_contiguous():
+                # many rows: the rows lie on the tiles' M side and every column tile adds one partial sum per row
+                if residual is not None:
+                    assert residual.shape == out.shape and residual.dtype == out.dtype and residual.stride() == out.stride()
+                plan = np.zeros((8,), dtype=np.int64)
+                lib.family("gemm_tc").call("gemm_tc_plan", rows, n, xt.shape[1], self._tc_buffers(xt.device)[3], -1, -1,
+                                           -1, plan.ctypes.data)
+                if plan[0] == 0:
+                    scaled = torch.empty_like(out)
+                    ssq = torch.empty((-(-n // int(plan[1])), rows), dtype=torch.float32, device=out.device)
+                    fusion = self._fusion_in(deferred, lib.GemmFusion())
+                    fusion.norm_w, fusion.norm_w_dtype = _ptr(norm_weight), code_of(norm_weight.dtype)
+                    fusion.norm_out, fusion.out_ssq = _ptr(scaled), _ptr(ssq)
+                    self._linear_tc(xt, weight, bias, residual, out, fusion=fusion)
+                    return out, DeferredNorm(scaled, ssq, eps, out, norm_weight)
         out = self.linear(x, weight, bias=bias, residual=residual)
         return out, self.rmsnorm(out, norm_weight, eps)
 

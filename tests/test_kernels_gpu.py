@@ -507,13 +507,49 @@ def test_gemm_begins_a_norm_that_the_next_gemm_finishes(m, n, k, k2, monkeypatch
     # a consumer that cannot finish the norm itself (a k that is no multiple of 8 is not for the tensor cores;
     # here: fp32 weights) gets the rows from the norm's own kernel
     close(ops.linear(h, w2.float()), ref, torch.bfloat16, "consumer on the CUDA cores")
-    # many rows: the norm's own kernel runs and a tensor comes back
-    xs = rnd((80, k), torch.bfloat16, 87, 0.5)
-    out3, h3 = ops.linear_norm(xs, w, g, eps)
-    assert torch.is_tensor(h3)
-    close(h3, pm.rms_norm(f64(out3), f64(g), eps), torch.bfloat16, "unfused norm")
     monkeypatch.setenv("FRIDAY_FUSE", "0")
-    assert torch.is_tensor(ops.linear_norm(x, w, g, eps, residual=res)[1])
+    out3, h3 = ops.linear_norm(x, w, g, eps, residual=res)
+    assert torch.is_tensor(h3), "switched off: the norm's own kernel runs and a tensor comes back"
+    close(h3, pm.rms_norm(f64(out3), f64(g), eps), torch.bfloat16, "unfused norm")
+    ops.backend().check_status()
+
+
+@pytest.mark.parametrize("m,n,k,k2", [(80, 3584, 512, 96), (128, 640, 4096, 64), (65, 48, 64, 24), (300, 3584, 1024, 128),
+                                      (2048, 3584, 256, 104), (257, 208, 72, 512), (130, 272, 18944, 40)])
+def test_gemm_of_many_rows_begins_a_norm(m, n, k, k2):
+    """More than 64 rows lie on the tiles' M side: every column tile, whatever its width, adds one share of each
+    row's sum of squares; the next product, the same way round, finishes the norm."""
+    x, w = rnd((m, k), torch.bfloat16, 180, 0.5), rnd((n, k), torch.bfloat16, 181, 0.05)
+    res, b = rnd((m, n), torch.bfloat16, 182, 2.0), rnd((n,), torch.bfloat16, 183)
+    g = rnd((n,), torch.bfloat16, 184) + 1.0
+    eps = 1e-6
+    out, h = ops.linear_norm(x, w, g, eps, bias=b, residual=res)
+    assert isinstance(h, ops.DeferredNorm)
+    assert torch.equal(out, ops.linear(x, w, bias=b, residual=res)), "the product itself is unchanged"
+    plan = np.zeros(5, dtype=np.int64)
+    ops.lib.family("gemm_tc").call("gemm_tc_plan", m, n, k, 148, -1, -1, -1, plan.ctypes.data)
+    bn = int(plan[1])
+    assert plan[0] == 0 and h.ssq.shape == (-(-n // bn), m)
+    sq = f64(out) ** 2
+    ssq = np.stack([sq[:, c:c + bn].sum(-1) for c in range(0, n, bn)])
+    close(h.ssq, ssq, torch.float32, "partial sums of squares", fp32_tol=1e-5)
+    close(h.scaled, f64(out) * f64(g), torch.bfloat16, "rows times the norm's weights")
+    normed = pm.rms_norm(f64(out), f64(g), eps)
+    close(h.materialize(), normed, torch.bfloat16, "materialised")
+    w2 = rnd((k2 * 2, n), torch.bfloat16, 185, 0.05)
+    ref = normed @ f64(w2).T
+    close(ops.linear(h, w2), ref, torch.bfloat16, "consumer")
+    close(ops.linear_swiglu(h, w2), pm.swiglu(ref[:, 0::2], ref[:, 1::2]), torch.bfloat16, "gated consumer")
+    if (2 * k2) % 16 == 0:
+        g2 = rnd((2 * k2,), torch.bfloat16, 186) + 1.0
+        out2, h2 = ops.linear_norm(h, w2, g2, eps)
+        assert isinstance(h2, ops.DeferredNorm)
+        close(out2, ref, torch.bfloat16, "consumer that begins a norm")
+        close(h2.materialize(), pm.rms_norm(f64(out2), f64(g2), eps), torch.bfloat16, "second norm")
+    # a width that is no multiple of 16: the norm's own kernel
+    out3, h3 = ops.linear_norm(x, w[:n - 8], g[:n - 8], eps)
+    assert torch.is_tensor(h3)
+    close(h3, pm.rms_norm(f64(out3), f64(g[:n - 8]), eps), torch.bfloat16, "unfused norm")
     ops.backend().check_status()
 
 
