@@ -301,7 +301,7 @@ def cta_trace(eng, batch):
     t = tc.cpu().numpy().astype(np.float64)
     t = t[t[:, 5] > 0]
     blocks = t[:, 5].sum()
-    print("prompt attention, %d tokens: %d CTAs, %d blocks of 128 keys; us per block: " % (PREFILL_TOKENS, len(t), blocks)
+    print("prompt attention, %d tokens: %d CTAs, %d blocks of 64 keys; us per block: " % (PREFILL_TOKENS, len(t), blocks)
           + ", ".join("%s %.2f" % (what, t[:, k].sum() / blocks / 1000.0) for k, what in
                       ((0, "row waits for S"), (1, "reads S, maximum"), (2, "exponentials and P"), (3, "rescales O"),
                        (4, "waits for the last product"), (8, "issuer waits for K"), (9, "issues Q K^T"),

@@ -3,25 +3,28 @@
 //
 // A CTA owns up to 128 rows of one sequence and kv head; row r stands for (token r / G, group head r % G),
 // G = heads / kv heads, so a block of keys and values is read once for all heads that share it (as the reference's
-// R = tq*G + g rows: attention_kernels.cu:493-499).  Blocks of 128 keys are two pages of the cache.
+// R = tq*G + g rows: attention_kernels.cu:493-499).  A block of 64 keys is one page of the cache; even and odd blocks
+// alternate between two stages of everything a block needs (K, V, the columns of S, the barriers).
 //
 //   warp 0      TMA producer: the queries (a 4-d box [64 dims][G heads][1][T tokens] per 64-dim slice lands as
-//               rows t*G + g, 128-byte swizzle), then per block the two K pages and the two V pages.  K's buffer is
-//               free again once the scores are done, V's after the second product.  A page that the block does
-//               not need, or that the table does not name, is loaded from beyond the pool's last row, which fills
-//               zeros.
-//   warp 1      allocates tensor memory (256 columns: S, and O); one lane issues S = Q K^T (M = 128 rows, N = 128
-//               keys, both operands K-major from shared memory) and O += P V (A = P from tensor memory, where it
-//               lies over the first half of S's columns; B = V as it lies in the cache, [keys][dims] = MN-major).
-//   warps 2-5   one thread per row (its TMEM lane): reads its row of S twice from tensor memory (maximum, then
-//               exponentials), keeps the running maximum and sum, and writes P (bf16, two to a column) back into
-//               tensor memory behind its reading.  The maximum that P is taken against only moves when a row's true
-//               maximum has grown by more than 8 (in log2 units; P then stays below 2^8 and the sums remain exact
-//               for that reference); only then is O rescaled, in tensor memory.  At the end the row's O is divided
-//               by its sum.
+//               rows t*G + g, 128-byte swizzle), then the K page of the block after and the V page of this one.  A
+//               stage of K is free again once its scores are done, one of V after the second product.  A page that
+//               the block does not need, or that the table does not name, is loaded from beyond the pool's last row,
+//               which fills zeros.
+//   warp 1      allocates tensor memory (256 columns: S of even blocks, S of odd blocks, O); one lane issues
+//               S = Q K^T (M = 128 rows, N = 64 keys, both operands K-major from shared memory) two blocks ahead of
+//               O += P V (A = P from tensor memory, where it lies over the first half of its S's columns; B = V as
+//               it lies in the cache, [keys][dims] = MN-major): the scores of block i + 1 are ready when the rows
+//               have finished block i, and the tensor core works on one block's products while the rows
+//               exponentiate the other's.
+//   warps 2-5   one thread per row (its TMEM lane): reads its 64 scores from tensor memory, takes maximum and
+//               exponentials, keeps the running maximum and sum, and writes P (bf16, two to a column) back into
+//               tensor memory.  The maximum that P is taken against only moves when a row's true maximum has grown
+//               by more than 8 (in log2 units; P then stays below 2^8 and the sums remain exact for that reference);
+//               only then is O rescaled, in tensor memory.  At the end the row's O is divided by its sum.
 //
 // Neither P nor O ever leaves tensor memory before the output is written.  A CTA needs 97 KB of shared memory and
-// half the tensor memory, so two share an SM: while the rows of one exponentiate, the products of the other run.
+// half the tensor memory, so two share an SM.
 // Scores, softmax and sums are fp32; P is rounded to bf16 for the second product, as the mma.sync kernel does.
 // Rows of V past the last key that any row of the CTA may see are zeroed in shared memory before the product (their
 // P is zero, but zero times a stale NaN is not); stale K only reaches scores that the mask replaces.  Long tiles (late
@@ -46,10 +49,12 @@ using namespace tc;
 typedef __nv_bfloat16 bf16;
 constexpr int THREADS = 192;
 constexpr int ROWS = 128;                 // rows of a CTA = M of the instruction
-constexpr int KEYS = 128;                 // keys of a block = two cache pages
+constexpr int KEYS = 64;                  // keys of a block = one cache page
 constexpr int PAGE = 64;
 constexpr int SLICE = ROWS * 128;         // bytes of 128 rows of 64 bf16 (one 128-byte swizzle row each)
-constexpr int TMEM_COLS = 256;           // S (and P over it) | O
+constexpr int KSLICE = KEYS * 128;        // bytes of a block's keys (or values), 64 dims of them
+constexpr int KV_STAGE = 2 * KSLICE;      // a block's keys (or values): two slices of 64 dims
+constexpr int TMEM_COLS = 256;           // S of even blocks | S of odd blocks (P over the first half of each) | O
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct TcArgs {
@@ -112,6 +117,14 @@ __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32])
 }
 __device__ __forceinline__ void tc_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// 2^x by the special-function unit alone: exp2f() adds a range fix for results below 2^-126, which a probability
+// that is rounded to bf16 and summed in fp32 has no use for (they become 0 here).
+__device__ __forceinline__ float exp2_fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&v);
@@ -142,16 +155,17 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* s_q = smem;                              // [2 slices][128 rows][128 B]
-    uint8_t* s_k = s_q + 2 * SLICE;                   // [2 slices][128 keys][128 B]
-    uint8_t* s_v = s_k + 2 * SLICE;                   // [2 slices of 64 dims][128 keys][128 B]
-    uint64_t* bars = (uint64_t*)(s_v + 2 * SLICE);
-    // bars: q_full, k_full, k_empty, v_full, v_empty, s_full, p_full, pv_done
-    uint32_t* tmem_slot = (uint32_t*)(bars + 8);
+    uint8_t* s_k = s_q + 2 * SLICE;                   // [2 stages][2 slices][64 keys][128 B]
+    uint8_t* s_v = s_k + 2 * KV_STAGE;                // [2 stages][2 slices of 64 dims][64 keys][128 B]
+    uint64_t* bars = (uint64_t*)(s_v + 2 * KV_STAGE);
+    // bars: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], pv_done[2]
+    uint32_t* tmem_slot = (uint32_t*)(bars + 15);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t q_full = smem_u32(bars), k_full = smem_u32(bars + 1), k_empty = smem_u32(bars + 2);
-    const uint32_t v_full = smem_u32(bars + 3), v_empty = smem_u32(bars + 4);
-    const uint32_t s_full = smem_u32(bars + 5), p_full = smem_u32(bars + 6), pv_done = smem_u32(bars + 7);
+    const uint32_t q_full = smem_u32(bars), k_full = smem_u32(bars + 1), k_empty = smem_u32(bars + 3);
+    const uint32_t v_full = smem_u32(bars + 5), v_empty = smem_u32(bars + 7);
+    const uint32_t s_full = smem_u32(bars + 9), p_full = smem_u32(bars + 11), pv_done = smem_u32(bars + 13);
+    // the barrier of stage b of a pair lies 8 bytes after that of stage 0
 
     // The CTA's rows and its range of key blocks.  The step's geometry is final before the step's first kernel
     // starts (common.cuh), so it is read ahead of the wait.
@@ -170,13 +184,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
-        mbar_init(k_full, 1);
-        mbar_init(k_empty, 1);
-        mbar_init(v_full, 1);
-        mbar_init(v_empty, 1);
-        mbar_init(s_full, 1);
-        mbar_init(p_full, 128);
-        mbar_init(pv_done, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(k_full + 8 * b, 1);
+            mbar_init(k_empty + 8 * b, 1);
+            mbar_init(v_full + 8 * b, 1);
+            mbar_init(v_empty + 8 * b, 1);
+            mbar_init(s_full + 8 * b, 1);
+            mbar_init(p_full + 8 * b, 128);
+            mbar_init(pv_done + 8 * b, 1);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -190,10 +206,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + KEYS;      // columns: S (P over its first half) | O
+    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * KEYS;      // columns: S0 | S1 (P over each one's first half) | O
     fr_pdl_wait();
     if (threadIdx.x == 0) fr_pdl_launch();
 
+    // Block i of the CTA uses stage i & 1 of K, V and S; its barriers are in their (i >> 1)-th use.
     if (warp == 0) {
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
@@ -203,29 +220,31 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             for (int s = 0; s < slices; ++s)
                 tma_load_4d(smem_u32(s_q + s * SLICE), &map_q, s * 64, 0, kvh, q_start + t0, q_full);
             const int* table = p.block_table + (size_t)seq * p.table_width;
-            bool ok = true;
-            for (int i = 0; i < n_blocks && ok; ++i) {
-                const int kb = kb_begin + i;
-                int rows[2];
-                for (int h = 0; h < 2; ++h) {
-                    const int lp = kb * 2 + h;
-                    rows[h] = p.pool_rows;                                   // beyond the pool: the box is filled with zeros
-                    if (lp * PAGE <= pos_hi && lp < p.table_width) {
-                        const int page = table[lp];
-                        if (page >= 0) rows[h] = page * PAGE;
-                    }
+            // the pool row of block i's page; a page that the table does not name is loaded from beyond the pool's last
+            // row, which fills zeros
+            auto page_row = [&](int i) {
+                const int lp = kb_begin + i;
+                if (lp * PAGE <= pos_hi && lp < p.table_width) {
+                    const int page = table[lp];
+                    if (page >= 0) return page * PAGE;
                 }
-                // K is free again as soon as its scores are done, V after the second product
-                if (!(ok = mbar_wait(k_empty, (i & 1) ^ 1, p.status, 1))) break;
-                mbar_expect_tx(k_full, (uint32_t)slices * 2 * PAGE * 128);
-                for (int h = 0; h < 2; ++h)
-                    for (int s = 0; s < slices; ++s)
-                        tma_load_3d(smem_u32(s_k) + (uint32_t)(s * SLICE + h * PAGE * 128), &map_k, s * 64, kvh, rows[h], k_full);
-                if (!(ok = mbar_wait(v_empty, (i & 1) ^ 1, p.status, 1))) break;
-                mbar_expect_tx(v_full, (uint32_t)slices * 2 * PAGE * 128);
-                for (int h = 0; h < 2; ++h)
-                    for (int s = 0; s < slices; ++s)
-                        tma_load_3d(smem_u32(s_v) + (uint32_t)(s * SLICE + h * PAGE * 128), &map_v, s * 64, kvh, rows[h], v_full);
+                return p.pool_rows;
+            };
+            // a stage is free again when the product that read it is done: K after the scores, V after the second product
+            auto load = [&](int i, const CUtensorMap* map, uint8_t* ring, uint32_t full, uint32_t empty) {
+                const int b = i & 1, par = (i >> 1) & 1;
+                if (!mbar_wait(empty + 8 * b, par ^ 1, p.status, 1)) return false;
+                mbar_expect_tx(full + 8 * b, (uint32_t)slices * KSLICE);
+                const int row = page_row(i);
+                for (int s = 0; s < slices; ++s)
+                    tma_load_3d(smem_u32(ring) + (uint32_t)(b * KV_STAGE + s * KSLICE), map, s * 64, kvh, row, full + 8 * b);
+                return true;
+            };
+            // in the order in which the products want them: K of the block after, then V of this one
+            bool ok = load(0, &map_k, s_k, k_full, k_empty);
+            for (int i = 0; i < n_blocks && ok; ++i) {
+                if (i + 1 < n_blocks) ok = load(i + 1, &map_k, s_k, k_full, k_empty);
+                if (ok) ok = load(i, &map_v, s_v, v_full, v_empty);
             }
         }
     } else if (warp == 1) {
@@ -242,36 +261,46 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     m_mark = now;
                 }
             };
-            for (int i = 0; i < n_blocks && ok; ++i) {
-                // S = Q K^T.  The tensor core takes its instructions in order, so the S columns (and P over them)
-                // are free: the product of P V of the block before was issued earlier.
-                if (!(ok = mbar_wait(k_full, i & 1, p.status, 3))) break;
+            // S[i & 1] = Q K_i^T.  The tensor core takes its instructions in order, so the columns of S[i & 1] (and P
+            // over them) are free: the product P V of block i - 2 was issued earlier.
+            auto scores = [&](int i) {
+                const int b = i & 1, par = (i >> 1) & 1;
+                if (!mbar_wait(k_full + 8 * b, par, p.status, 3)) return false;
                 mlap(0);
                 tc_fence_after();
                 for (int ks = 0; ks < k_steps; ++ks) {
                     const int s = ks >> 2, k = ks & 3;
                     const uint64_t da = smem_desc(smem_u32(s_q + s * SLICE)) + 2 * k;
-                    const uint64_t db = smem_desc(smem_u32(s_k + s * SLICE)) + 2 * k;
-                    tc_mma(tmem_s, da, db, idesc_qk, ks > 0 ? 1u : 0u);
+                    const uint64_t db = smem_desc(smem_u32(s_k + b * KV_STAGE + s * KSLICE)) + 2 * k;
+                    tc_mma(tmem_s + b * KEYS, da, db, idesc_qk, ks > 0 ? 1u : 0u);
                 }
-                tc_commit(s_full);
-                tc_commit(k_empty);
+                tc_commit(s_full + 8 * b);
+                tc_commit(k_empty + 8 * b);
                 mlap(1);
-                if (!(ok = mbar_wait(v_full, i & 1, p.status, 3))) break;
+                return true;
+            };
+            // The scores run two blocks ahead of the second product: while the rows of block i exponentiate, the
+            // scores of block i + 1 are done or under way.
+            if (ok) ok = scores(0);
+            if (ok && n_blocks > 1) ok = scores(1);
+            for (int i = 0; i < n_blocks && ok; ++i) {
+                const int b = i & 1, par = (i >> 1) & 1;
+                if (!(ok = mbar_wait(v_full + 8 * b, par, p.status, 3))) break;
                 mlap(2);
-                if (!(ok = mbar_wait(p_full, i & 1, p.status, 4))) break;
+                if (!(ok = mbar_wait(p_full + 8 * b, par, p.status, 4))) break;
                 mlap(3);
                 tc_fence_after();
                 // O += P V over the keys of this block that some row may see, in steps of 16; P from tensor memory
                 const int keys_here = min(KEYS, pos_hi - (kb_begin + i) * KEYS + 1);
                 const int pv_steps = (keys_here + 15) / 16;
                 for (int ks = 0; ks < pv_steps; ++ks) {
-                    const uint64_t db = smem_desc_mn(smem_u32(s_v) + ks * 16 * 128, SLICE, 1024);
-                    tc_mma_ta(tmem_o, tmem_s + 8 * ks, db, idesc_pv, (i > 0 || ks > 0) ? 1u : 0u);
+                    const uint64_t db = smem_desc_mn(smem_u32(s_v) + b * KV_STAGE + ks * 16 * 128, KSLICE, 1024);
+                    tc_mma_ta(tmem_o, tmem_s + b * KEYS + 8 * ks, db, idesc_pv, (i > 0 || ks > 0) ? 1u : 0u);
                 }
-                tc_commit(pv_done);
-                tc_commit(v_empty);
+                tc_commit(pv_done + 8 * b);
+                tc_commit(v_empty + 8 * b);
                 mlap(4);
+                if (i + 2 < n_blocks) ok = scores(i + 2);
             }
             if (p.trace != nullptr) {
                 unsigned long long* at = p.trace + ((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 + 8;
@@ -299,36 +328,41 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             }
         };
         for (int i = 0; i < n_blocks && ok; ++i) {
+            const int b = i & 1, par = (i >> 1) & 1;
             const int kb = kb_begin + i;
             const int j0 = kb * KEYS;
-            if (!(ok = mbar_wait(s_full, i & 1, p.status, 6))) break;
+            if (!(ok = mbar_wait(s_full + 8 * b, par, p.status, 6))) break;
             tc_fence_after();
             lap(0);
-            // Two passes over the row of S in tensor memory, 32 columns at a time, as compact loops (the fully
-            // unrolled form, with the row held in 128 registers, ran three times slower: it does not fit the
-            // instruction cache).  Masked and unmasked blocks have loops of their own; most blocks need no mask
-            // (the choice must be the same for a whole warp: the loads from tensor memory are warp-wide instructions).
-            const uint32_t s_addr = tmem_s + lane_addr;
+            // The row's 64 scores are read from tensor memory once and stay in registers for both passes.  Masked and
+            // unmasked blocks have code of their own; most blocks need no mask (the choice must be the same for a whole
+            // warp: loads from and stores to tensor memory are warp-wide instructions).
+            const uint32_t s_addr = tmem_s + b * KEYS + lane_addr;
             const bool need_mask = __any_sync(0xffffffffu, j0 + KEYS - 1 > pos0 + t0 ||
                                                                (p.window > 0 && j0 < pos_hi - p.window + 1) || !valid);
-            float mx = -INFINITY;
-            auto max_pass = [&](auto masked) {
-#pragma unroll 1
-                for (int c = 0; c < KEYS / 32; ++c) {
-                    uint32_t raw[32];
-                    tc_ld32(s_addr + c * 32, raw);
-                    tc_ld_wait();
-                    const int hi = pos_r - (j0 + c * 32), lo = lo_r - (j0 + c * 32);    // columns hi < j or j < lo are masked
+            uint32_t raw[KEYS];
+            {
+                uint32_t (&lo32)[32] = *reinterpret_cast<uint32_t (*)[32]>(&raw[0]);
+                uint32_t (&hi32)[32] = *reinterpret_cast<uint32_t (*)[32]>(&raw[32]);
+                tc_ld32(s_addr, lo32);
+                tc_ld32(s_addr + 32, hi32);
+                tc_ld_wait();
+            }
+            const int hi = pos_r - j0, lo = lo_r - j0;     // columns hi < j or j < lo are masked
+            // The maximum of the raw scores in four strands (one strand of dependent comparisons would be paid in full:
+            // a scheduler has few such warps to choose from); the positive scale is applied to the result.
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            if (need_mask) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        float v = __uint_as_float(raw[j]) * p.scale_log2;
-                        if (decltype(masked)::value && (j > hi || j < lo)) v = -INFINITY;
-                        mx = fmaxf(mx, v);
-                    }
+                for (int j = 0; j < KEYS; ++j) {
+                    if (j > hi || j < lo) raw[j] = 0xff800000u;      // -inf
+                    mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(raw[j]));
                 }
-            };
-            if (need_mask) max_pass(std::true_type{});
-            else max_pass(std::false_type{});
+            } else {
+#pragma unroll
+                for (int j = 0; j < KEYS; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(raw[j]));
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
             lap(1);
             // The reference maximum moves only when the true one has grown by more than 8; O is rescaled then.
             // tcgen05.ld and .st are warp-wide, so a warp rescales if any of its rows must.
@@ -340,62 +374,49 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     l_run *= alpha;
                 }
                 if (i > 0) {
-                    // every product into O so far must be done
-                    if (!(ok = mbar_wait(pv_done, (i - 1) & 1, p.status, 8))) break;
+                    // every product into O so far must be done.  (The scores of this block were issued after the second
+                    // product of block i - 2, so that one is done: a wait for a phase's parity is unambiguous only if
+                    // the barrier is at most one phase behind, which is why the blocks alternate between two barriers.)
+                    if (!(ok = mbar_wait(pv_done + 8 * (b ^ 1), ((i - 1) >> 1) & 1, p.status, 8))) break;
                     tc_fence_after();
 #pragma unroll 1
-                    for (int c = 0; c < 4; ++c) {
-                        if (c * 32 < p.hd) {
-                            uint32_t raw[32];
-                            tc_ld32(tmem_o + lane_addr + c * 32, raw);
+                    for (int c = 0; c < 8; ++c) {
+                        if (c * 16 < p.hd) {
+                            uint32_t o16[16];
+                            tc_ld16(tmem_o + lane_addr + c * 16, o16);
                             tc_ld_wait();
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) raw[j] = __float_as_uint(__uint_as_float(raw[j]) * alpha);
-                            tc_st32(tmem_o + lane_addr + c * 32, raw);
+                            for (int j = 0; j < 16; ++j) o16[j] = __float_as_uint(__uint_as_float(o16[j]) * alpha);
+                            tc_st16(tmem_o + lane_addr + c * 16, o16);
                         }
                     }
                     tc_st_wait();
                 }
             }
             lap(3);
-            // Exponentials; P (bf16, two to a column) goes over the columns of S that this pass has already read:
-            // 32 scores in, 16 columns out, always behind the reading.
-            const float m_use = m_run == -INFINITY ? 0.f : m_run;
-            float sum = 0.f;
-            auto exp_pass = [&](auto masked) {
-#pragma unroll 1
-                for (int c = 0; c < KEYS / 32; ++c) {
-                    uint32_t raw[32];
-                    tc_ld32(s_addr + c * 32, raw);
-                    tc_ld_wait();
-                    const int hi = pos_r - (j0 + c * 32), lo = lo_r - (j0 + c * 32);
-                    uint32_t packed[16];
+            // Exponentials; P (bf16, two to a column) goes over the first half of the columns of S.  A masked score is
+            // -inf and stays so; a row that has seen no key takes its exponentials against 0.
+            const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};            // four strands, for the same reason
+            uint32_t packed[KEYS / 2];
 #pragma unroll
-                    for (int j = 0; j < 32; j += 2) {
-                        float v0 = __uint_as_float(raw[j]) * p.scale_log2, v1 = __uint_as_float(raw[j + 1]) * p.scale_log2;
-                        if (decltype(masked)::value) {
-                            if (j > hi || j < lo) v0 = -INFINITY;
-                            if (j + 1 > hi || j + 1 < lo) v1 = -INFINITY;
-                        }
-                        const float e0 = exp2f(v0 - m_use), e1 = exp2f(v1 - m_use);
-                        sum += e0;
-                        sum += e1;
-                        packed[j >> 1] = pack2(e0, e1);
-                    }
-                    tc_st16(s_addr + c * 16, packed);
-                }
-            };
-            if (need_mask) exp_pass(std::true_type{});
-            else exp_pass(std::false_type{});
+            for (int j = 0; j < KEYS; j += 2) {
+                const float e0 = exp2_fast(fmaf(__uint_as_float(raw[j]), p.scale_log2, neg_m));
+                const float e1 = exp2_fast(fmaf(__uint_as_float(raw[j + 1]), p.scale_log2, neg_m));
+                sum4[j & 2] += e0;
+                sum4[(j & 2) + 1] += e1;
+                packed[j >> 1] = pack2(e0, e1);
+            }
+            tc_st32(s_addr, packed);
             tc_st_wait();
-            l_run += sum;
+            l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             if (kb == kb_end) {
                 // keys past the last one that any row may see: their V rows may hold anything; zero them
                 const int key = j0 + r;
-                if (key > pos_hi) {
-                    if (!(ok = mbar_wait(v_full, i & 1, p.status, 7))) break;
+                if (r < KEYS && key > pos_hi) {
+                    if (!(ok = mbar_wait(v_full + 8 * b, par, p.status, 7))) break;
                     for (int s = 0; s < slices; ++s) {
-                        uint4* line = (uint4*)(s_v + s * SLICE + r * 128);
+                        uint4* line = (uint4*)(s_v + b * KV_STAGE + s * KSLICE + r * 128);
 #pragma unroll
                         for (int q = 0; q < 8; ++q) line[q] = make_uint4(0u, 0u, 0u, 0u);
                     }
@@ -403,11 +424,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
             tc_fence_before();
-            mbar_arrive(p_full);
+            mbar_arrive(p_full + 8 * b);
             lap(2);
         }
         // the last product; then the row's output
-        if (ok) ok = mbar_wait(pv_done, (n_blocks - 1) & 1, p.status, 8);
+        if (ok) ok = mbar_wait(pv_done + 8 * ((n_blocks - 1) & 1), ((n_blocks - 1) >> 1) & 1, p.status, 8);
         tc_fence_after();
         lap(4);
         if (ok) {
@@ -416,8 +437,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll 1
             for (int c = 0; c < 4; ++c) {
                 if (c * 32 < p.hd) {                                   // uniform: the load is warp-wide
-                    uint32_t raw[32];
-                    tc_ld32(tmem_o + lane_addr + c * 32, raw);
+                    uint32_t o32[32];
+                    tc_ld32(tmem_o + lane_addr + c * 32, o32);
                     tc_ld_wait();
                     if (valid) {
 #pragma unroll
@@ -425,7 +446,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                             if (c * 32 + q * 8 < p.hd) {
                                 float x[8];
 #pragma unroll
-                                for (int j = 0; j < 8; ++j) x[j] = __uint_as_float(raw[q * 8 + j]) * inv;
+                                for (int j = 0; j < 8; ++j) x[j] = __uint_as_float(o32[q * 8 + j]) * inv;
                                 *(uint4*)(dst + c * 32 + q * 8) =
                                     make_uint4(pack2(x[0], x[1]), pack2(x[2], x[3]), pack2(x[4], x[5]), pack2(x[6], x[7]));
                             }

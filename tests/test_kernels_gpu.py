@@ -405,7 +405,8 @@ def test_gemm_tensor_core_gated_epilogue(m, inner, k):
     be.check_status()
 
 
-@pytest.mark.parametrize("m,n,k", [(2048, 3584, 512), (1100, 3584 + 256, 1024), (2048 + 77, 2400, 320), (2048, 3584, 18944)])
+@pytest.mark.parametrize("m,n,k", [(2048, 3584, 512), (1100, 3584 + 256, 1024), (2048 + 77, 2400, 320), (2048, 3584, 18944),
+                                   (4096, 3584, 1024), (19 * 128, 2048, 4096)])
 def test_gemm_tensor_core_partial_last_wave(m, n, k, monkeypatch):
     """More 128 x 256 tiles than SMs with a remainder: with FRIDAY_STREAM_K=1 the last wave is cut along k over
     all SMs.  The switch is read once per process, so this test runs the product in a child process."""
@@ -427,6 +428,13 @@ def partial_last_wave(m, n, k):
     ref = (a.float() @ w.float().t()).double() + res.double()          # fp32 matmul of exact bf16 inputs as the yardstick
     err = float((io.double() - ref).abs().max() / ref.abs().max())
     assert err <= 0.01, err
+    # the same product with a bias, beginning a norm: the tile's last CTA has whole rows of the tile
+    b, g = rnd((n,), dt, 47), rnd((n,), dt, 48) + 1.0
+    out, h = ops.linear_norm(a, w, g, 1e-6, bias=b, residual=res)
+    assert isinstance(h, ops.DeferredNorm)
+    close(out, f64(a) @ f64(w).T + f64(b) + f64(res), dt, "product")
+    close(h.ssq.sum(0), (f64(out) ** 2).sum(-1), torch.float32, "sums of squares", fp32_tol=1e-5)
+    close(h.scaled, f64(out) * f64(g), dt, "rows times the norm's weights")
     ops.backend().check_status()
 
 
