@@ -149,6 +149,43 @@ __device__ __forceinline__ void mark(const GemmParams& p, int point) {
     if (p.f.trace != nullptr) p.f.trace[(size_t)blockIdx.x * 16 + point] = global_ns();
 }
 
+// Rows on the M side, the RMSNorm of the output begun: 16 whole columns gj0.. of row gi (the launcher has seen to
+// n % 16 == 0 and 16-byte aligned rows): bias, residual, rounding, store; then the rounded values' squares into ss and,
+// times the norm's weights g16[0..15], into norm_out.  pre_added: bias and residual are in v already.
+__device__ __forceinline__ void finish16_begin_norm(const GemmParams& p, const float* g16, int gi, int gj0, float (&v)[16],
+                                                    float& ss, bool pre_added = false) {
+    if (gi >= p.p_rows || gj0 >= p.q_rows) return;
+    const size_t base = (size_t)gi * p.ldo + gj0;
+    if (p.bias != nullptr && !pre_added)
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] += bias_at(p, gj0 + j);
+    if (p.residual != nullptr && !pre_added) {
+        const uint4* rp = (const uint4*)((const __nv_bfloat16*)p.residual + base);
+        const uint4 r0 = rp[0], r1 = rp[1];
+        const uint32_t rw[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            v[2 * j] += __uint_as_float(rw[j] << 16);
+            v[2 * j + 1] += __uint_as_float(rw[j] & 0xffff0000u);
+        }
+    }
+    uint32_t w[8], h[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        w[j] = pack2(v[2 * j], v[2 * j + 1]);
+        const float x0 = __uint_as_float(w[j] << 16), x1 = __uint_as_float(w[j] & 0xffff0000u);
+        ss += x0 * x0;
+        ss += x1 * x1;
+        h[j] = pack2(x0 * g16[2 * j], x1 * g16[2 * j + 1]);
+    }
+    uint4* o = (uint4*)((__nv_bfloat16*)p.out + base);
+    o[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    o[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    uint4* ho = (uint4*)((__nv_bfloat16*)p.f.norm_out + base);
+    ho[0] = make_uint4(h[0], h[1], h[2], h[3]);
+    ho[1] = make_uint4(h[4], h[5], h[6], h[7]);
+}
+
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
@@ -498,40 +535,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 for (int j = 0; j < 16; ++j) v[j] *= r;
             }
         };
-        // Rows-on-M orientation with the RMSNorm of the output begun: 16 whole columns of row gi (the launcher has seen
-        // to n % 16 == 0 and 16-byte aligned rows): bias, residual, rounding, store; then the rounded values' squares
-        // into ss and, times the norm's weights, into norm_out.
         auto finish16_norm = [&](int q_blk, int gi, int gj0, float (&v)[16], float& ss) {
-            if (gi >= p.p_rows || gj0 >= p.q_rows) return;
-            const size_t base = (size_t)gi * p.ldo + gj0;
-            if (p.bias != nullptr)
-#pragma unroll
-                for (int j = 0; j < 16; ++j) v[j] += bias_at(p, gj0 + j);
-            if (p.residual != nullptr) {
-                const uint4* rp = (const uint4*)((const __nv_bfloat16*)p.residual + base);
-                const uint4 r0 = rp[0], r1 = rp[1];
-                const uint32_t rw[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    v[2 * j] += __uint_as_float(rw[j] << 16);
-                    v[2 * j + 1] += __uint_as_float(rw[j] & 0xffff0000u);
-                }
-            }
-            uint32_t w[8], h[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                w[j] = pack2(v[2 * j], v[2 * j + 1]);
-                const float x0 = __uint_as_float(w[j] << 16), x1 = __uint_as_float(w[j] & 0xffff0000u);
-                ss += x0 * x0;
-                ss += x1 * x1;
-                h[j] = pack2(x0 * s_gw[gj0 - q_blk * bn + 2 * j], x1 * s_gw[gj0 - q_blk * bn + 2 * j + 1]);
-            }
-            uint4* o = (uint4*)((__nv_bfloat16*)p.out + base);
-            o[0] = make_uint4(w[0], w[1], w[2], w[3]);
-            o[1] = make_uint4(w[4], w[5], w[6], w[7]);
-            uint4* ho = (uint4*)((__nv_bfloat16*)f.norm_out + base);
-            ho[0] = make_uint4(h[0], h[1], h[2], h[3]);
-            ho[1] = make_uint4(h[4], h[5], h[6], h[7]);
+            finish16_begin_norm(p, s_gw + (gj0 - q_blk * bn), gi, gj0, v, ss);
         };
         const bool norm_rows = f.norm_out != nullptr && !p.swapped;
         // Rows of a staged tile are finished 16 at a time (a chunk of the accumulator's columns): chunks c_begin,
@@ -715,6 +720,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     }
 }
 
+}  // namespace
+
+#include "gemm_tc_pair.cuh"
+
+namespace {
+
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -758,6 +769,19 @@ bool use_stream_k() {
     }
     return v != 0;
 }
+
+// FRIDAY_GEMM_PAIR=0: products of many rows run on single SMs (128 x bn tiles) instead of pairs (256 x bn).
+bool use_pair() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("FRIDAY_GEMM_PAIR");
+        v = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return v != 0;
+}
+
+// Rows on the M side, more than one tile of 128 of them, wide outputs: pairs of SMs share 256 x bn tiles.
+bool pair_shape(int m, int n, int swap, int sm_count) { return !swap && m > TILE_P && n >= 256 && sm_count >= 2 && use_pair(); }
 
 // FRIDAY_GEMM_SHARED_FINISH=0: the last CTA of a tile to arrive always finishes the whole tile (for comparison).
 bool use_shared_finish() {
@@ -811,11 +835,14 @@ FR_EXPORT int gemm_tc_plan(int m, int n, int k, int sm_count, int swap, int bn, 
             // Many rows: 128 x bn tiles, bn a multiple of 16 from 128 to 256, chosen so that the tiles fill whole
             // waves of the SMs.  A tile costs about bn + 16 (its products, and an epilogue that is mostly hidden);
             // 2048 x 3584: 14 column tiles of 256 are 224 tiles, two waves at 76 %; 18 of 208 are 288, two at 97 %.
-            const long long tiles_p = (p_rows + TILE_P - 1) / TILE_P;
+            // On pairs of SMs the tiles are 256 rows high and there are half as many units to fill.
+            const bool pair = pair_shape(m, n, swap, sm_count);
+            const long long tiles_p = pair ? (p_rows + 2 * TILE_P - 1) / (2 * TILE_P) : (p_rows + TILE_P - 1) / TILE_P;
+            const long long units = pair ? sm_count / 2 : sm_count;
             long long best = -1;
             for (int cand = 256; cand >= 128; cand -= 16) {
                 const long long tiles = tiles_p * ((q_rows + cand - 1) / cand);
-                const long long cost = ((tiles + sm_count - 1) / sm_count) * (cand + 16);
+                const long long cost = ((tiles + units - 1) / units) * (cand + 16);
                 if (best < 0 || cost < best) { best = cost; bn = cand; }
             }
         } else if (!skinny) bn = q_rows > 64 ? 128 : 64;
@@ -945,6 +972,26 @@ FR_EXPORT int gemm_tc_fused(const void* x, const void* w, void* out, int out_dty
             p.sk_units = (rem * p.kb_total + sm_count - 1) / sm_count;
             grid = sm_count;
         }
+    }
+    if (pair_shape(m, n, swap, sm_count) && splits == 1 && bn >= 128 && p.sk_tiles == 0) {
+        // 256 x bn tiles on pairs of SMs; each CTA loads half of a tile's weight rows
+        p.tiles_p = (m + 2 * TILE_P - 1) / (2 * TILE_P);
+        const int pair_tiles = p.tiles_p * p.tiles_q;
+        p.dp_tiles = pair_tiles;
+        CUtensorMap mp, mq;
+        int rc = make_map(&mp, x, m, k, lda, TILE_P);
+        if (rc) return rc;
+        rc = make_map(&mq, w, n, k, ldw, bn / 2);
+        if (rc) return rc;
+        static bool configured = false;
+        if (!configured) {
+            FR_CUDA(cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES));
+            configured = true;
+        }
+        const int pairs = pair_tiles < sm_count / 2 ? pair_tiles : sm_count / 2;
+        FR_CUDA(fr_launch_cluster(gemm_tc_pair_kernel, dim3(2 * pairs), dim3(THREADS), PAIR_SMEM_BYTES, stream, 2u, mp, mq, p));
+        FR_CHECK_LAUNCH("gemm_tc (pairs)");
+        return FR_OK;
     }
     p.shared_finish = swap && splits > 1 && bn >= 32 && bn <= 64 && !act && grid == tiles * splits && grid <= sm_count &&
                       2 * tiles <= n_counters && use_shared_finish();
