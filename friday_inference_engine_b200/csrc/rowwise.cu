@@ -241,7 +241,40 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
     const int h0 = blockIdx.y * per, h1 = min(h0 + per, heads);
     // q and k heads: rotate the pairs (i, i + rot/2) in place; k also goes to the cache.
     const int rot_heads = max(0, min(h1, nq + nkv) - h0);
-    if (denom != nullptr) {
+    bool by_eights = false;
+    if constexpr (sizeof(T) == 2) {
+        // bf16 with 16-byte aligned heads: eight pairs per thread, as two 16-byte pieces in and two (or four) out
+        by_eights = denom != nullptr && half % 8 == 0 && hd % 8 == 0 && (((uintptr_t)base) & 15) == 0 &&
+                    (!write || (((uintptr_t)k_dst) & 15) == 0);
+        if (by_eights) {
+            const int pieces = half / 8;
+            for (int idx = threadIdx.x; idx < rot_heads * pieces; idx += blockDim.x) {
+                const int h = h0 + idx / pieces, i = (idx % pieces) * 8;
+                T* v = base + (size_t)h * hd;
+                uint4 lo = *(const uint4*)(v + i), hi = *(const uint4*)(v + i + half);
+                uint32_t* lw = (uint32_t*)&lo;
+                uint32_t* hw = (uint32_t*)&hi;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float ra0, rb0, ra1, rb1;
+                    fr_rotate(__uint_as_float(lw[j] << 16), __uint_as_float(hw[j] << 16), cos_sin[2 * (i + 2 * j)],
+                              cos_sin[2 * (i + 2 * j) + 1], ra0, rb0);
+                    fr_rotate(__uint_as_float(lw[j] & 0xffff0000u), __uint_as_float(hw[j] & 0xffff0000u),
+                              cos_sin[2 * (i + 2 * j + 1)], cos_sin[2 * (i + 2 * j + 1) + 1], ra1, rb1);
+                    const __nv_bfloat162 a2 = __floats2bfloat162_rn(ra0, ra1), b2 = __floats2bfloat162_rn(rb0, rb1);
+                    lw[j] = *(const uint32_t*)&a2;
+                    hw[j] = *(const uint32_t*)&b2;
+                }
+                *(uint4*)(v + i) = lo;
+                *(uint4*)(v + i + half) = hi;
+                if (write && h >= nq) {
+                    *(uint4*)(k_dst + (size_t)(h - nq) * hd + i) = lo;
+                    *(uint4*)(k_dst + (size_t)(h - nq) * hd + i + half) = hi;
+                }
+            }
+        }
+    }
+    if (denom != nullptr && !by_eights) {
         for (int idx = threadIdx.x; idx < rot_heads * half; idx += blockDim.x) {
             const int h = h0 + idx / half, i = idx % half;
             const float c = cos_sin[2 * i], s = cos_sin[2 * i + 1];
