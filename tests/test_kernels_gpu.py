@@ -236,6 +236,9 @@ TC_SHAPES = [
     (1, 128, 64), (1, 4608, 3584), (8, 3584, 3584), (7, 1001, 328), (16, 777, 96), (17, 256, 512), (33, 200, 1024),
     (64, 3584, 18944), (64, 130, 72), (65, 96, 768), (130, 96, 768), (200, 1001, 328), (257, 300, 64),
     (512, 4608, 3584), (2048, 512, 1024),
+    # more than 128 rows and at least 256 columns: 256-row tiles on pairs of SMs; a last row tile whose second half is
+    # empty, widths that are no multiple of the tile width, of 16 or of 8, more tiles than pairs
+    (129, 256, 64), (256, 1000, 136), (300, 1001, 328), (513, 4104, 72), (1300, 2400, 4096), (2500, 9000, 128),
 ]
 
 
@@ -354,7 +357,7 @@ def test_attention_mma_prompts_of_unequal_lengths(nq, nkv, hd, window):
     (5, 5, 80, None), (9, 3, 96, 100), (32, 1, 64, None), (40, 8, 128, 300), (128, 1, 16, None), (3, 3, 128, 128)])
 def test_attention_tcgen05_prompts_of_unequal_lengths(nq, nkv, hd, window):
     """The kernel for prompts with both products on tcgen05: the same cases as the mma.sync kernel (stale pages
-    hold NaN), lengths around its 128-key blocks, 128 heads on one kv head (one token per tile), and a window
+    hold NaN), lengths around its 64-key blocks and twice that, 128 heads on one kv head (one token per tile), and a window
     that is exactly one block."""
     mma_case([(0, 37), (0, 130), (70, 65), (0, 1), (63, 2), (0, 64)], nq, nkv, hd, window, False, 1, tcgen05=True)
     mma_case([(0, 128), (0, 129), (127, 2), (255, 258), (0, 700)], nq, nkv, hd, window, False, 1, seed=77, tcgen05=True)
