@@ -4,7 +4,7 @@ device memory unless they ask for it.
 
 Where the reference has an option, its name and meaning are kept: `model_path`,
 `max_ctx` (tokens one sequence can hold, default 2048: engine.h:22).  Its options for
-CPU offload, VRAM budget and quantized KV (`vram_gb`, `cpu_threads`, `backend`,
+CPU offload, a VRAM limit and quantized KV (`vram_gb`, `cpu_threads`, `backend`,
 `kv_cache`) have nothing to act on here and are not offered.  New ones: `dtype`,
 `max_batch` (sequences alive at once), `max_tokens` (cache capacity), and a
 random-weights mode from a configuration and a seed.

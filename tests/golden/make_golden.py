@@ -149,5 +149,7 @@ def main(reference_dir, build_dir):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference",
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py REFERENCE_SOURCE_TREE [BUILD_DIR]")
+    main(sys.argv[1],
          sys.argv[2] if len(sys.argv) > 2 else os.path.join(os.path.dirname(os.path.dirname(HERE)), "baseline", "_ref", "build"))
