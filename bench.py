@@ -284,7 +284,7 @@ def cta_trace(eng, batch):
         eng.free_slot(s)
 
     # the prompt attention of the last layer: where the thread of a CTA's first row and the thread that issues the
-    # products spend the time of a block of 128 keys
+    # products spend the time of a block of 64 keys
     (p,) = random_prompts(1, PREFILL_TOKENS, eng.vocab_size, 99)
     for _ in range(2):
         s = eng.alloc_slot()

@@ -65,7 +65,7 @@ struct TcArgs {
     const int* seq_pos0;      // position of its first row
     const int* seq_live;      // may be null; < 0 at seq_start[s]: the sequence has ended
     int* status;
-    int table_width, nq, nkv, hd, window, pool_rows;
+    int table_width, nq, nkv, hd, window, pool_rows, n_seqs;
     float scale_log2;         // softmax scale times log2(e)
     unsigned long long* trace;   // for measurements (may be null): [cta][8] sums of time (ns) that row 0's thread spent
                                  // waiting for S, reading it, writing P, rescaling O, waiting for the last product;
@@ -169,7 +169,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
     // The CTA's rows and its range of key blocks.  The step's geometry is final before the step's first kernel
     // starts (common.cuh), so it is read ahead of the wait.
-    const int seq = blockIdx.z, kvh = blockIdx.y, tile = gridDim.x - 1 - blockIdx.x;     // long tiles first
+    // The grid is one line of CTAs, long tiles (late tokens) first over all sequences and kv heads: CTAs start in the
+    // order of their index, and the longest tile bounds the launch (one prompt of 2,048 tokens: 71 us with the kv
+    // heads as a grid dimension of their own, whose last head's long tiles started after the first heads' short
+    // ones; 53 us in this order).  x = (tile rank * kv heads + kv head) * sequences + sequence.
+    const int seq = blockIdx.x % p.n_seqs;
+    const int kvh = (blockIdx.x / p.n_seqs) % p.nkv;
+    const int n_tiles = gridDim.x / (p.n_seqs * p.nkv);
+    const int tile = n_tiles - 1 - blockIdx.x / (p.n_seqs * p.nkv);
     const int G = p.nq / p.nkv, T = ROWS / G;         // T tokens of G heads each fill the tile's rows
     const int q_len = p.seq_qlen[seq], q_start = p.seq_start[seq], pos0 = p.seq_pos0[seq];
     const int t0 = tile * T;
@@ -303,7 +310,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 if (i + 2 < n_blocks) ok = scores(i + 2);
             }
             if (p.trace != nullptr) {
-                unsigned long long* at = p.trace + ((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 + 8;
+                unsigned long long* at = p.trace + (size_t)blockIdx.x * 16 + 8;
                 for (int k = 0; k < 5; ++k) at[k] = m_spent[k];
             }
         }
@@ -456,7 +463,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             }
         }
         if (tracing) {
-            unsigned long long* at = p.trace + ((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16;
+            unsigned long long* at = p.trace + (size_t)blockIdx.x * 16;
             for (int k = 0; k < 5; ++k) at[k] = spent[k];
             at[5] = (unsigned long long)n_blocks;
             at[6] = global_ns() - t_begin;
@@ -532,7 +539,6 @@ FR_EXPORT int attention_tc(const void* q, int q_stride, int total_rows, void* ou
     if (((uintptr_t)q & 15) || ((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15) || ((uintptr_t)out & 15))
         FR_REFUSE("attention_tc: buffers must be 16-byte aligned");
     if (status == nullptr) FR_REFUSE("attention_tc: a status word is needed");
-    if (n_seqs > 65535 || nkv > 65535) FR_REFUSE("attention_tc: %d sequences x %d kv heads exceed the grid", n_seqs, nkv);
     const int G = nq / nkv, T = ROWS / G;
     CUtensorMap mq, mk, mv;
     {
@@ -561,7 +567,10 @@ FR_EXPORT int attention_tc(const void* q, int q_stride, int total_rows, void* ou
         FR_CUDA(cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         configured = true;
     }
-    const dim3 grid((max_q_len + T - 1) / T, nkv, n_seqs);
+    const long long tiles = (long long)((max_q_len + T - 1) / T) * nkv * n_seqs;
+    if (tiles > 0x7fffffffLL) FR_REFUSE("attention_tc: %lld tiles exceed the grid", tiles);
+    p.n_seqs = n_seqs;
+    const dim3 grid((unsigned)tiles);
     FR_CUDA(fr_launch(attention_tc_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, mq, mk, mv, p));
     FR_CHECK_LAUNCH("attention_tc");
     return FR_OK;
