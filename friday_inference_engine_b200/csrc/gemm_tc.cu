@@ -21,7 +21,9 @@
 // one that feeds its N side ("Q", tiles of BN rows) are chosen by the launcher:
 //   many rows (prompts):   P = x, Q = w, BN = 128 ... 256 in steps of 16 (the widest
 //                          kernel instance takes the width as a number), chosen so that
-//                          the tiles fill whole waves of the SMs;
+//                          the tiles fill whole waves; with more than 128 rows and at
+//                          least 256 columns the tiles are 256 rows high and run on
+//                          pairs of SMs (gemm_tc_pair.cuh, cta_group::2);
 //   few rows (decoding):   P = w, Q = x, BN = 16/32/64 >= rows (up to 64 rows): every
 //                          weight is streamed once at full width, the handful of
 //                          activations ride along, and the epilogue writes the tile
@@ -824,7 +826,7 @@ FR_EXPORT int gemm_tc_plan(int m, int n, int k, int sm_count, int swap, int bn, 
     //    way round; at 32 rows 13 / 12 / 31 against 21 / 20 / 39);
     //  * 65 to 128 rows: rows on the M side (one tile, partly empty) and narrow weight tiles, so that about a
     //    hundred CTAs stream weights without splitting k; very long k is split four ways over wide tiles instead;
-    //  * more rows: 128 x 256 tiles.
+    //  * more rows: 128 x bn tiles, or 256 x bn tiles on pairs of SMs (wide outputs).
     const int kb_total = (k + TILE_K - 1) / TILE_K;
     if (swap < 0) swap = m <= 64 ? 1 : 0;
     const int q_rows = swap ? m : n, p_rows = swap ? n : m;
