@@ -29,7 +29,14 @@ def _ptr(t):
     return 0 if t is None else t.data_ptr()
 
 
+_raw_current_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream():
+    """The current stream's handle.  A prompt's pass launches some 170 kernels from Python: the direct query costs a
+    fraction of a microsecond where building a torch.cuda.Stream object each time cost half of the pass's host time."""
+    if _raw_current_stream is not None:
+        return _raw_current_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -78,6 +85,7 @@ class CudaOps:
     def __init__(self):
         self._tc = {}
         self._attn_counters = {}
+        self._plans = {}
         self._cluster_fit = {}
 
     # -- row-wise ---------------------------------------------------------
@@ -174,6 +182,18 @@ class CudaOps:
         fusion.in_width, fusion.in_eps = float(deferred.scaled.shape[1]), deferred.eps
         return fusion
 
+    def _plan(self, rows, n, k, device):
+        """(operands swapped, tile width) that the tensor-core product will choose for a shape."""
+        key = (rows, n, k, device)
+        hit = self._plans.get(key)
+        if hit is None:
+            plan = np.zeros((8,), dtype=np.int64)
+            lib.family("gemm_tc").call("gemm_tc_plan", rows, n, k, self._tc_buffers(device)[3], -1, -1, -1, plan.ctypes.data)
+            if len(self._plans) > 4096:
+                self._plans.clear()
+            hit = self._plans[key] = (bool(plan[0]), int(plan[1]))
+        return hit
+
     def _few_rows_tile_ok(self, x, weight, out, residual, max_rows, columns=128):
         """What the fused epilogues of the tensor-core product need: no more rows than max_rows, bf16, whole
         groups of `columns` output columns (128: the tiles of a one-token step's few rows)."""
@@ -207,12 +227,10 @@ class CudaOps:
                 # many rows: the rows lie on the tiles' M side and every column tile adds one partial sum per row
                 if residual is not None:
                     assert residual.shape == out.shape and residual.dtype == out.dtype and residual.stride() == out.stride()
-                plan = np.zeros((8,), dtype=np.int64)
-                lib.family("gemm_tc").call("gemm_tc_plan", rows, n, xt.shape[1], self._tc_buffers(xt.device)[3], -1, -1,
-                                           -1, plan.ctypes.data)
-                if plan[0] == 0:
+                swapped, bn = self._plan(rows, n, xt.shape[1], xt.device)
+                if not swapped:
                     scaled = torch.empty_like(out)
-                    ssq = torch.empty((-(-n // int(plan[1])), rows), dtype=torch.float32, device=out.device)
+                    ssq = torch.empty((-(-n // bn), rows), dtype=torch.float32, device=out.device)
                     fusion = self._fusion_in(deferred, lib.GemmFusion())
                     fusion.norm_w, fusion.norm_w_dtype = _ptr(norm_weight), code_of(norm_weight.dtype)
                     fusion.norm_out, fusion.out_ssq = _ptr(scaled), _ptr(ssq)
