@@ -25,6 +25,43 @@ WIDE = {
 }
 
 
+# The layer sizes of the two larger models of the family (14B: 40 heads in 8 groups, width 5120, inner width 13824;
+# 32B: the same heads and width, inner width 27648), one layer each, their norms' eps.
+WIDER = dict(WIDE, num_hidden_layers=1, hidden_size=5120, num_attention_heads=40, num_key_value_heads=8,
+             intermediate_size=27648, rms_norm_eps=1e-5, vocab_size=3000)
+WIDER_14B = dict(WIDER, intermediate_size=13824)
+
+
+@pytest.mark.parametrize("config", [WIDER, WIDER_14B], ids=["32b_layer", "14b_layer"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layer_sizes_of_the_larger_models(config, dtype, tmp_path):
+    """A prompt pass of unequal prompts and a one-token step at these sizes against the plain implementation."""
+    d = str(tmp_path / "model")
+    tiny_configs.make_model_dir(d, config, 11)
+    harness.sharpen(d, 2.0)
+    pm = plain_model.PlainModel.from_dir(d)
+    eng = Engine(model_path=d, dtype=dtype, max_ctx=512, max_batch=2)
+    lens = [150, 33]
+    prompts = tiny_configs.random_prompts([n + 1 for n in lens], config["vocab_size"], 62)
+    refs = [plain_model.logits(pm, p, at=[n - 1, n]) for p, n in zip(prompts, lens)]
+    slots = [eng.alloc_slot() for _ in prompts]
+
+    def check(got_rows, ref_rows, what):
+        if dtype == "float32":
+            err = float(np.abs(got_rows - ref_rows).max())
+            assert err <= WIDE_FP32_ABS, "%s: |engine - plain| = %.3g > %.3g" % (what, err, WIDE_FP32_ABS)
+        else:
+            harness.check_logits(got_rows, ref_rows, dtype, what)
+
+    got = eng.step(slots, [p[:n] for p, n in zip(prompts, lens)], [[n - 1] for n in lens])
+    for i in range(2):
+        check(harness.to_np(got[i:i + 1]), refs[i][0:1], "prompt %d" % i)
+    got = eng.step(slots, [[p[n]] for p, n in zip(prompts, lens)], [[0]] * 2)
+    for i in range(2):
+        check(harness.to_np(got[i:i + 1]), refs[i][1:2], "first token after prompt %d" % i)
+    eng.check()
+
+
 @pytest.fixture(scope="module")
 def wide(tmp_path_factory):
     d = str(tmp_path_factory.mktemp("wide") / "model")
