@@ -859,6 +859,18 @@ FR_EXPORT int gemm_tc_plan(int m, int n, int k, int sm_count, int swap, int bn, 
             if (splits > kb_total / 4) splits = kb_total / 4;      // at least four k-slices per split
             if (skinny && splits > 4) splits = 4;                  // wide partial tiles are costly to merge
             if (splits < 1) splits = 1;
+        } else if (swap && bn <= 16 && tiles > sm_count) {
+            // More tiles than SMs and a last wave that is partly empty (216 tiles on 148 SMs: the second wave costs as
+            // much as the first for half the work): cutting k in two to four makes the waves shorter.  An item costs its
+            // k blocks and about six more (filling the ring, partial tile, counter); the few rows of such a step keep
+            // the sum of a tile's partial tiles cheap.
+            const long long fixed = 6;
+            long long best = (long long)((tiles + sm_count - 1) / sm_count) * (kb_total + fixed);
+            for (int s = 2; s <= 4; ++s) {
+                if (kb_total / s < 8) break;
+                const long long cost = (long long)((tiles * s + sm_count - 1) / sm_count) * ((kb_total + s - 1) / s + fixed);
+                if (cost * 20 < best * 19) { best = cost; splits = s; }
+            }
         }
     }
     if (splits > kb_total) splits = kb_total;

@@ -236,6 +236,8 @@ TC_SHAPES = [
     (1, 128, 64), (1, 4608, 3584), (8, 3584, 3584), (7, 1001, 328), (16, 777, 96), (17, 256, 512), (33, 200, 1024),
     (64, 3584, 18944), (64, 130, 72), (65, 96, 768), (130, 96, 768), (200, 1001, 328), (257, 300, 64),
     (512, 4608, 3584), (2048, 512, 1024),
+    # few rows, more tiles of weights than SMs with a half-empty last wave: k is cut although every SM has a tile
+    (8, 27648, 5120), (3, 128 * 160, 1024),
     # more than 128 rows and at least 256 columns: 256-row tiles on pairs of SMs; a last row tile whose second half is
     # empty, widths that are no multiple of the tile width, of 16 or of 8, more tiles than pairs
     (129, 256, 64), (256, 1000, 136), (300, 1001, 328), (513, 4104, 72), (1300, 2400, 4096), (2500, 9000, 128),
@@ -389,7 +391,7 @@ def test_attention_mma_dead_rows_give_zero():
     assert float(out.float().abs().max()) == 0.0
 
 
-@pytest.mark.parametrize("m,inner,k", [(1, 64, 64), (8, 18944, 3584), (40, 177, 512), (64, 200, 96), (100, 177, 512),
+@pytest.mark.parametrize("m,inner,k", [(1, 64, 64), (8, 18944, 3584), (8, 13824, 5120), (40, 177, 512), (64, 200, 96), (100, 177, 512),
                                        (300, 1000, 1024), (2048, 2368, 512)])
 def test_gemm_tensor_core_gated_epilogue(m, inner, k):
     dt = torch.bfloat16
