@@ -210,11 +210,16 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
                                      int nq, int nkv, int hd, T* __restrict__ k_pool, T* __restrict__ v_pool,
                                      const int* __restrict__ block_table, int table_width, int page, int write) {
     extern __shared__ float cos_sin[];           // [rot/2][2], the row's angles, shared by all heads
-    fr_pdl_wait();
-    fr_pdl_launch();
+    // The row's sequence, position and page and the angles depend on the step's geometry alone, which is final
+    // before the step's first kernel starts (common.cuh): they are taken ahead of the wait for the kernel that
+    // writes qkv.
     const int row = blockIdx.x;
     const int seq = row_seq[row];
-    if (seq < 0) return;
+    if (seq < 0) {
+        fr_pdl_wait();
+        fr_pdl_launch();
+        return;
+    }
     const int pos = row_pos[row];
     T* base = qkv + (size_t)row * (nq + 2 * nkv) * hd;
     const int half = rot / 2;
@@ -235,6 +240,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
         k_dst = k_pool + cache_row;
         v_dst = v_pool + cache_row;
     }
+    fr_pdl_wait();
+    fr_pdl_launch();
     // The heads (q, then k, then v) are dealt out to the blocks of this row.
     const int heads = nq + 2 * nkv;
     const int per = (heads + gridDim.y - 1) / gridDim.y;
