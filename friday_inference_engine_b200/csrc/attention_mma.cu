@@ -150,7 +150,8 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
     const int seq = blockIdx.z, kvh = blockIdx.y;
     // The page table is written by copies from the host, never by a kernel, so it may be read before the
     // kernel before this one has finished; so may everything that is arithmetic only.  The rest waits.
-    if (tid < p.table_width) s_pages[tid] = p.block_table[(size_t)seq * p.table_width + tid];
+    // (s_pages holds the first WARPS * 32 entries; keys mode runs one warp more than that, whose threads must not store)
+    if (tid < p.table_width && tid < WARPS * 32) s_pages[tid] = p.block_table[(size_t)seq * p.table_width + tid];
     const int split = blockIdx.x % p.splits, tile = blockIdx.x / p.splits;
     const int G = p.nq / p.nkv;
     const int r0 = tile * ROWS_CTA;

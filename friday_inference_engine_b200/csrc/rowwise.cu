@@ -11,6 +11,7 @@
 // (:439-480), the embedding row (transformer.cpp:958-991).  The reference's fp16
 // clamps and NaN scrubbing are not reproduced.
 #include "common.cuh"
+#include "philox.h"
 
 FR_EXPORT const char* rowwise_last_error() { return fr_error_text; }
 
@@ -372,5 +373,74 @@ FR_EXPORT int rowwise_advance(int* tokens, const int* sampled, int* row_pos, int
     FR_CUDA(fr_launch(advance_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, tokens, sampled, row_pos, kv_len,
                       row_seq, draws, n));
     FR_CHECK_LAUNCH("advance");
+    return FR_OK;
+}
+
+// ------------------------------------------------------------------ multipliers, logit finish, random numbers
+// x *= scale, for architectures whose token rows carry a multiplier.
+template <typename T>
+__global__ void scale_rows_kernel(T* x, long long n, float scale) {
+    fr_pdl_wait();
+    fr_pdl_launch();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        fr_store(x + i, __fmul_rn(fr_load(x + i), scale));
+}
+
+FR_EXPORT int rowwise_scale_rows(void* x, long long n, float scale, int dtype, cudaStream_t stream) {
+    if (n <= 0) return FR_OK;
+    const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+    if (dtype == FR_F32)
+        FR_CUDA(fr_launch(scale_rows_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)x, n, scale));
+    else if (dtype == FR_BF16)
+        FR_CUDA(fr_launch(scale_rows_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)x, n, scale));
+    else
+        FR_REFUSE("scale_rows: unknown dtype %d", dtype);
+    FR_CHECK_LAUNCH("scale_rows");
+    return FR_OK;
+}
+
+// logits = softcap(scale * logits + bias): what a head may ask for beyond the product (a bias, a multiplier, a
+// soft cap c * tanh(x / c)); each is skipped when it is not wanted (bias null, scale 1, softcap 0).
+__global__ void finish_logits_kernel(float* logits, int vocab, int ld, FrVec bias, int has_bias, float scale, float softcap) {
+    fr_pdl_wait();
+    fr_pdl_launch();
+    float* row = logits + (size_t)blockIdx.y * ld;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < vocab; i += gridDim.x * blockDim.x) {
+        float v = __fmul_rn(row[i], scale);
+        if (has_bias) v = __fadd_rn(v, bias.at(i));
+        if (softcap > 0.f) v = __fmul_rn(softcap, tanhf(__fdiv_rn(v, softcap)));
+        row[i] = v;
+    }
+}
+
+FR_EXPORT int rowwise_finish_logits(float* logits, int rows, int vocab, int ld, const void* bias, int bias_dtype,
+                                    float scale, float softcap, cudaStream_t stream) {
+    if (rows <= 0 || vocab <= 0) return FR_OK;
+    if (rows > 65535) FR_REFUSE("finish_logits: %d rows (at most 65535)", rows);
+    const int bx = (vocab + 255) / 256 < 64 ? (vocab + 255) / 256 : 64;
+    FR_CUDA(fr_launch(finish_logits_kernel, dim3(bx, rows), dim3(256), 0, stream, logits, vocab, ld, FrVec{bias, bias_dtype},
+                      bias != nullptr ? 1 : 0, scale, softcap));
+    FR_CHECK_LAUNCH("finish_logits");
+    return FR_OK;
+}
+
+// out[i] = mean + std * N(0, 1)_(key, i), drawn in double, formed in fp32 and rounded once to the storage type.
+template <typename T>
+__global__ void random_normal_kernel(T* out, long long n, unsigned long long key, float mean, float std) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        fr_store(out + i, __fadd_rn(__fmul_rn((float)fr_normal_at(key, (uint64_t)i), std), mean));
+}
+
+FR_EXPORT int rowwise_random_normal(void* out, long long n, int dtype, unsigned long long key, float mean, float std,
+                                    cudaStream_t stream) {
+    if (n <= 0) return FR_OK;
+    const int blocks = (int)((n + 255) / 256 < 148 * 32 ? (n + 255) / 256 : 148 * 32);
+    if (dtype == FR_F32)
+        random_normal_kernel<float><<<blocks, 256, 0, stream>>>((float*)out, n, key, mean, std);
+    else if (dtype == FR_BF16)
+        random_normal_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((__nv_bfloat16*)out, n, key, mean, std);
+    else
+        FR_REFUSE("random_normal: unknown dtype %d", dtype);
+    FR_CHECK_LAUNCH("random_normal");
     return FR_OK;
 }

@@ -34,22 +34,47 @@ def check_logits(got, ref, dtype, what=""):
         assert ok, "%s: %s" % (what, text)
 
 
-def sharpen(model_dir, factor=6.0):
-    """Scales the query and key projections so that attention is peaked: with N(0, 0.02)
-    weights every softmax is nearly flat and a wrong key would hardly show."""
+def bf16_bytes_to_f32(raw):
+    return (np.frombuffer(raw, dtype="<u2").astype(np.uint32) << 16).view(np.float32)
+
+
+def f32_to_bf16_bytes(x):
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    u = (u + 0x7FFF + ((u >> 16) & 1)) >> 16                  # round to nearest, ties to even
+    return u.astype("<u2").tobytes()
+
+
+def rewrite(model_dir, change):
+    """Rewrites model.safetensors: change(name, float32 array) -> float32 array (or None to keep).  BF16 and F32
+    tensors only; other dtypes are copied as they are."""
     from friday_inference_engine_b200.weights import SafetensorsFile, write_safetensors
     path = os.path.join(model_dir, "model.safetensors")
     f = SafetensorsFile(path)
-    tensors = {}
+    tensors = []
     for n in f.names():
-        t = f.tensor(n).clone()
-        if ".q_proj." in n or ".k_proj." in n:
-            t = (t.float() * factor).to(t.dtype)
-        if ".embed_tokens." in n:
-            t = (t.float() * 10.0).to(t.dtype)
-        tensors[n] = t
+        dtype, shape = f.dtype_shape(n)
+        raw = f.raw(n)
+        if dtype in ("BF16", "F32"):
+            x = bf16_bytes_to_f32(raw) if dtype == "BF16" else np.frombuffer(raw, dtype="<f4")
+            y = change(n, x.reshape(shape).copy())
+            if y is not None:
+                y = np.asarray(y, dtype=np.float32)
+                raw = f32_to_bf16_bytes(y) if dtype == "BF16" else y.astype("<f4").tobytes()
+        tensors.append((n, dtype, shape, raw))
     f.close()
     write_safetensors(path, tensors)
+
+
+def sharpen(model_dir, factor=6.0):
+    """Scales the query and key projections so that attention is peaked: with N(0, 0.02)
+    weights every softmax is nearly flat and a wrong key would hardly show."""
+    def change(n, x):
+        if ".q_proj." in n or ".k_proj." in n:
+            return x * np.float32(factor)
+        if ".embed_tokens." in n:
+            return x * np.float32(10.0)
+        return None
+    rewrite(model_dir, change)
 
 
 _made = {}

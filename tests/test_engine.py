@@ -1,9 +1,6 @@
-"""The engine against the plain implementation, however the work is cut.
-
-Every test runs twice: on the GPU with the library's kernels (marked gpu), and, where
-there is no GPU, with the kernel layer replaced by tests/ops_double.py, which checks the
-code around the kernels (pages, step function, passes, loop) and nothing of the kernels.
-"""
+"""The engine against the plain implementation, however the work is cut: each request alone
+and whole, the last 32 tokens one by one, batches of unequal lengths one after another in
+reused slots, prompts cut into passes, mixed steps, long decoding, generation."""
 import numpy as np
 import pytest
 import torch
@@ -11,11 +8,10 @@ import torch
 import harness
 import plain_model
 import tiny_configs
-from friday_inference_engine_b200 import Engine, ops
+from friday_inference_engine_b200 import Engine
 
-BACKENDS = [pytest.param(("cuda:0", "float32"), marks=pytest.mark.gpu, id="gpu-f32"),
-            pytest.param(("cuda:0", "bfloat16"), marks=pytest.mark.gpu, id="gpu-bf16"),
-            pytest.param(("cpu", "float32"), id="double-f32")]
+pytestmark = pytest.mark.gpu
+BACKENDS = [pytest.param(("cuda:0", "float32"), id="f32"), pytest.param(("cuda:0", "bfloat16"), id="bf16")]
 
 
 @pytest.fixture(scope="module")
@@ -25,14 +21,12 @@ def root(tmp_path_factory):
 
 @pytest.fixture(params=BACKENDS)
 def where(request):
-    device, dtype = request.param
-    prev = None
-    if device == "cpu":
-        import ops_double
-        prev = ops.set_backend(ops_double.TorchOps())
-    yield device, dtype
-    if prev is not None:
-        ops.set_backend(prev)
+    return request.param
+
+
+def nothing_held(eng):
+    st = eng.stats()
+    return st["slots_held"] == 0 and all(g["pages_held"] == 0 for g in st["groups"])
 
 
 def engine(root, name, where, **kw):
@@ -96,7 +90,7 @@ def test_unequal_batches_one_after_another_reuse_slots(root, where, name):
             for i in [i for i in live if t >= extra[i]]:       # the shorter requests end earlier
                 eng.free_slot(slots[i])
                 live.remove(i)
-        assert eng.cache.slots.held_count == 0 and all(g.pages.held_count == 0 for g in eng.cache.groups)
+        assert nothing_held(eng)
 
 
 @pytest.mark.parametrize("name", ["B", "C"])
@@ -179,7 +173,7 @@ def test_stop_tokens_end_sequences_early(root, where):
             assert c.finish_reason == "stop" and c.tokens == f.tokens[:f.tokens.index(stop)]
         else:
             assert c.finish_reason == "length" and c.tokens == f.tokens
-    assert eng.cache.slots.held_count == 0
+    assert nothing_held(eng)
 
 
 def test_refusals(root, where):

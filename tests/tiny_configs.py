@@ -1,8 +1,6 @@
 """The tests' own small configurations of the architecture.  A and B differ in every
 size and option: layers, width, head counts and groups, head size, inner width (no
 power of two), vocabulary, rotary base, the norms' eps, tied or own head, window."""
-import os
-
 import torch
 
 TINY_A = {
@@ -39,15 +37,10 @@ TINY_D = {
 CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3)}
 
 
-def make_model_dir(path, cfg_dict, seed, dtype=torch.bfloat16):
-    """Writes a model folder with the package's random-weights mode."""
-    from friday_inference_engine_b200.engine.model import DecoderModel
-    from friday_inference_engine_b200.registry import read_config
-    from friday_inference_engine_b200.weights import expected_params, write_model_dir
-    arch, cfg = read_config(cfg_dict)
-    model = DecoderModel(arch.build_spec(cfg), torch.bfloat16, torch.device("cpu"))
-    write_model_dir(path, cfg.to_dict(), expected_params(model), seed, dtype=dtype)
-    return path
+def make_model_dir(path, cfg_dict, seed, dtype="BF16", shards=1):
+    """Writes a model folder with the library's random-weights mode."""
+    from friday_inference_engine_b200 import write_model_dir
+    return write_model_dir(path, cfg_dict, seed, dtype=dtype, shards=shards)
 
 
 def random_prompts(lengths, vocab, seed):
