@@ -96,7 +96,10 @@ Cache::Cache(const std::map<int, CacheRequest>& requests, int64_t max_tokens, in
     : max_seq_tokens(max_seq), max_slots(max_slots_ > 0 ? max_slots_ : std::min(pages_for(max_tokens), 4096)),
       slots(max_slots, "slot"), lens((size_t)max_slots, 0), on_device_(on_device), stream_(stream) {
     const int n_pages = pages_for(max_tokens);
-    const int width = std::max(1, std::min(n_pages, (max_seq_tokens + PAGE - 1) / PAGE));
+    // A sequence's table has a place for every page of the longest sequence.  Without a window a sequence can never
+    // hold more pages than there are, so the table need not be wider than that; with a window it holds few pages
+    // at a time but at any logical place.
+    const int seq_pages = std::max(1, (max_seq_tokens + PAGE - 1) / PAGE);
     typedef std::tuple<int, int, int> Need;
     std::vector<std::pair<Need, std::vector<int>>> by_need;          // in order of first appearance
     for (const auto& kv : requests) {
@@ -119,6 +122,7 @@ Cache::Cache(const std::map<int, CacheRequest>& requests, int64_t max_tokens, in
     }
     for (auto& p : by_need) {
         const CacheRequest req = requests.at(p.second[0]);
+        const int width = req.window > 0 ? seq_pages : std::min(n_pages, seq_pages);
         groups.emplace_back(new KVGroup(req, p.second, max_slots, n_pages, width, dtype, on_device));
         for (int e : p.second) group_of[e] = (int)groups.size() - 1;
     }

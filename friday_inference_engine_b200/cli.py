@@ -10,7 +10,12 @@ is refused: there is no CPU path); `--kv auto|bf16|f32` (`q8` is refused: no qua
 cache); `--info` (main.cpp:145-164).  `--vram` and `--threads` steer the reference's
 CPU offload, which does not exist here; they are accepted and ignored with a note.
 Added: `--batch`, `--dtype`, `--random`, `--seed`, `--prompt-ids`, `--prompt-file`,
-`--max-new-tokens`, `--temperature`, `--sample-seed`, `--stop-ids`, `--ignore-eos`.
+`--max-new-tokens`, `--temperature`, `--sample-seed`, `--stop-ids`, `--ignore-eos`, and
+`--profile`, which prints per request batch where the time went (host time per step,
+device time of products, attention and the rest between CUDA events), as the reference
+prints its per-token phases under FRIDAY_PROFILE (transformer.cpp:603-613, 1162-1183).
+
+The program is a binding: everything it runs is friday::Engine of libfriday_engine.so.
 """
 import argparse
 import json
@@ -24,6 +29,7 @@ def _ids(text):
 
 def info():
     import torch
+    from . import registered_architectures, registered_parts
     print("FRIDAY Engine (B200) capability report")
     print("  CUDA     : %s" % ("available" if torch.cuda.is_available() else "no device visible"))
     for i in range(torch.cuda.device_count()):
@@ -32,6 +38,9 @@ def info():
         print("  GPU      : %s, compute %d.%d, %d SMs, %.1f GB memory (%.1f GB free)"
               % (p.name, p.major, p.minor, p.multi_processor_count, total / 1e9, free / 1e9))
     print("  Backend  : CUDA kernels for sm_100a only; there is no CPU path")
+    print("  Models   : %s" % ", ".join(registered_architectures()))
+    print("  Parts    : %s" % "; ".join("%s: %s" % (c, ", ".join(registered_parts(c)))
+                                        for c in ("norm", "position", "mixer", "feed_forward", "block")))
     return 0
 
 
@@ -56,6 +65,8 @@ def build_parser():
     ap.add_argument("--stop-ids", default="", help='token ids that end a sequence, "151643,151645"')
     ap.add_argument("--ignore-eos", action="store_true", help="never stop on a stop id")
     ap.add_argument("--json", action="store_true", help="print results as JSON lines")
+    ap.add_argument("--profile", action="store_true",
+                    help="print where each batch's time went: host time per step; products, attention, other on the device")
     return ap
 
 
@@ -79,7 +90,7 @@ def main(argv=None):
         return 2
     from .engine import Engine
     try:
-        kw = dict(dtype=args.dtype, max_ctx=args.ctx, max_batch=args.batch)
+        kw = dict(dtype=args.dtype, max_ctx=args.ctx, max_batch=args.batch, profile=args.profile)
         if args.random:
             with open(args.random) as f:
                 eng = Engine(config=json.load(f), seed=args.seed, **kw)
@@ -98,6 +109,13 @@ def main(argv=None):
         except Exception as e:  # noqa: BLE001
             print("[Hata] %s" % e, file=sys.stderr)
             return 1
+        if args.profile:
+            pr = eng.profile()
+            total = pr["product_ms"] + pr["attention_ms"] + pr["other_ms"]
+            print("[Profile] %d step calls, host %.2f ms in all; device %.2f ms between events: products %.2f ms (%d), "
+                  "attention %.2f ms (%d), other %.2f ms (%d)"
+                  % (pr["steps"], pr["host_ms"], total, pr["product_ms"], pr["product_calls"], pr["attention_ms"],
+                     pr["attention_calls"], pr["other_ms"], pr["other_calls"]), file=sys.stderr)
         for p, g in zip(prompts, results):
             if args.json:
                 print(json.dumps({"prompt_tokens": len(p), "tokens": g.tokens, "finish_reason": g.finish_reason}))

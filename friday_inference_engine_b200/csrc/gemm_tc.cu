@@ -51,6 +51,8 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include <atomic>
+#include <mutex>
 #include "tc_common.cuh"
 
 FR_EXPORT const char* gemm_tc_last_error() { return fr_error_text; }
@@ -795,13 +797,27 @@ bool use_shared_finish() {
     return v != 0;
 }
 
+// A kernel's shared-memory limit is a property of the function on one device: it is raised once per device, the
+// devices that have it kept as bits of an atomic word (two host threads that both find the bit clear both set the
+// attribute, which is harmless; neither launches before its own call has returned).
+inline int current_device_bit(unsigned long long* bit) {
+    int device = 0;
+    FR_CUDA(cudaGetDevice(&device));
+    if (device < 0 || device >= 64) FR_REFUSE("gemm_tc: device %d is outside the table of 64", device);
+    *bit = 1ull << device;
+    return FR_OK;
+}
+
 template <int BN, int STAGES>
 int configure() {
-    static bool configured = false;
-    if (!configured) {
+    static std::atomic<unsigned long long> configured{0};
+    unsigned long long bit = 0;
+    const int rc = current_device_bit(&bit);
+    if (rc) return rc;
+    if (!(configured.load(std::memory_order_acquire) & bit)) {
         FR_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      smem_bytes<BN, STAGES>()));
-        configured = true;
+        configured.fetch_or(bit, std::memory_order_release);
     }
     return FR_OK;
 }
@@ -997,10 +1013,13 @@ FR_EXPORT int gemm_tc_fused(const void* x, const void* w, void* out, int out_dty
         if (rc) return rc;
         rc = make_map(&mq, w, n, k, ldw, bn / 2);
         if (rc) return rc;
-        static bool configured = false;
-        if (!configured) {
+        static std::atomic<unsigned long long> configured{0};
+        unsigned long long bit = 0;
+        rc = current_device_bit(&bit);
+        if (rc) return rc;
+        if (!(configured.load(std::memory_order_acquire) & bit)) {
             FR_CUDA(cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES));
-            configured = true;
+            configured.fetch_or(bit, std::memory_order_release);
         }
         const int pairs = pair_tiles < sm_count / 2 ? pair_tiles : sm_count / 2;
         FR_CUDA(fr_launch_cluster(gemm_tc_pair_kernel, dim3(2 * pairs), dim3(THREADS), PAIR_SMEM_BYTES, stream, 2u, mp, mq, p));
@@ -1038,6 +1057,7 @@ struct NoAllocDevice {
     int sm_count = 0;
 };
 NoAllocDevice noalloc_devices[64];
+std::mutex noalloc_mutex;          // the first calls of two host threads on one device must not both fill the entry
 
 template <int BN, int STAGES>
 cudaError_t allow_smem() {
@@ -1069,9 +1089,12 @@ FR_EXPORT int gemm_tc_noalloc(const void* x, const void* w, void* out, int out_d
     int device = 0;
     FR_CUDA(cudaGetDevice(&device));
     if (device < 0 || device >= 64) FR_REFUSE("gemm_tc_noalloc: device %d is outside the table of 64", device);
-    if (!noalloc_devices[device].ready) {
-        const int rc = noalloc_setup(device);
-        if (rc) return rc;
+    {
+        std::lock_guard<std::mutex> lock(noalloc_mutex);
+        if (!noalloc_devices[device].ready) {
+            const int rc = noalloc_setup(device);
+            if (rc) return rc;
+        }
     }
     const NoAllocDevice& d = noalloc_devices[device];
     if (m <= 0 || n <= 0) return FR_OK;

@@ -24,8 +24,9 @@
 //     (gemm_tc_last_error()); nothing is launched.  Products with few rows (decoding,
 //     up to 64 rows) always fit; wide prompts that would split k may not.
 //   * The first call on a device looks the array's address up (cudaGetSymbolAddress, with
-//     that device current) and sets the kernels' shared-memory limit.  That first call
-//     should come before any stream capture.
+//     that device current) and sets the kernels' shared-memory limit, under a lock, so
+//     host threads may make their first calls at the same time.  That first call should
+//     come before any stream capture.
 //   * All calls on a device share the one array, and it keeps what the last call left.
 //     The call clears the counters itself; partial tiles are always written before they
 //     are read.  Two calls that overlap on the GPU (different streams) race on the array:

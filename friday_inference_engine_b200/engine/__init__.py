@@ -224,6 +224,14 @@ class Engine:
             raise failure[0]
         return [Generation(list(g["tokens"]), g["finish_reason"]) for g in out]
 
+    def set_trace(self, tensor):
+        """For measurements: the next tensor.shape[0] tensor-core products fill tensor[launch] ([sm_count, 16] int64)
+        with their CTAs' time stamps; None switches it off."""
+        if tensor is None:
+            native.call("friday_engine_set_trace", self._h, None, 0)
+        else:
+            native.call("friday_engine_set_trace", self._h, c_void_p(tensor.data_ptr()), int(tensor.shape[0]))
+
     def check(self):
         """Raises KernelError if a kernel reported that it gave up on a wait (its results would be invalid)."""
         native.call("friday_engine_check", self._h)
@@ -242,3 +250,59 @@ class Engine:
                     float(temperature), int(seed), None if streams is None else native.ints(streams),
                     None if steps_done is None else native.ints(steps_done), byref(h))
         return Decoder(self, h, len(slots))
+
+
+def generate_loop(prompts, *, step, sample, alloc_slot, free_slot, max_batch, max_context, vocab_size,
+                  max_new_tokens=100, stop_token_ids=(), ignore_eos=False):
+    """The library's generation loop alone (engine/generate.cpp), with the step function, the sampler and the slot
+    book-keeping handed in as Python callables, so that its decisions can be tested without a model:
+    step(slots, tokens, want); sample(streams, steps) -> ids; alloc_slot() -> slot; free_slot(slot).
+    An exception raised by a callable ends the loop (slots are given back first) and is raised again here."""
+    failure = []
+
+    def guarded(fn):
+        def run(*args):
+            try:
+                return fn(*args)
+            except Exception as e:  # noqa: BLE001 - raised again once the library has returned
+                failure.append(e)
+                return 1
+        return run
+
+    @guarded
+    def c_step(_user, n, slots, t_off, t_val, w_off, w_val):
+        step([slots[i] for i in range(n)], [[t_val[j] for j in range(t_off[i], t_off[i + 1])] for i in range(n)],
+             [[w_val[j] for j in range(w_off[i], w_off[i + 1])] for i in range(n)])
+        return 0
+
+    @guarded
+    def c_sample(_user, n, streams, steps, out):
+        ids = sample([streams[i] for i in range(n)], [steps[i] for i in range(n)])
+        for i in range(n):
+            out[i] = int(ids[i])
+        return 0
+
+    @guarded
+    def c_alloc(_user, out):
+        out[0] = int(alloc_slot())
+        return 0
+
+    @guarded
+    def c_free(_user, slot):
+        free_slot(slot)
+        return 0
+
+    hooks = native.LoopHooks(None, native.STEP_HOOK(c_step), native.SAMPLE_HOOK(c_sample), native.ALLOC_HOOK(c_alloc),
+                             native.FREE_HOOK(c_free))
+    prompts = [[int(t) for t in p] for p in prompts]
+    off, val = native.ragged(prompts)
+    opts = {"max_new_tokens": int(max_new_tokens), "stop_token_ids": [int(t) for t in stop_token_ids],
+            "ignore_eos": bool(ignore_eos)}
+    try:
+        out = native.call_json("friday_generate_loop", len(prompts), off, val, byref(hooks), int(max_batch),
+                               int(max_context), int(vocab_size), native.text(json.dumps(opts)))
+    except native.FridayError:
+        if failure:
+            raise failure[0] from None
+        raise
+    return [Generation(list(g["tokens"]), g["finish_reason"]) for g in out]

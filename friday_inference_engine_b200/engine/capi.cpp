@@ -282,6 +282,24 @@ FR_API int friday_check_weights(const char* model_dir) {
     })
 }
 
+FR_API int friday_storage_plan(const char* model_dir, const char* dtype, const char** json) {
+    GUARD({
+        const Json cfg = read_config_file(model_dir);
+        const Architecture& arch = architecture(architecture_name_of(cfg));
+        DecoderModel model(arch.build_spec(arch.read_config(cfg)), parse_dtype(dtype));
+        std::unique_ptr<WeightSource> src = open_model_weights(model_dir);
+        Json out = Json::array();
+        for (const auto& s : model.plan_storage(*src)) {
+            Json e = Json::object();
+            e.set("name", Json(s.param.name));
+            e.set("dtype", Json(dtype_name(s.dtype)));
+            e.set("into", Json(s.param.decl.into));
+            out.push(e);
+        }
+        *json = hand_back(out.dump());
+    })
+}
+
 FR_API int friday_random_tensor(uint64_t seed, const char* name, int one, int64_t count, float* out) {
     GUARD(random_tensor_host(seed, name, one != 0, count, out))
 }
@@ -535,6 +553,10 @@ FR_API int friday_engine_generate(void* e, int n_prompts, const int* offsets, co
     })
 }
 
+FR_API int friday_engine_set_trace(void* e, void* trace, int launches) {
+    GUARD(((Engine*)e)->impl()->ops->set_trace((unsigned long long*)trace, launches))
+}
+
 FR_API int friday_engine_check(void* e) { GUARD(((Engine*)e)->check()) }
 
 FR_API int friday_engine_profile(void* e, const char** json) {
@@ -560,6 +582,7 @@ FR_API int friday_engine_stats(void* e, const char** json) {
         j.set("launches", Json((int64_t)eng.launches()));
         j.set("held_tokens", Json(eng.cacheHeldTokens()));
         j.set("last_upload_bytes", Json((int64_t)eng.impl()->stepper->last_upload_bytes));
+        j.set("last_queue_ms", Json(eng.impl()->stepper->last_queue_ms));
         j.set("kept_decoders", Json((int64_t)eng.impl()->kept.size()));
         *json = hand_back(j.dump());
     })

@@ -75,6 +75,7 @@ void Stepper::check(const StepBatch& b) const {
 static inline size_t pad4(size_t n) { return (n + 3) & ~(size_t)3; }
 
 size_t Stepper::step(const StepBatch& b, float* out, bool out_on_device) {
+    const auto t_begin = std::chrono::steady_clock::now();
     check(b);
     const size_t n = b.slots.size();
     const int64_t vocab = model_.spec.vocab_size;
@@ -197,6 +198,7 @@ size_t Stepper::step(const StepBatch& b, float* out, bool out_on_device) {
     }
     ops_.arena = nullptr;
     last_logits = result;
+    last_queue_ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t_begin).count();
     if (total_want && out) {
         cuda_check(cudaMemcpyAsync(out, result.data, total_want * vocab * sizeof(float),
                                    out_on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost, ops_.stream()),

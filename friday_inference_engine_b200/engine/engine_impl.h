@@ -52,6 +52,7 @@ public:
     // The logits of the last step stay on the device until the next one: [rows, vocab], in the order of the result.
     Tensor last_logits;
     size_t last_upload_bytes = 0;
+    double last_queue_ms = 0;      // host time of the last step until all its launches were queued
 
 private:
     DecoderModel& model_;

@@ -45,48 +45,61 @@ static DType storage_dtype(const StoredTensor& st, const ParamDecl& d, DType com
     return compute;
 }
 
-void DecoderModel::load(WeightSource& source, Ops& ops) {
-    std::vector<Part::Named> all = named_params(), named;
+std::vector<StoredParam> plan_storage(const std::vector<Part::Named>& all, const WeightSource& source, DType compute,
+                                      const std::vector<std::string>& ignorable) {
+    std::vector<Part::Named> named;
     std::set<std::string> seen;
     for (auto& e : all)
         if (seen.insert(e.name).second) named.push_back(e);
-    check_names(named, source, spec.ignorable);
-    parameter_bytes_ = 0;
-    // stacked tensors first: 32-bit if any member is stored so
+    check_names(named, source, ignorable);
+    std::vector<StoredParam> plan;
+    // a stacked tensor is 32-bit if any member is stored so
     std::map<std::pair<Part*, std::string>, DType> stacked_dtype;
     for (const auto& e : named) {
-        if (e.decl.into.empty()) continue;
         StoredTensor st;
         source.info(e.name, &st);
-        const DType d = storage_dtype(st, e.decl, env.dtype, e.name);
-        auto key = std::make_pair(e.owner, e.decl.into);
-        auto it = stacked_dtype.find(key);
-        if (it == stacked_dtype.end()) stacked_dtype[key] = d;
-        else if (d == DType::F32) it->second = DType::F32;
+        StoredParam s;
+        s.param = e;
+        s.dtype = storage_dtype(st, e.decl, compute, e.name);
+        if (!e.decl.into.empty()) {
+            auto key = std::make_pair(e.owner, e.decl.into);
+            auto it = stacked_dtype.find(key);
+            if (it == stacked_dtype.end()) stacked_dtype[key] = s.dtype;
+            else if (s.dtype == DType::F32) it->second = DType::F32;
+        }
+        plan.push_back(s);
     }
-    for (const auto& kv : stacked_dtype) {
-        Part* owner = kv.first.first;
+    for (auto& s : plan)
+        if (!s.param.decl.into.empty()) s.dtype = stacked_dtype[std::make_pair(s.param.owner, s.param.decl.into)];
+    return plan;
+}
+
+size_t load_params(const std::vector<StoredParam>& plan, WeightSource& source, Ops& ops) {
+    size_t bytes = 0;
+    for (const auto& s : plan) {          // stacked tensors first
+        const Part::Named& e = s.param;
+        if (e.decl.into.empty() || e.owner->tensors.count(e.decl.into)) continue;
         const std::vector<int64_t>* shape = nullptr;
-        for (const auto& s : owner->stacked)
-            if (s.first == kv.first.second) shape = &s.second;
-        if (!shape) throw ConfigError("a parameter is stacked into '" + kv.first.second + "', which its part never declared");
-        auto mem = std::make_shared<DeviceBuffer>((size_t)(*shape)[0] * (*shape)[1] * dtype_size(kv.second));
-        owner->set_tensor(kv.first.second, Tensor::make(mem->get(), kv.second, *shape));
-        owner->hold(mem);
-        parameter_bytes_ += mem->bytes();
+        for (const auto& st : e.owner->stacked)
+            if (st.first == e.decl.into) shape = &st.second;
+        if (!shape) throw ConfigError("a parameter is stacked into '" + e.decl.into + "', which its part never declared");
+        auto mem = std::make_shared<DeviceBuffer>((size_t)(*shape)[0] * (*shape)[1] * dtype_size(s.dtype));
+        e.owner->set_tensor(e.decl.into, Tensor::make(mem->get(), s.dtype, *shape));
+        e.owner->hold(mem);
+        bytes += mem->bytes();
     }
-    for (const auto& e : named) {
-        StoredTensor st;
-        source.info(e.name, &st);
+    for (const auto& s : plan) {
+        const Part::Named& e = s.param;
         Tensor dst;
         const int64_t cols = e.decl.shape.size() >= 2 ? e.decl.shape.back() : 1;
         if (e.decl.into.empty()) {
-            const DType d = storage_dtype(st, e.decl, env.dtype, e.name);
-            auto mem = std::make_shared<DeviceBuffer>((size_t)st.numel() * dtype_size(d));
-            Tensor t = Tensor::make(mem->get(), d, e.decl.shape);
+            int64_t n = 1;
+            for (int64_t d : e.decl.shape) n *= d;
+            auto mem = std::make_shared<DeviceBuffer>((size_t)n * dtype_size(s.dtype));
+            Tensor t = Tensor::make(mem->get(), s.dtype, e.decl.shape);
             e.owner->set_tensor(e.local, t);
             e.owner->hold(mem);
-            parameter_bytes_ += mem->bytes();
+            bytes += mem->bytes();
             dst = t;
             dst.ld = cols;
         } else {
@@ -100,6 +113,15 @@ void DecoderModel::load(WeightSource& source, Ops& ops) {
         source.load(e.name, dst, ops.stream());
     }
     cuda_check(cudaStreamSynchronize(ops.stream()), "cudaStreamSynchronize");
+    return bytes;
+}
+
+std::vector<StoredParam> DecoderModel::plan_storage(const WeightSource& source) {
+    return friday::plan_storage(named_params(), source, env.dtype, spec.ignorable);
+}
+
+void DecoderModel::load(WeightSource& source, Ops& ops) {
+    parameter_bytes_ = load_params(plan_storage(source), source, ops);
     embedding = root_->tensor(spec.embedding);
     head = spec.head.empty() ? embedding : root_->tensor(spec.head);       // tied: one copy in memory
     if (!spec.head_bias.empty()) head_bias = root_->tensor(spec.head_bias);

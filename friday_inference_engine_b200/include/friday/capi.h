@@ -52,6 +52,8 @@ int friday_describe_model(const char* config_json, const char** json);
 /* weights */
 int friday_write_random_model(const char* dir, const char* config_json, uint64_t seed, const char* dtype, int shards);
 int friday_check_weights(const char* model_dir);
+/* in which dtype every tensor of the folder would be kept by an engine of `dtype` (name, dtype, into) */
+int friday_storage_plan(const char* model_dir, const char* dtype, const char** json);
 int friday_random_tensor(uint64_t seed, const char* name, int one, int64_t count, float* out);
 int friday_safetensors_open(const char* path_or_dir, void** handle);
 int friday_safetensors_list(void* handle, const char** json);
@@ -94,6 +96,8 @@ int friday_engine_prefill(void* engine, const int* tokens, int n, int pos, float
 typedef void (*friday_on_step)(void* user, int n, const int* requests, const int* tokens);
 int friday_engine_generate(void* engine, int n_prompts, const int* offsets, const int* tokens, const char* options_json,
                            friday_on_step on_step, void* user, const char** result_json);
+/* the next `launches` tensor-core products write their CTAs' time stamps to trace[launch][sm][16] (uint64) */
+int friday_engine_set_trace(void* engine, void* trace, int launches);
 int friday_engine_check(void* engine);
 int friday_engine_profile(void* engine, const char** json);
 int friday_engine_stats(void* engine, const char** json);

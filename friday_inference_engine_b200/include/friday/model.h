@@ -16,6 +16,14 @@
 
 namespace friday {
 
+// The loader, for any tree of parts.  plan_storage compares the declared tensors with the source (one WeightsError
+// for everything that does not fit) and decides in which dtype each is kept; load_params allocates device memory,
+// stacks what the parts asked to have stacked, copies, and returns the bytes held.  Parts are finalized by the caller.
+struct StoredParam { Part::Named param; DType dtype; };
+std::vector<StoredParam> plan_storage(const std::vector<Part::Named>& declared, const WeightSource& source, DType compute,
+                                      const std::vector<std::string>& ignorable);
+size_t load_params(const std::vector<StoredParam>& plan, WeightSource& source, Ops& ops);
+
 class DecoderModel {
 public:
     // Builds the parts (host only: no device memory is touched until load()).
@@ -30,7 +38,10 @@ public:
 
     // Every tensor the model needs, by full name (a layer that the run order names twice has its tensors once).
     std::vector<Part::Named> named_params();
-    // Compares names and shapes with the source (one WeightsError for everything), then copies and finalizes.
+    // Compares names and shapes with the source (one WeightsError for everything) and decides in which dtype every
+    // tensor is kept (the storage rule of weights.h; members of a stacked tensor share its dtype).  Host only.
+    std::vector<StoredParam> plan_storage(const WeightSource& source);
+    // plan_storage, then allocates, copies and finalizes.
     void load(WeightSource& source, Ops& ops);
     std::map<int, CacheRequest> cache_requests() const;
     size_t parameter_bytes() const { return parameter_bytes_; }

@@ -152,7 +152,11 @@ public:
     void plan(int64_t rows, int64_t n, int64_t k, bool* swapped, int* bn, int* splits = nullptr);
     int decode_splits(int n_seqs, int n_heads, int n_kv_heads, int head_dim, int max_kv_len);
     int attention_splits(int64_t rows, int n_heads, int max_kv_len) const;
-    bool fusion_enabled() const { return fuse_; }
+    // FRIDAY_FUSE=0 keeps norms, rotation and cache write in kernels of their own (read at every call, for A/B runs)
+    bool fusion_enabled() const;
+    // For measurements: the next `launches` tensor-core products each fill one [sm_count][16] block of `trace`
+    // (unsigned 64-bit) with their CTAs' time stamps (csrc/gemm_tc_fusion.h, part 4); null switches it off.
+    void set_trace(unsigned long long* trace, int launches) { trace_ = trace; trace_left_ = launches; trace_next_ = 0; }
     long long launches() const { return launches_; }
     void add_launches(long long n) { launches_ += n; }
 
@@ -174,8 +178,10 @@ private:
     DeviceBuffer tc_scratch_, tc_counters_, status_, attn_counters_;
     std::map<std::tuple<int64_t, int64_t, int64_t>, std::tuple<bool, int, int>> plans_;
     std::map<std::pair<int, int>, int> cluster_fit_;
-    bool fuse_, attn_tc_, profile_ = false;
+    bool attn_tc_, profile_ = false;
     long long launches_ = 0;
+    unsigned long long* trace_ = nullptr;
+    int trace_left_ = 0, trace_next_ = 0;
     std::vector<std::tuple<int, cudaEvent_t, cudaEvent_t>> events_;
     std::vector<cudaEvent_t> spare_events_;
 };

@@ -103,6 +103,7 @@ _SIGNATURES = {
     "friday_describe_model": [S, PS],
     "friday_write_random_model": [S, S, c_uint64, S, I],
     "friday_check_weights": [S],
+    "friday_storage_plan": [S, S, PS],
     "friday_random_tensor": [c_uint64, S, I, c_int64, P],
     "friday_safetensors_open": [S, PP],
     "friday_safetensors_list": [P, PS],
@@ -124,6 +125,7 @@ _SIGNATURES = {
     "friday_engine_step_token": [P, I, I, P],
     "friday_engine_prefill": [P, PI, I, I, P],
     "friday_engine_generate": [P, I, PI, PI, S, ON_STEP, P, PS],
+    "friday_engine_set_trace": [P, P, I],
     "friday_engine_check": [P],
     "friday_engine_profile": [P, PS],
     "friday_engine_stats": [P, PS],

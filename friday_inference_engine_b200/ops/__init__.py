@@ -9,7 +9,6 @@ ordered with the torch operations around them.
 from ctypes import byref, c_int, c_void_p
 
 from .. import native
-from . import lib  # noqa: F401  (direct access to the kernel libraries' C entry points, for tests of those)
 
 _CODES = None
 
@@ -247,6 +246,43 @@ class CudaOps:
         native.call("friday_ops_attention_splits", self._h, rows, n_heads, max_kv_len, byref(s))
         return s.value
 
+    # -- one attention kernel's launcher, called directly with chosen arguments (tests of that kernel alone) -----
+    def _test_buffers(self, device):
+        import torch
+        if getattr(self, "_tb", None) is None:
+            self._tb = (torch.zeros((1 << 16,), dtype=torch.int32, device=device),
+                        torch.zeros((4,), dtype=torch.int32, device=device))
+        return self._tb
+
+    def attention_tc(self, q, q_stride, out, k_pool, v_pool, block_table, seq_start, seq_qlen, seq_pos0, seq_live,
+                     n_seqs, max_q_len, n_heads, n_kv_heads, head_dim, window, scale):
+        from . import lib
+        status = self._test_buffers(q.device)[1]
+        lib.family("attention_tc").call(
+            "attention_tc", q.data_ptr(), q_stride, q.shape[0], out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
+            k_pool.shape[0], block_table.data_ptr(), block_table.shape[1], seq_start.data_ptr(), seq_qlen.data_ptr(),
+            seq_pos0.data_ptr(), 0 if seq_live is None else seq_live.data_ptr(), n_seqs, max_q_len, n_heads, n_kv_heads,
+            head_dim, window or 0, float(scale), status.data_ptr(), None)
+        if int(status[0].item()):
+            status.zero_()
+            raise native.KernelError("the tcgen05 attention kernel gave up on one of its bounded waits")
+
+    def attention_mma(self, q, q_stride, out, k_pool, v_pool, block_table, seq_start, seq_qlen, seq_pos0, seq_live,
+                      n_seqs, max_q_len, n_heads, n_kv_heads, head_dim, window, scale, keys_mode, splits, geometry=None):
+        import torch
+        from . import lib
+        rows = out.shape[0]
+        counters, status = self._test_buffers(q.device)
+        scratch = None
+        if splits > 1:
+            scratch = torch.empty((rows * n_heads * splits * (head_dim + 2),), dtype=torch.float32, device=q.device)
+        lib.family("attention_mma").call(
+            "attention_mma", q.data_ptr(), q_stride, out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), k_pool.shape[0],
+            block_table.data_ptr(), block_table.shape[1], 64, seq_start.data_ptr(), seq_qlen.data_ptr(),
+            seq_pos0.data_ptr(), 0 if seq_live is None else seq_live.data_ptr(), n_seqs, rows, max_q_len, n_heads,
+            n_kv_heads, head_dim, window or 0, float(scale), 1 if keys_mode else 0, splits,
+            0 if scratch is None else scratch.data_ptr(), counters.data_ptr(), counters.numel(), status.data_ptr(), None)
+
     # -- sampling ---------------------------------------------------------
     def sample(self, logits, temperature, streams, steps, seed, row_live=None, out=None):
         import torch
@@ -274,6 +310,13 @@ def fusion_enabled():
 
 def launch_count():
     return backend().info()["launches"]
+
+
+def __getattr__(name):
+    if name == "lib":          # direct access to the kernel libraries' C entry points, for tests of those
+        import importlib
+        return importlib.import_module(".lib", __name__)
+    raise AttributeError(name)
 
 
 def embedding(*a, **k):

@@ -33,7 +33,7 @@ FAMILIES = ("rowwise", "gemm_simt", "attention_simt", "sampling", "gemm_tc", "at
 PACKAGE = os.path.dirname(_HERE)
 SOURCE_DIRS = ("config", "weights", "parts", "cache", "engine", "sampling", "ops")
 INCLUDE = os.path.join(PACKAGE, "include")
-HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-ffp-contract=off", "-Wall", "-Wno-unused-function"]
+HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-ffp-contract=off", "-Wall", "-Wno-unused-function"]
 # libraries other than the runtime that a family links
 EXTRA_LIBS = {}
 

@@ -1,8 +1,9 @@
-"""Loads the kernel libraries (ctypes) and declares their C entry points.
+"""Direct access to the kernel libraries' C entry points (ctypes), for tests that call one
+kernel's launcher with chosen arguments and for measurements.  The product path does not
+come through here: the engine library opens the same files itself (ops/kernels.cpp).
 
 A library is built on first use (ops/build.py) and loaded from the package's own
-build folder, never from an installed location.  A failure to build or load is an
-error of the call that needed the kernel: nothing falls back to another path.
+build folder, never from an installed location.
 """
 import ctypes
 from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
@@ -10,14 +11,6 @@ from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
 from . import build
 
 P, I, F = c_void_p, c_int, c_float
-
-
-class GemmFusion(ctypes.Structure):
-    """csrc/gemm_tc_fusion.h, field for field."""
-    _fields_ = [("in_ssq", P), ("in_parts", I), ("in_width", F), ("in_eps", F),
-                ("norm_w", P), ("norm_out", P), ("out_ssq", P), ("norm_w_dtype", I),
-                ("row_seq", P), ("row_pos", P), ("denom", P), ("k_pool", P), ("v_pool", P), ("table", P),
-                ("rot", I), ("nq", I), ("nkv", I), ("hd", I), ("table_width", I), ("page", I), ("trace", P)]
 
 
 _SIGNATURES = {
@@ -35,7 +28,6 @@ _SIGNATURES = {
     "gemm_tc": {
         "gemm_tc": [P, P, P, I, P, I, P, I, I, I, I, I, I, P, c_longlong, P, I, P, I, I, I, I, P],
         "gemm_tc_act": [P, P, P, I, P, I, P, I, I, I, I, I, I, P, c_longlong, P, I, P, I, I, I, I, I, P],
-        "gemm_tc_fused": [P, P, P, I, P, I, P, I, I, I, I, I, I, P, c_longlong, P, I, P, I, I, I, I, I, P, P],
         "gemm_tc_plan": [I, I, I, I, I, I, I, P],
     },
     "attention_simt": {
@@ -56,22 +48,7 @@ _SIGNATURES = {
 }
 
 
-_launches = 0
-
-
-def launch_count():
-    """Calls into the kernel libraries so far (each launches at least one kernel); graph replays add the
-    number of calls that were captured."""
-    return _launches
-
-
-def add_launches(n):
-    global _launches
-    _launches += n
-
-
-class KernelError(RuntimeError):
-    """A kernel refused its arguments or the CUDA runtime reported an error."""
+from ..native import KernelError  # noqa: E402
 
 
 class Family:
@@ -92,8 +69,6 @@ class Family:
             f.restype = c_int
 
     def call(self, fn, *args):
-        global _launches
-        _launches += 1
         rc = getattr(self.cdll, fn)(*args)
         if rc != 0:
             raise KernelError("%s: %s" % (fn, self._last_error().decode("utf-8", "replace")))

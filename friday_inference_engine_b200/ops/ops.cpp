@@ -66,7 +66,6 @@ Ops::Ops(int device, cudaStream_t stream) : device_(device), stream_(stream) {
     tc_counters_ = DeviceBuffer(4096 * sizeof(int), true);
     status_ = DeviceBuffer(4 * sizeof(int), true);
     attn_counters_ = DeviceBuffer(((size_t)1 << 16) * sizeof(int), true);
-    fuse_ = env_on("FRIDAY_FUSE");
     attn_tc_ = env_on("FRIDAY_ATTN_TC");
     profile_ = env_on("FRIDAY_PROFILE", false);
 }
@@ -77,6 +76,8 @@ Ops::~Ops() {
 }
 
 void Ops::set_profile(bool on) { profile_ = on; }
+
+bool Ops::fusion_enabled() const { return env_on("FRIDAY_FUSE"); }
 
 void Ops::take_profile(double ms[Segments], long long calls[Segments]) {
     for (int i = 0; i < Segments; ++i) { ms[i] = 0; calls[i] = 0; }
@@ -196,7 +197,7 @@ bool Ops::tensor_core_ok(const Tensor& x, const Tensor& weight, const Tensor& ou
 
 bool Ops::few_rows_tile_ok(const Tensor& x, const Tensor& weight, const Tensor& out, const Tensor* residual,
                            int64_t max_rows, int columns) const {
-    return fuse_ && out.dtype == DType::BF16 && x.rows() <= max_rows && weight.rows() % columns == 0 && out.ld % 8 == 0 &&
+    return fusion_enabled() && out.dtype == DType::BF16 && x.rows() <= max_rows && weight.rows() % columns == 0 && out.ld % 8 == 0 &&
            aligned16(out.data) && (!residual || aligned16(residual->data)) && tensor_core_ok(x, weight, out, residual);
 }
 
@@ -235,6 +236,13 @@ Tensor Ops::linear_tc(const Tensor& x, const Tensor& weight, const Tensor* bias,
                       int swap, int bn, int splits, int act, GemmFusion* fusion) {
     Timed t(*this, Product);
     const auto& g = kernels::gemm_tc();
+    GemmFusion traced;
+    if (trace_ && trace_next_ < trace_left_) {
+        if (fusion) traced = *fusion;
+        else memset(&traced, 0, sizeof traced);
+        traced.trace = trace_ + (size_t)trace_next_++ * sms_ * 16;
+        fusion = &traced;
+    }
     call(launches_, g,
          g.fused(x.data, weight.data, out.data, code(out.dtype), bias ? bias->data : nullptr, bias ? code(bias->dtype) : 0,
                  residual ? residual->data : nullptr, (int)x.rows(), (int)weight.rows(), (int)x.cols(), (int)x.ld,

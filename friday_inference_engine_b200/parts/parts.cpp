@@ -104,6 +104,8 @@ void register_part(const std::string& category, const std::string& kind, PartFac
 }
 
 std::vector<std::string> registered_parts(const std::string& category) {
+    if (!known_category(category))
+        throw ConfigError("unknown part category '" + category + "' (have: norm, position, mixer, feed_forward, block)");
     std::lock_guard<std::mutex> lock(reg_mutex());
     std::vector<std::string> out;
     for (const auto& kv : reg()[category]) out.push_back(kv.first);

@@ -23,6 +23,12 @@ def check_weights(model_dir):
     native.call("friday_check_weights", native.text(str(model_dir)))
 
 
+def storage_plan(model_dir, dtype="bfloat16"):
+    """For every tensor of the folder, the dtype an engine of `dtype` keeps it in, and the stacked tensor it lands in
+    (bfloat16 unless the file stores it in 32 bits; members of a stacked tensor share its dtype).  Needs no GPU."""
+    return native.call_json("friday_storage_plan", native.text(str(model_dir)), native.text(dtype))
+
+
 def random_tensor(seed, name, count, one=False):
     """The random-weights mode's float32 numbers for tensor `name` (before rounding to the stored dtype)."""
     import numpy as np

@@ -110,6 +110,45 @@ def test_cut_into_passes_and_continued(root, where, name):
     eng.free_slot(s)
 
 
+@pytest.mark.parametrize("name", ["B", "C"])
+def test_several_sequences_over_several_passes(root, where, name):
+    """Three sequences of unequal lengths cut into passes of 48 tokens: the later passes hold fewer sequences, and
+    every pass finds the earlier tokens of its sequences in the cache."""
+    eng, pm = engine(root, name, where, prefill_chunk=48)
+    lens = [150, 40, 97]
+    prompts = tiny_configs.random_prompts(lens, eng.vocab_size, 18)
+    want = [[149, 0, 47, 48, 96], [39, 5], [96, 95, 48, 1]]
+    slots = [eng.alloc_slot() for _ in prompts]
+    got = harness.to_np(eng.step(slots, prompts, want))
+    row = 0
+    for i, (p, w) in enumerate(zip(prompts, want)):
+        harness.check_logits(got[row:row + len(w)], plain_model.logits(pm, p)[w], where[1], "%s sequence %d in passes" % (name, i))
+        row += len(w)
+    for s in slots:
+        eng.free_slot(s)
+    assert nothing_held(eng)
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_a_request_joins_a_running_batch(root, where, name):
+    """One step carries one-token continuations of two running sequences and the whole prompt of a third; the next
+    step continues all three by one token."""
+    eng, pm = engine(root, name, where)
+    prompts = tiny_configs.random_prompts([72, 30, 101], eng.vocab_size, 19)
+    refs = [plain_model.logits(pm, p) for p in prompts]
+    a, b, c = (eng.alloc_slot() for _ in range(3))
+    eng.step([a, b], [prompts[0][:64], prompts[1][:20]], [[], []])
+    got = harness.to_np(eng.step([a, c, b], [[prompts[0][64]], prompts[2][:95], [prompts[1][20]]], [[0], [94, 0], [0]]))
+    harness.check_logits(got[0:1], refs[0][64:65], where[1], "%s running sequence a in a mixed step" % name)
+    harness.check_logits(got[1:3], refs[2][[94, 0]], where[1], "%s joining prompt" % name)
+    harness.check_logits(got[3:4], refs[1][20:21], where[1], "%s running sequence b in a mixed step" % name)
+    got = harness.to_np(eng.step([a, b, c], [[prompts[0][65]], [prompts[1][21]], [prompts[2][95]]], [[0]] * 3))
+    for k, (i, at) in enumerate([(0, 65), (1, 21), (2, 95)]):
+        harness.check_logits(got[k:k + 1], refs[i][at:at + 1], where[1], "%s after the mixed step, request %d" % (name, i))
+    for s in (a, b, c):
+        eng.free_slot(s)
+
+
 def test_first_tokens_of_a_sequence(root, where):
     eng, pm = engine(root, "B", where)
     (p,) = tiny_configs.random_prompts([6], eng.vocab_size, 14)

@@ -1,7 +1,7 @@
-"""The generation loop's decisions, with a scripted step function and sampler (no GPU)."""
+"""The generation loop's decisions (engine/generate.cpp), with a scripted step function and sampler (no GPU)."""
 import pytest
 
-from friday_inference_engine_b200.engine.generate import GenerationError, generate
+from friday_inference_engine_b200.engine import GenerationError, generate_loop as generate
 
 
 class Script:
@@ -32,7 +32,7 @@ class Script:
             self.held[s] += len(t)
         return list(slots)
 
-    def sample(self, logits, streams, steps):
+    def sample(self, streams, steps):
         return [self.scripts[r][k] for r, k in zip(streams, steps)]
 
     def run(self, prompts, **kw):
@@ -92,7 +92,7 @@ def test_refusals_and_cleanup():
 def test_streams_are_request_numbers():
     seen = []
 
-    def sample(logits, streams, steps):
+    def sample(streams, steps):
         seen.append((list(streams), list(steps)))
         return [1] * len(streams)
 

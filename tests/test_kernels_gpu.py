@@ -377,6 +377,98 @@ def test_attention_mma_long_prompt_sizes_of_the_7b_shape():
     mma_case([(0, 2048), (1000, 1100)], 28, 4, 128, None, False, 1, tcgen05=True)
 
 
+class StepGeo:
+    """The geometry of a step as the engine hands it to attention: per-sequence arrays on the device."""
+
+    def __init__(self, seqs):
+        i32 = dict(dtype=torch.int32, device=DEV)
+        self.n_seqs = len(seqs)
+        self.max_q_len = max(q for _, q in seqs)
+        self.max_kv_len = max(a + q for a, q in seqs)
+        self.decode = self.max_q_len == 1
+        starts = np.concatenate([[0], np.cumsum([q for _, q in seqs])[:-1]])
+        self.seq_start = torch.tensor(starts.tolist(), **i32)
+        self.seq_qlen = torch.tensor([q for _, q in seqs], **i32)
+        self.seq_pos0 = torch.tensor([a for a, _ in seqs], **i32)
+        self.row_seq = torch.tensor(np.repeat(np.arange(len(seqs)), [q for _, q in seqs]).tolist(), **i32)
+        self.row_pos = torch.tensor(np.concatenate([np.arange(a, a + q) for a, q in seqs]).tolist(), **i32)
+
+
+def rows_reference(q, pos, k, v, window):
+    """Attention of a few query rows at positions `pos` over keys 0 .. pos (the last `window` of them), float64; the
+    formula of cpu_ops.cpp:45-83.  q [rows, nq, hd], k and v [n, nkv, hd]."""
+    rows, nq, hd = q.shape
+    group = nq // k.shape[1]
+    out = np.zeros((rows, nq, hd))
+    for r in range(rows):
+        lo = 0 if not window else max(0, pos[r] - window + 1)
+        for h in range(nq):
+            kk, vv = k[lo:pos[r] + 1, h // group], v[lo:pos[r] + 1, h // group]
+            s = kk @ q[r, h] * hd ** -0.5
+            e = np.exp(s - s.max())
+            out[r, h] = (e / e.sum()) @ vv
+    return out.reshape(rows, nq * hd)
+
+
+def long_case(seqs, nq, nkv, hd, window, dtype=torch.bfloat16, width=None, seed=60):
+    """seqs: (tokens held, tokens of the step).  Through ops.attention with the step's full geometry, so the kernel and
+    the number of splits are the ones the engine picks for these lengths."""
+    n_pages_each = [(a + q + PAGE - 1) // PAGE for a, q in seqs]
+    total_pages = sum(n_pages_each) + 2
+    perm = torch.randperm(total_pages, generator=torch.Generator().manual_seed(seed)).tolist()
+    kp = torch.full((total_pages, PAGE, nkv, hd), float("nan"), dtype=dtype, device=DEV)
+    vp = kp.clone()
+    table = torch.full((len(seqs), width or max(n_pages_each)), -1, dtype=torch.int32)
+    rows = sum(q for _, q in seqs)
+    qbuf = torch.zeros((rows, (nq + 2 * nkv) * hd), dtype=dtype, device=DEV)
+    refs, row = [], 0
+    for s, (a, q) in enumerate(seqs):
+        n = a + q
+        qs = rnd((q, nq, hd), dtype, seed + 3 * s + 1) * 2
+        ks, vs = rnd((n, nkv, hd), dtype, seed + 3 * s + 2), rnd((n, nkv, hd), dtype, seed + 3 * s + 3)
+        far = 7 + s                                       # one key far back matches the first query's first head
+        ks[far, :, :] = 0
+        ks[far, :, 1] = 6.0
+        qs[0, 0, :] = 0
+        qs[0, 0, 1] = 6.0 * hd ** 0.5
+        refs.append(rows_reference(f64(qs), list(range(a, n)), f64(ks), f64(vs), window))
+        pages = [perm.pop() for _ in range(n_pages_each[s])]
+        table[s, :len(pages)] = torch.tensor(pages, dtype=torch.int32)
+        pad = len(pages) * PAGE - n
+        kp[pages] = torch.cat([ks, torch.full((pad, nkv, hd), float("nan"), dtype=dtype, device=DEV)]).view(len(pages), PAGE, nkv, hd)
+        vp[pages] = torch.cat([vs, torch.full((pad, nkv, hd), float("nan"), dtype=dtype, device=DEV)]).view(len(pages), PAGE, nkv, hd)
+        qbuf[row:row + q, : nq * hd] = qs.reshape(q, nq * hd)
+        row += q
+    geo = StepGeo(seqs)
+    out = torch.full((rows, nq * hd), float("nan"), dtype=dtype, device=DEV)
+    ops.attention(qbuf, qbuf.stride(0), out, kp, vp, table.to(DEV), PAGE, geo.row_seq, geo.row_pos, nq, nkv, hd, window,
+                  hd ** -0.5, geo)
+    ops.backend().check_status()
+    close(out, np.concatenate(refs, axis=0), dtype, "attention over long contexts", bf16_rel=0.02)
+    return geo
+
+
+@pytest.mark.parametrize("nq,nkv", [(28, 4), (40, 8)])
+@pytest.mark.parametrize("longest", [4096, 8192])
+def test_one_token_steps_over_long_contexts(nq, nkv, longest):
+    """Page tables of 64 and 128 entries and as many splits as the engine picks for the longest sequence."""
+    geo = long_case([(longest - 1, 1), (longest // 2 + 5, 1), (99, 1)], nq, nkv, 128, None)
+    assert ops.backend().decode_splits(3, nq, nkv, 128, geo.max_kv_len) == 8
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_one_token_steps_with_a_page_table_wider_than_a_cta(dtype):
+    """More pages than the kernel's CTA has threads (one sequence really holds 130 of them, the table has room for
+    170): the first pages come from shared memory, the rest from the table itself."""
+    long_case([(8300, 1), (69, 1)], 2, 1, 16, None, dtype=dtype, width=170)
+    long_case([(8300, 1), (69, 1)], 2, 1, 16, 4000, dtype=dtype, width=170)
+
+
+@pytest.mark.parametrize("nq,nkv", [(28, 4), (40, 8)])
+def test_continued_prompt_over_a_long_context(nq, nkv):
+    long_case([(6000, 300), (0, 130)], nq, nkv, 128, None)
+
+
 def test_attention_mma_dead_rows_give_zero():
     dt = torch.bfloat16
     nq, nkv, hd = 4, 2, 32
@@ -467,9 +559,9 @@ def test_gemm_with_rotation_and_cache_write_in_its_epilogue(m, nq, nkv, hd, rot,
         monkeypatch.setenv("FRIDAY_FUSE", fuse)
         kp = torch.zeros((8, PAGE, nkv, hd), dtype=torch.bfloat16, device=DEV)
         vp = torch.zeros_like(kp)
-        before = ops.lib.launch_count()
+        before = ops.launch_count()
         qkv = ops.qkv_rope_write(x, w, b, row_seq, row_pos, denom, rot, nq, nkv, hd, kp, vp, table, PAGE)
-        assert ops.lib.launch_count() - before == (1 if fuse == "1" else 2), "fused: one launch; else two"
+        assert ops.launch_count() - before == (1 if fuse == "1" else 2), "fused: one launch; else two"
         results.append((qkv, kp, vp))
     ops.backend().check_status()
     live = (row_seq >= 0).cpu().numpy()
@@ -540,7 +632,7 @@ def test_gemm_of_many_rows_begins_a_norm(m, n, k, k2):
     assert isinstance(h, ops.DeferredNorm)
     assert torch.equal(out, ops.linear(x, w, bias=b, residual=res)), "the product itself is unchanged"
     plan = np.zeros(5, dtype=np.int64)
-    ops.lib.family("gemm_tc").call("gemm_tc_plan", m, n, k, 148, -1, -1, -1, plan.ctypes.data)
+    ops.lib.family("gemm_tc").call("gemm_tc_plan", m, n, k, ops.backend().info()["sm_count"], -1, -1, -1, plan.ctypes.data)
     bn = int(plan[1])
     assert plan[0] == 0 and h.ssq.shape == (-(-n // bn), m)
     sq = f64(out) ** 2
@@ -572,7 +664,7 @@ def test_norm_and_rotation_fused_into_split_k_products():
     n = (nq + 2 * nkv) * hd
     x, w = rnd((m, k), torch.bfloat16, 90, 0.5), rnd((n, k), torch.bfloat16, 91, 0.05)
     plan = np.zeros(5, dtype=np.int64)
-    ops.lib.family("gemm_tc").call("gemm_tc_plan", m, n, k, 148, -1, -1, -1, plan.ctypes.data)
+    ops.lib.family("gemm_tc").call("gemm_tc_plan", m, n, k, ops.backend().info()["sm_count"], -1, -1, -1, plan.ctypes.data)
     assert plan[0] == 1 and plan[2] > 1, "this shape is meant to be split along k"
     g = rnd((n,), torch.bfloat16, 92) + 1.0
     out, h = ops.linear_norm(x, w, g, 1e-6)

@@ -96,3 +96,32 @@ def test_replay_three_ways(root, name, dtype):
     rp.step(n, [{"id": "q", "tokens": reqs[0][:5], "want": []}], end=["q"])       # nothing wanted: no file
     assert not os.path.exists(os.path.join(out, "%d.f32" % n))
     rp.close()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_a_request_joins_a_running_batch(root, dtype):
+    """Steps that mix one-token entries with a fresh prompt (the step function allows it), on the windowed model."""
+    d, pm = harness.model_dir(root, "B")
+    vocab = pm.vocab
+    reqs = tiny_configs.random_prompts([90, 70, 40], vocab, 32)
+    refs = [plain_model.logits(pm, p) for p in reqs]
+    out = str(root / ("mixed_%s" % dtype))
+    rp = Replay(d, dtype, out, max_tokens=320)
+    rp.step(0, [{"id": "a", "tokens": reqs[0][:66], "want": [65]}])
+    harness.check_logits(rp.logits(0, vocab), refs[0][65:66], dtype, "first prompt")
+    rp.step(1, [{"id": "a", "tokens": [reqs[0][66]], "want": [0]}, {"id": "b", "tokens": reqs[1][:50], "want": [0, 49]}])
+    got = rp.logits(1, vocab)
+    harness.check_logits(got[0:1], refs[0][66:67], dtype, "running request in a mixed step")
+    harness.check_logits(got[1:3], refs[1][[0, 49]], dtype, "joining prompt")
+    rp.step(2, [{"id": "c", "tokens": reqs[2][:39], "want": [38]}, {"id": "b", "tokens": [reqs[1][50]], "want": [0]},
+                {"id": "a", "tokens": [reqs[0][67]], "want": [0]}], end=["a"])
+    got = rp.logits(2, vocab)
+    harness.check_logits(got[0:1], refs[2][38:39], dtype, "second joining prompt")
+    harness.check_logits(got[1:2], refs[1][50:51], dtype, "request b after joining")
+    harness.check_logits(got[2:3], refs[0][67:68], dtype, "request a in its last step")
+    rp.step(3, [{"id": "b", "tokens": [reqs[1][51]], "want": [0]}, {"id": "c", "tokens": [reqs[2][39]], "want": [0]}],
+            end=["b", "c"])
+    got = rp.logits(3, vocab)
+    harness.check_logits(got[0:1], refs[1][51:52], dtype, "request b, one token more")
+    harness.check_logits(got[1:2], refs[2][39:40], dtype, "request c, one token more")
+    rp.close()

@@ -97,21 +97,53 @@ def test_wide_layers_prompt_then_tokens(wide, dtype):
     eng.check()
 
 
-def test_wide_layers_device_decoder(wide, monkeypatch):
+def test_wide_layers_device_decoder(wide):
     d, pm = wide
-    for fused in ("0", "1"):
-        monkeypatch.setenv("FRIDAY_FUSED_DECODE", fused)
-        eng = Engine(model_path=d, dtype="bfloat16", max_ctx=512, max_batch=2)
-        lens, extra = [100, 61], 6
-        prompts = tiny_configs.random_prompts([n + extra for n in lens], WIDE["vocab_size"], 61)
-        refs = [plain_model.logits(pm, p, at=[len(p) - 1]) for p in prompts]
-        slots = [eng.alloc_slot() for _ in prompts]
-        eng.step(slots, [p[:n] for p, n in zip(prompts, lens)], [[]] * 2)
-        dec = eng.decoder(slots, [p[n] for p, n in zip(prompts, lens)])
-        for t in range(extra):
-            dec.step([p[n + t] for p, n in zip(prompts, lens)])
-        got = harness.to_np(dec.logits)
-        for i in range(2):
-            harness.check_logits(got[i:i + 1], refs[i], "bfloat16", "wide decoder (fused %s) row %d" % (fused, i))
-        dec.check()
-        dec.close()
+    eng = Engine(model_path=d, dtype="bfloat16", max_ctx=512, max_batch=2)
+    lens, extra = [100, 61], 6
+    prompts = tiny_configs.random_prompts([n + extra for n in lens], WIDE["vocab_size"], 61)
+    refs = [plain_model.logits(pm, p, at=[len(p) - 1]) for p in prompts]
+    slots = [eng.alloc_slot() for _ in prompts]
+    eng.step(slots, [p[:n] for p, n in zip(prompts, lens)], [[]] * 2)
+    dec = eng.decoder(slots, [p[n] for p, n in zip(prompts, lens)])
+    for t in range(extra):
+        dec.step([p[n + t] for p, n in zip(prompts, lens)])
+    got = harness.to_np(dec.logits)
+    for i in range(2):
+        harness.check_logits(got[i:i + 1], refs[i], "bfloat16", "wide decoder row %d" % i)
+    dec.close()
+    eng.check()
+
+
+@pytest.mark.parametrize("rows", [17, 64])
+def test_wide_layers_decoder_of_many_rows(tmp_path, rows):
+    """The benchmark's batch-64 step at its layer sizes (one layer): 32- and 64-row tiles with split k where all CTAs
+    of a tile finish 16 rows each, the norm in the epilogues beside the rotary kernel, attention over 64 x 4 CTAs."""
+    cfg = dict(WIDE, num_hidden_layers=1, vocab_size=3000)
+    d = tiny_configs.make_model_dir(str(tmp_path / "model"), cfg, 12)
+    harness.sharpen(d, 2.0)
+    pm = plain_model.PlainModel.from_dir(d)
+    eng = Engine(model_path=d, dtype="bfloat16", max_ctx=128, max_batch=rows)
+    steps = 4
+    lens = [1 + (5 * i) % 23 for i in range(rows)]
+    prompts = tiny_configs.random_prompts([n + steps for n in lens], cfg["vocab_size"], 63)
+    refs = [plain_model.logits(pm, p, at=[n, n + steps - 1]) for p, n in zip(prompts, lens)]
+    slots = [eng.alloc_slot() for _ in prompts]
+    eng.step(slots, [p[:n] for p, n in zip(prompts, lens)], [[]] * rows)
+    dec = eng.decoder(slots, [p[n] for p, n in zip(prompts, lens)])
+    live = [True] * rows
+    for t in range(steps):
+        dec.step([p[n + t] if live[i] else 0 for i, (p, n) in enumerate(zip(prompts, lens))])
+        if t in (0, steps - 1):
+            got = harness.to_np(dec.logits)
+            for i in range(rows):
+                if live[i]:
+                    harness.check_logits(got[i:i + 1], refs[i][0 if t == 0 else 1][None], "bfloat16",
+                                         "%d wide rows: row %d step %d" % (rows, i, t))
+        if t == 1:
+            for i in range(1, rows, 4):
+                live[i] = False
+                dec.retire(i)
+                eng.free_slot(slots[i])
+    dec.close()
+    eng.check()

@@ -31,8 +31,9 @@ def test_noalloc_entry_point_matches_the_ordinary_one_twice():
     be = ops.backend()
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     stream = torch.cuda.current_stream().cuda_stream
-    # a decoding shape that splits k (36 tiles on 148 SMs), and one that does not
-    for m, n, k in ((8, 4608, 3584), (40, 18944, 512)):
+    # a decoding shape that splits k (36 tiles on 148 SMs) with the last CTA finishing the tile, one of 17 to 64 rows
+    # whose CTAs all finish 16 rows each of a split tile, and one that does not split
+    for m, n, k in ((8, 4608, 3584), (40, 4608, 3584), (40, 18944, 512)):
         x = torch.randn((m, k), generator=g).to(torch.bfloat16).to(dev)
         w = (torch.randn((n, k), generator=g) * 0.05).to(torch.bfloat16).to(dev)
         bias = torch.randn((n,), generator=g).to(torch.bfloat16).to(dev)
@@ -51,15 +52,13 @@ def test_noalloc_entry_point_matches_the_ordinary_one_twice():
             diff = float((out.double() - want.double()).abs().max())
             assert diff <= 3e-5 * scale, "call %d of %dx%dx%d differs from gemm_tc by %.3g" % (call, m, n, k, diff)
     # beyond the built-in area: refused with a message, nothing launched
-    m, n, k = 300, 700, 8192
+    m, n, k = 128, 5120, 16384
     x = torch.zeros((m, k), dtype=torch.bfloat16, device=dev)
     w = torch.zeros((n, k), dtype=torch.bfloat16, device=dev)
     out = torch.zeros((m, n), dtype=torch.float32, device=dev)
-    plan = (ctypes.c_longlong * 5)()
-    cdll.gemm_tc_plan(m, n, k, 148, -1, -1, -1, plan)
+    plan = (ctypes.c_longlong * 8)()
+    cdll.gemm_tc_plan(m, n, k, torch.cuda.get_device_properties(dev).multi_processor_count, -1, -1, -1, plan)
+    assert plan[3] > 2 * 1024 * 1024, "the test's premise: this shape's partial tiles do not fit the area"
     rc = fn(x.data_ptr(), w.data_ptr(), out.data_ptr(), 0, None, 0, None, m, n, k, k, k, n, status.data_ptr(), stream)
-    if plan[3] > 2 * 1024 * 1024:
-        assert rc != 0 and b"built-in area" in err()
-    else:
-        assert rc == 0
+    assert rc != 0 and b"built-in area" in err()
     torch.cuda.synchronize()
