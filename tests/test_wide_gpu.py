@@ -51,7 +51,7 @@ def test_layer_sizes_of_the_larger_models(config, dtype, tmp_path):
             err = float(np.abs(got_rows - ref_rows).max())
             assert err <= WIDE_FP32_ABS, "%s: |engine - plain| = %.3g > %.3g" % (what, err, WIDE_FP32_ABS)
         else:
-            harness.check_logits(got_rows, ref_rows, dtype, what)
+            harness.check_logits(got_rows, ref_rows, dtype, what, harness.BF16_WIDE)
 
     got = eng.step(slots, [p[:n] for p, n in zip(prompts, lens)], [[n - 1] for n in lens])
     for i in range(2):
@@ -85,7 +85,7 @@ def test_wide_layers_prompt_then_tokens(wide, dtype):
             err = float(np.abs(got_rows - ref_rows).max())
             assert err <= WIDE_FP32_ABS, "%s: |engine - plain| = %.3g > %.3g" % (what, err, WIDE_FP32_ABS)
         else:
-            harness.check_logits(got_rows, ref_rows, dtype, what)
+            harness.check_logits(got_rows, ref_rows, dtype, what, harness.BF16_WIDE)
 
     for i in range(3):
         check(harness.to_np(got[i:i + 1]), refs[i][0:1], "wide prompt %d" % i)
@@ -110,7 +110,7 @@ def test_wide_layers_device_decoder(wide):
         dec.step([p[n + t] for p, n in zip(prompts, lens)])
     got = harness.to_np(dec.logits)
     for i in range(2):
-        harness.check_logits(got[i:i + 1], refs[i], "bfloat16", "wide decoder row %d" % i)
+        harness.check_logits(got[i:i + 1], refs[i], "bfloat16", "wide decoder row %d" % i, harness.BF16_WIDE)
     dec.close()
     eng.check()
 
@@ -139,7 +139,7 @@ def test_wide_layers_decoder_of_many_rows(tmp_path, rows):
             for i in range(rows):
                 if live[i]:
                     harness.check_logits(got[i:i + 1], refs[i][0 if t == 0 else 1][None], "bfloat16",
-                                         "%d wide rows: row %d step %d" % (rows, i, t))
+                                         "%d wide rows: row %d step %d" % (rows, i, t), harness.BF16_WIDE)
         if t == 1:
             for i in range(1, rows, 4):
                 live[i] = False

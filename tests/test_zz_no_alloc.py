@@ -51,14 +51,21 @@ def test_noalloc_entry_point_matches_the_ordinary_one_twice():
             assert int(status.item()) == 0
             diff = float((out.double() - want.double()).abs().max())
             assert diff <= 3e-5 * scale, "call %d of %dx%dx%d differs from gemm_tc by %.3g" % (call, m, n, k, diff)
-    # beyond the built-in area: refused with a message, nothing launched
-    m, n, k = 128, 5120, 16384
+    # beyond the built-in area: refused with a message, nothing launched.  How k is split depends on the number of
+    # SMs, so the shape is chosen by asking the planner with this device's count.
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    plan = (ctypes.c_longlong * 8)()
+    too_big = None
+    for m, n, k in ((128, 9216, 8192), (300, 700, 8192), (128, 5120, 16384), (128, 4608, 32768), (256, 2304, 65536)):
+        cdll.gemm_tc_plan(m, n, k, sms, -1, -1, -1, plan)
+        if plan[3] > 2 * 1024 * 1024:
+            too_big = (m, n, k)
+            break
+    assert too_big is not None, "the test's premise: one of these shapes needs more partial tiles than the area holds"
+    m, n, k = too_big
     x = torch.zeros((m, k), dtype=torch.bfloat16, device=dev)
     w = torch.zeros((n, k), dtype=torch.bfloat16, device=dev)
     out = torch.zeros((m, n), dtype=torch.float32, device=dev)
-    plan = (ctypes.c_longlong * 8)()
-    cdll.gemm_tc_plan(m, n, k, torch.cuda.get_device_properties(dev).multi_processor_count, -1, -1, -1, plan)
-    assert plan[3] > 2 * 1024 * 1024, "the test's premise: this shape's partial tiles do not fit the area"
     rc = fn(x.data_ptr(), w.data_ptr(), out.data_ptr(), 0, None, 0, None, m, n, k, k, k, n, status.data_ptr(), stream)
     assert rc != 0 and b"built-in area" in err()
     torch.cuda.synchronize()
