@@ -29,23 +29,31 @@ __device__ __forceinline__ void copy_row(const T* __restrict__ src, T* __restric
     }
 }
 
+// Ids are checked on the host before a step runs.  An id that a sampler chose on the device can still be outside
+// the table (-1 for a row of logits without a finite entry): such a row reads nothing and becomes zeros, and the
+// host, which sees the id when it reads the chosen tokens, raises.
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ tokens, const T* __restrict__ table, T* __restrict__ out,
-                                 int width) {
+                                 int width, int vocab) {
     fr_pdl_wait();
     fr_pdl_launch();
     const int row = blockIdx.x;
-    copy_row(table + (size_t)tokens[row] * width, out + (size_t)row * width, width);
+    const int token = tokens[row];
+    if (token < 0 || token >= vocab) {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) fr_store(out + (size_t)row * width + i, 0.f);
+        return;
+    }
+    copy_row(table + (size_t)token * width, out + (size_t)row * width, width);
 }
 
-FR_EXPORT int rowwise_embedding(const int* tokens, const void* table, void* out, int n_rows, int width, int dtype,
-                                cudaStream_t stream) {
+FR_EXPORT int rowwise_embedding(const int* tokens, const void* table, void* out, int n_rows, int width, int vocab,
+                                int dtype, cudaStream_t stream) {
     if (n_rows <= 0) return FR_OK;
     if (dtype == FR_F32)
-        embedding_kernel<float><<<n_rows, 256, 0, stream>>>(tokens, (const float*)table, (float*)out, width);
+        embedding_kernel<float><<<n_rows, 256, 0, stream>>>(tokens, (const float*)table, (float*)out, width, vocab);
     else if (dtype == FR_BF16)
         FR_CUDA(fr_launch(embedding_kernel<__nv_bfloat16>, dim3(n_rows), dim3(256), 0, stream, tokens,
-                          (const __nv_bfloat16*)table, (__nv_bfloat16*)out, width));
+                          (const __nv_bfloat16*)table, (__nv_bfloat16*)out, width, vocab));
     else
         FR_REFUSE("embedding: unknown dtype %d", dtype);
     FR_CHECK_LAUNCH("embedding");

@@ -19,7 +19,7 @@ typedef const char* (*last_error_fn)();
 
 struct Rowwise {
     last_error_fn last_error;
-    int (*embedding)(const int*, const void*, void*, int, int, int, cudaStream_t);
+    int (*embedding)(const int*, const void*, void*, int, int, int, int, cudaStream_t);
     int (*gather_rows)(const int*, const void*, void*, int, int, int, cudaStream_t);
     int (*rmsnorm)(const void*, const void*, int, void*, int, int, float, int, cudaStream_t);
     int (*swiglu)(const void*, void*, int, int, int, cudaStream_t);

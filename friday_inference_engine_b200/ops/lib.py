@@ -15,7 +15,7 @@ P, I, F = c_void_p, c_int, c_float
 
 _SIGNATURES = {
     "rowwise": {
-        "rowwise_embedding": [P, P, P, I, I, I, P],
+        "rowwise_embedding": [P, P, P, I, I, I, I, P],
         "rowwise_gather_rows": [P, P, P, I, I, I, P],
         "rowwise_rmsnorm": [P, P, I, P, I, I, F, I, P],
         "rowwise_swiglu": [P, P, I, I, I, P],

@@ -111,7 +111,7 @@ Tensor Ops::embedding(const int* tokens, int64_t n, const Tensor& table, Tensor*
     Timed t(*this, Other);
     Tensor o = out ? *out : alloc(table.dtype, n, table.cols());
     const auto& k = kernels::rowwise();
-    call(launches_, k, k.embedding(tokens, table.data, o.data, (int)n, (int)table.cols(), code(table.dtype), stream_),
+    call(launches_, k, k.embedding(tokens, table.data, o.data, (int)n, (int)table.cols(), (int)table.rows(), code(table.dtype), stream_),
          "embedding");
     return o;
 }

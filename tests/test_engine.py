@@ -226,3 +226,27 @@ def test_refusals(root, where):
     with pytest.raises(StepError):
         eng.step([s, s], [[1], [2]], [[0], [0]])
     eng.free_slot(s)
+
+
+def test_a_kernel_that_gave_up_is_reported_and_the_word_is_cleared(root):
+    """Every bounded wait of a kernel that runs out leaves a code in a status word on the device; Engine.check() raises
+    on it and clears it.  The failure is made on the host: the code is written into the word with a copy, no kernel is
+    made to wait."""
+    try:
+        from cuda.bindings import runtime as cudart
+    except ImportError:
+        from cuda import cudart
+    from friday_inference_engine_b200 import KernelError
+    eng, _ = engine(root, "A", ("cuda:0", "bfloat16"))
+    eng.check()                                              # nothing has happened: no error
+    word = eng.info()["status_word"]
+    code = np.array([7], dtype=np.int32)
+    (err,) = cudart.cudaMemcpy(word, code.ctypes.data, 4, cudart.cudaMemcpyKind.cudaMemcpyHostToDevice)
+    assert int(err) == 0
+    with pytest.raises(KernelError) as e:
+        eng.check()
+    assert "code 7" in str(e.value)
+    eng.check()                                              # cleared: the engine goes on
+    s = eng.alloc_slot()
+    assert eng.step([s], [[1, 2, 3]], [[2]]).shape == (1, eng.vocab_size)
+    eng.free_slot(s)

@@ -39,6 +39,10 @@ def test_embedding_and_gather(dtype):
     toks = torch.tensor([0, 776, 5, 5, 300], dtype=torch.int32, device=DEV)
     assert torch.equal(ops.embedding(toks, table), table[toks.long()])
     assert torch.equal(ops.gather_rows(toks, table), table[toks.long()])
+    # an id outside the table (what a sampler leaves for a row without a finite logit) reads nothing: zeros
+    bad = torch.tensor([3, -1, 777, 2], dtype=torch.int32, device=DEV)
+    got = ops.embedding(bad, table)
+    assert torch.equal(got[[0, 3]], table[[3, 2]]) and float(got[[1, 2]].float().abs().max()) == 0.0
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -375,6 +379,32 @@ def test_attention_mma_one_token_steps(nq, nkv, hd, window, splits):
 def test_attention_mma_long_prompt_sizes_of_the_7b_shape():
     mma_case([(0, 700), (300, 500)], 28, 4, 128, None, False, 1)
     mma_case([(0, 2048), (1000, 1100)], 28, 4, 128, None, False, 1, tcgen05=True)
+
+
+def sampled_columns(n, count, seed):
+    g = torch.Generator().manual_seed(seed)
+    cols = torch.randperm(n, generator=g)[:count].sort().values
+    return torch.cat([torch.tensor([0, 127, 128, n - 129, n - 128, n - 1]), cols]).unique()
+
+
+@pytest.mark.parametrize("m", [1, 8, 64, 130])
+def test_products_at_the_full_width_of_the_head(m):
+    """n = 152,064 columns with k = 3,584: the head's 1,188 weight tiles (eight waves and four tiles of a ninth) on the
+    tensor cores, and the same product in true 32-bit on the CUDA cores, against float64 on 4,096 sampled columns."""
+    n, k = 152064, 3584
+    x, w = rnd((m, k), torch.bfloat16, 200 + m), rnd((n, k), torch.bfloat16, 201, 0.02)
+    cols = sampled_columns(n, 4096, 202).to(DEV)
+    ref = f64(x) @ f64(w[cols]).T
+    out = ops.linear(x, w, out_dtype=torch.float32)
+    assert out.shape == (m, n) and bool(torch.isfinite(out).all())
+    close(out[:, cols], ref, torch.float32, "tensor cores, fp32 logits", fp32_tol=2e-5)      # bf16 inputs are exact
+    out16 = ops.linear(x, w)
+    close(out16[:, cols], ref, torch.bfloat16, "tensor cores, bf16 out")
+    if m <= 8:
+        x32, w32 = x.float(), w.float()
+        out32 = ops.linear(x32, w32)
+        close(out32[:, cols], ref, torch.float32, "CUDA cores, true 32-bit", fp32_tol=2e-5)
+    ops.backend().check_status()
 
 
 class StepGeo:

@@ -147,3 +147,35 @@ def test_wide_layers_decoder_of_many_rows(tmp_path, rows):
                 eng.free_slot(slots[i])
     dec.close()
     eng.check()
+
+
+FULL_VOCABULARY = dict(WIDE, num_hidden_layers=1, vocab_size=152064, tie_word_embeddings=True, intermediate_size=2048)
+
+
+@pytest.fixture(scope="module")
+def full_vocabulary(tmp_path_factory):
+    d = tiny_configs.make_model_dir(str(tmp_path_factory.mktemp("vocab") / "model"), FULL_VOCABULARY, 13)
+    return d, plain_model.PlainModel.from_dir(d)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_full_vocabulary(full_vocabulary, dtype):
+    """One layer of the benchmark's width with its whole vocabulary of 152,064 (the head tied to the token table, so that
+    the plain implementation holds the table once): the widest product of the model inside the engine."""
+    cfg = FULL_VOCABULARY
+    d, pm = full_vocabulary
+    eng = Engine(model_path=d, dtype=dtype, max_ctx=64, max_batch=2)
+    prompts = tiny_configs.random_prompts([12, 5], cfg["vocab_size"], 64)
+    refs = [plain_model.logits(pm, p, at=[len(p) - 2, len(p) - 1]) for p in prompts]
+    slots = [eng.alloc_slot() for _ in prompts]
+    got = harness.to_np(eng.step(slots, [p[:-1] for p in prompts], [[len(p) - 2] for p in prompts]))
+    more = harness.to_np(eng.step(slots, [[p[-1]] for p in prompts], [[0], [0]]))
+    for i in range(2):
+        for rows, ref, what in ((got[i:i + 1], refs[i][0:1], "prompt"), (more[i:i + 1], refs[i][1:2], "next token")):
+            assert rows.shape == (1, 152064)
+            if dtype == "float32":
+                err = float(np.abs(rows - ref).max())
+                assert err <= WIDE_FP32_ABS, "full vocabulary, %s %d: |engine - plain| = %.3g" % (what, i, err)
+            else:
+                harness.check_logits(rows, ref, dtype, "full vocabulary, %s %d" % (what, i), harness.BF16_WIDE)
+    eng.check()
