@@ -53,6 +53,7 @@
 #include "common.cuh"
 #include <atomic>
 #include <mutex>
+#include <unordered_map>
 #include "tc_common.cuh"
 
 FR_EXPORT const char* gemm_tc_last_error() { return fr_error_text; }
@@ -70,7 +71,7 @@ constexpr int SIDE_BYTES = 3 * TILE_P * 4 + 3 * 64 * 4 + 64 * 8;      // row fac
 template <int BN, int STAGES>
 constexpr int smem_bytes() {
     return STAGES * (P_BYTES + BN * TILE_K * 2) + 1024 + (2 * STAGES + 4) * 8 + 64 + SIDE_BYTES +
-           (BN <= 64 ? BN * TILE_P * 4 : BN * 4) + (BN == 16 ? 16 * 64 * 8 : 0);
+           (BN <= 64 ? BN * TILE_P * 4 : BN * 4) + (BN <= 64 ? 16 * 64 * 8 : 0);
 }
 
 struct GemmParams {
@@ -220,7 +221,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     // go through this buffer so that global memory sees 16-byte pieces of whole rows.
     constexpr int T_BYTES = BN <= 64 ? BN * TILE_P * 4 : 0;
     uint8_t* s_tile = (uint8_t*)s_scale + SIDE_BYTES;
-    float2* s_cs = (float2*)(s_tile + T_BYTES);                              // [16][64], 16-wide tiles only
+    float2* s_cs = (float2*)(s_tile + T_BYTES);                              // [16][64]: the rotation's (cos, sin) of the 16 rows being finished
     float* s_gw = (float*)s_tile;                                            // [BN] norm weights of the columns of a tile with rows on M
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
@@ -356,9 +357,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         // [rows of the step][128 columns] floats; then every thread finishes pieces of 8 consecutive columns of one
         // row (bias, residual, rounding, and the fused work) with 16-byte accesses to global memory.
         const bool bf16_out = p.out_dtype == FR_BF16;
-        const bool can_stage = T_BYTES > 0 && p.swapped && !p.act && (p.ldo % 8) == 0 &&
+        const bool can_stage = T_BYTES > 0 && p.swapped && (p.ldo % 8) == 0 &&
                                (((uintptr_t)p.out | (uintptr_t)p.residual) & 15) == 0 && (bf16_out || p.residual == nullptr);
-        const bool rope = f.row_pos != nullptr;            // the launcher grants it to 16-wide tiles only
+        const bool rope = f.row_pos != nullptr;            // the launcher grants it to tiles of up to 64 rows
         float* s_sum = (float*)s_tile;
         constexpr int ITEMS = 2;                           // pieces per thread of 16 rows: 16 * 16 pieces over 128 threads
         uint4 res[ITEMS];                                  // this thread's pieces of the residual rows being finished
@@ -398,7 +399,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 s_crow[et] = crow;
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (rope && f.denom != nullptr) {
+            if (BN == 16 && rope && f.denom != nullptr) {       // wider tiles make them 16 rows at a time, when they finish them
                 const int half = f.rot >> 1;
                 for (int idx = et; idx < nt * half; idx += 128) {
                     const int token = idx / half, i = idx - token * half;
@@ -425,7 +426,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             w.x = pack2(x[0], x[1]); w.y = pack2(x[2], x[3]); w.z = pack2(x[4], x[5]); w.w = pack2(x[6], x[7]);
             return w;
         };
+        // The gated epilogue on a staged tile: the tile's 128 columns are 64 (gate, up) pairs; a thread turns 16 sums of
+        // one row into 8 values silu(gate) * up and stores them as one 16-byte piece (8 pieces per row, 16 rows a time).
+        auto finish_rows_gated = [&](int p_blk, int q_blk, int t_lo, int t_cnt) {
+            if (et >= t_cnt * 8) return;
+            const int token = t_lo + (et >> 3), f0 = (et & 7) * 16;
+            const float* src = s_sum + token * TILE_P + f0;
+            float x[8];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float4 a = *(const float4*)(src + 4 * j);
+                x[2 * j] = silu_mul(a.x, a.y);
+                x[2 * j + 1] = silu_mul(a.z, a.w);
+            }
+            __nv_bfloat16* out_at = (__nv_bfloat16*)p.out + (size_t)(q_blk * bn + token) * p.ldo + ((p_blk * TILE_P + f0) >> 1);
+            *(uint4*)out_at = round8(x);
+        };
         auto finish_rows = [&](int p_blk, int q_blk, int t_lo, int t_cnt) {     // rows t_lo .. t_lo + t_cnt - 1 of the tile
+            if (p.act) {
+                finish_rows_gated(p_blk, q_blk, t_lo, t_cnt);
+                return;
+            }
             const int half = f.rot >> 1;
 #pragma unroll
             for (int k = 0; k < ITEMS; ++k) {
@@ -472,7 +493,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                                     for (int j = 0; j < 8; ++j) {
                                         const float a = __uint_as_float(j & 1 ? lo[j >> 1] & 0xffff0000u : lo[j >> 1] << 16);
                                         const float b = __uint_as_float(j & 1 ? hi[j >> 1] & 0xffff0000u : hi[j >> 1] << 16);
-                                        const float2 cs = s_cs[token * 64 + f_in + j];
+                                        const float2 cs = s_cs[(token - (BN == 16 ? 0 : t_lo)) * 64 + f_in + j];
                                         fr_rotate(a, b, cs.x, cs.y, ra[j], rb[j]);
                                     }
                                     const uint4 wa = round8(ra), wb = round8(rb);
@@ -586,6 +607,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                     put16(c, v);
                     asm volatile("bar.sync 1, 128;" ::: "memory");
                     if (et == 0) mark(p, 11);
+                }
+                if (BN > 16 && rope && f.denom != nullptr) {
+                    // the cosines and sines of these 16 rows (s_seq and s_pos were filled when the tile was taken)
+                    const int half = f.rot >> 1;
+                    for (int idx = et; idx < t_cnt * half; idx += 128) {
+                        const int t = idx / half, i = idx - t * half;
+                        float sn = 0.f, cs = 1.f;
+                        if (s_seq[c * 16 + t] >= 0) sincosf(__fdiv_rn((float)s_pos[c * 16 + t], s_den[i]), &sn, &cs);
+                        s_cs[t * 64 + i] = make_float2(cs, sn);
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
                 }
                 finish_rows(p_blk, q_blk, c * 16, t_cnt);
                 asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -748,7 +780,40 @@ EncodeTiled encode_fn() {
 }
 
 // [rows][k] bf16, row stride ld elements; box = 64 elements of k by box_rows rows.
+// A map depends on (address, shape, stride, box) only, and a model asks for the same few hundred over and over (its
+// weights, and activations at the addresses its working memory repeats): the encoded maps are kept per thread.
+struct MapKey {
+    const void* base;
+    int rows, k, ld, box_rows;
+    bool operator==(const MapKey& o) const { return base == o.base && rows == o.rows && k == o.k && ld == o.ld && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& m) const {
+        size_t h = (size_t)(uintptr_t)m.base * 0x9E3779B97F4A7C15ull;
+        h ^= ((size_t)m.rows << 32 | (unsigned)m.k) * 0xC2B2AE3D27D4EB4Full;
+        h ^= ((size_t)m.ld << 20 | (unsigned)m.box_rows) * 0x165667B19E3779F9ull;
+        return h ^ (h >> 29);
+    }
+};
+
+int encode_map(CUtensorMap* map, const void* base, int rows, int k, int ld, int box_rows);
+
 int make_map(CUtensorMap* map, const void* base, int rows, int k, int ld, int box_rows) {
+    static thread_local std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    const MapKey key{base, rows, k, ld, box_rows};
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *map = it->second;
+        return FR_OK;
+    }
+    const int rc = encode_map(map, base, rows, k, ld, box_rows);
+    if (rc) return rc;
+    if (cache.size() >= 8192) cache.clear();
+    cache.emplace(key, *map);
+    return FR_OK;
+}
+
+int encode_map(CUtensorMap* map, const void* base, int rows, int k, int ld, int box_rows) {
     EncodeTiled enc = encode_fn();
     if (enc == nullptr) FR_REFUSE("gemm_tc: the driver does not offer cuTensorMapEncodeTiled");
     cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
@@ -974,8 +1039,8 @@ FR_EXPORT int gemm_tc_fused(const void* x, const void* w, void* out, int out_dty
                 FR_REFUSE("gemm_tc: fused rotation needs a head size that divides %d and n = (q + 2 kv heads) * head size", TILE_P);
             if (f.denom != nullptr && (f.rot <= 0 || f.rot > f.hd || f.rot % 16))
                 FR_REFUSE("gemm_tc: fused rotation needs a rotary size (%d) that is a multiple of 16, at most the head size %d", f.rot, f.hd);
-            if (bn != 16 || f.norm_out != nullptr || residual != nullptr)
-                FR_REFUSE("gemm_tc: fused rotation needs at most 16 rows and goes without residual or fused norm");
+            if (bn > 64 || f.norm_out != nullptr || residual != nullptr)
+                FR_REFUSE("gemm_tc: fused rotation needs at most 64 rows and goes without residual or fused norm");
             if (f.k_pool != nullptr && (f.v_pool == nullptr || f.table == nullptr || f.page <= 0 ||
                                         (((uintptr_t)f.k_pool | (uintptr_t)f.v_pool) & 15)))
                 FR_REFUSE("gemm_tc: cache write asked for without a whole cache");
@@ -1026,7 +1091,7 @@ FR_EXPORT int gemm_tc_fused(const void* x, const void* w, void* out, int out_dty
         FR_CHECK_LAUNCH("gemm_tc (pairs)");
         return FR_OK;
     }
-    p.shared_finish = swap && splits > 1 && bn >= 32 && bn <= 64 && !act && grid == tiles * splits && grid <= sm_count &&
+    p.shared_finish = swap && splits > 1 && bn >= 32 && bn <= 64 && grid == tiles * splits && grid <= sm_count &&
                       2 * tiles <= n_counters && use_shared_finish();
     CUtensorMap mp, mq;
     int rc = swap ? make_map(&mp, w, n, k, ldw, TILE_P) : make_map(&mp, x, m, k, lda, TILE_P);
@@ -1035,7 +1100,7 @@ FR_EXPORT int gemm_tc_fused(const void* x, const void* w, void* out, int out_dty
     if (rc) return rc;
     switch (bn) {
         case 16: return launch<16, 10>(mp, mq, p, grid, stream);
-        case 32: return launch<32, 10>(mp, mq, p, grid, stream);
+        case 32: return launch<32, 9>(mp, mq, p, grid, stream);
         case 64: return launch<64, 7>(mp, mq, p, grid, stream);
         case 128: return launch<128, 6>(mp, mq, p, grid, stream);
         default: return launch<256, 4>(mp, mq, p, grid, stream);       // any width from 144 to 256
@@ -1072,7 +1137,7 @@ int noalloc_setup(int device) {
     FR_CUDA(cudaGetSymbolAddress(&ptr, noalloc_area));
     FR_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, device));
     FR_CUDA((allow_smem<16, 10>()));
-    FR_CUDA((allow_smem<32, 10>()));
+    FR_CUDA((allow_smem<32, 9>()));
     FR_CUDA((allow_smem<64, 7>()));
     FR_CUDA((allow_smem<128, 6>()));
     FR_CUDA((allow_smem<256, 4>()));

@@ -121,7 +121,7 @@ public:
     // product's epilogue and the second result is deferred; otherwise the norm's kernel runs.
     std::pair<Tensor, Rows> linear_norm(const Rows& x, const Tensor& weight, const Tensor& norm_weight, float eps,
                                         const Tensor* bias = nullptr, const Tensor* residual = nullptr);
-    // linear(x, weight, bias) followed by rope_kv_write on its result; for a few bf16 rows and a head size that
+    // linear(x, weight, bias) followed by rope_kv_write on its result; for up to 64 bf16 rows and a head size that
     // divides 128 both happen in the product's epilogue.
     Tensor qkv_rope_write(const Rows& x, const Tensor& weight, const Tensor* bias, const int* row_seq,
                           const int* row_pos, const float* denominators, int rotary_dim, int n_heads, int n_kv_heads,

@@ -347,7 +347,7 @@ Tensor Ops::qkv_rope_write(const Rows& x, const Tensor& weight, const Tensor* bi
     if (128 % head_dim == 0 && head_dim % 8 == 0 && n == (int64_t)(n_heads + 2 * n_kv_heads) * head_dim &&
         (!denominators || rotary_dim % 16 == 0)) {
         Tensor probe = Tensor::make((void*)16, xt.dtype, {xt.rows(), n});
-        if (few_rows_tile_ok(xt, weight, probe, nullptr, 16) && (!write || view->dtype == DType::BF16)) {
+        if (few_rows_tile_ok(xt, weight, probe, nullptr, 64) && (!write || view->dtype == DType::BF16)) {
             Tensor out = alloc(xt.dtype, xt.rows(), n);
             GemmFusion f;
             memset(&f, 0, sizeof f);

@@ -572,7 +572,9 @@ def denominators(theta, rot):
 
 
 @pytest.mark.parametrize("m,nq,nkv,hd,rot,k", [(1, 4, 2, 32, 32, 64), (8, 28, 4, 128, 128, 3584), (16, 2, 1, 64, 32, 512),
-                                                 (5, 6, 1, 16, 16, 1024), (9, 2, 3, 128, 64, 200)])
+                                                 (5, 6, 1, 16, 16, 1024), (9, 2, 3, 128, 64, 200),
+                                                 (17, 28, 4, 128, 128, 3584), (33, 2, 1, 32, 32, 200), (40, 6, 2, 64, 64, 512),
+                                                 (64, 28, 4, 128, 128, 3584), (64, 4, 2, 16, 16, 96)])
 def test_gemm_with_rotation_and_cache_write_in_its_epilogue(m, nq, nkv, hd, rot, k, monkeypatch):
     """The fused epilogue against the product followed by the rotation kernel: same bits in q, k, v and in the
     cache; against the plain rotation for the values."""
