@@ -379,13 +379,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                                                    (size_t)p_blk * TILE_P + (idx & 15) * 8));
             }
         };
-        auto prefetch_tile = [&](int p_blk, int q_blk) {
+        // r_lo, r_cnt: the rows of the tile whose residual pieces this CTA will need first (16-wide tiles)
+        auto prefetch_tile = [&](int p_blk, int q_blk, int r_lo, int r_cnt) {
             const int nt = min(bn, p.q_rows - q_blk * bn);
             s_bias[et] = p.bias != nullptr ? bias_at(p, p_blk * TILE_P + et) : 0.f;
             if (f.norm_out != nullptr)
                 s_g[et] = f.norm_w_dtype == FR_F32 ? ((const float*)f.norm_w)[p_blk * TILE_P + et]
                                                    : __bfloat162float(((const __nv_bfloat16*)f.norm_w)[p_blk * TILE_P + et]);
-            if (BN == 16) load_res(p_blk, q_blk, 0, nt);       // wider tiles fetch them 16 rows at a time, when they finish them
+            if (BN == 16) load_res(p_blk, q_blk, r_lo, min(r_cnt, nt - r_lo));   // wider tiles fetch them 16 rows at a time, when they finish them
             if (rope && et < nt) {
                 const int row = q_blk * bn + et;
                 const int seq = f.row_seq[row], pos = f.row_pos[row];
@@ -623,6 +624,42 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 asm volatile("bar.sync 1, 128;" ::: "memory");
             }
         };
+        // 16-wide tiles whose k-splits all finish a share of the tile: groups of 4 rows g_begin, g_begin + g_step, ...
+        // (a thread's partial sums of 4 rows of its column are one 16-byte piece of a partial tile)
+        auto finish_quarters = [&](int p_blk, int q_blk, int g_begin, int g_step) {
+            const int nt = min(bn, p.q_rows - q_blk * bn);
+            const float* mine = p.ws + (size_t)i_local * 4;
+            bool first = true;
+#pragma unroll 1
+            for (int g = g_begin; g * 4 < nt; g += g_step) {
+                const int t_cnt = min(4, nt - g * 4);
+                if (!first) load_res(p_blk, q_blk, g * 4, t_cnt);      // the first group's pieces came when the tile was taken
+                first = false;
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int s0 = 0; s0 < item.nseg; s0 += 8) {
+                    float4 x[8];
+#pragma unroll
+                    for (int sp = 0; sp < 8; ++sp)
+                        if (s0 + sp < item.nseg)
+                            x[sp] = __ldcg((const float4*)(mine + (size_t)work.contributor(item, s0 + sp) * TILE_P * bn + (size_t)g * TILE_P * 4));
+#pragma unroll
+                    for (int sp = 0; sp < 8; ++sp)
+                        if (s0 + sp < item.nseg) { v.x += x[sp].x; v.y += x[sp].y; v.z += x[sp].z; v.w += x[sp].w; }
+                }
+                if (et == 0) mark(p, 10);
+                if (f.in_ssq != nullptr) {
+                    v.x *= s_scale[g * 4]; v.y *= s_scale[g * 4 + 1]; v.z *= s_scale[g * 4 + 2]; v.w *= s_scale[g * 4 + 3];
+                }
+                s_sum[(g * 4) * TILE_P + i_local] = v.x;
+                s_sum[(g * 4 + 1) * TILE_P + i_local] = v.y;
+                s_sum[(g * 4 + 2) * TILE_P + i_local] = v.z;
+                s_sum[(g * 4 + 3) * TILE_P + i_local] = v.w;
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (et == 0) mark(p, 11);
+                finish_rows(p_blk, q_blk, g * 4, t_cnt);
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+            }
+        };
         for (; ok && work.next(item); ++it) {
             const int tile = item.tile;
             const int q_blk = tile / p.tiles_p, p_blk = tile - q_blk * p.tiles_p;
@@ -631,7 +668,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             const int gi = p_blk * TILE_P + i_local;
             const bool staged = can_stage && (p_blk + 1) * TILE_P <= p.p_rows;
             load_scale(p.swapped ? q_blk : p_blk);
-            if (staged) prefetch_tile(p_blk, q_blk);
+            const bool quarters = BN == 16 && p.shared_finish && item.nseg > 1;      // this CTA finishes a share of the rows
+            if (staged) prefetch_tile(p_blk, q_blk, quarters ? 4 * (item.part - tile * p.splits) : 0, quarters ? 4 : bn);
             float ss_row = 0.f;                            // rows-on-M with a norm begun: this row's sum of squares over the tile
             if (norm_rows) {
                 asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -695,7 +733,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (flags[0]) {
                     if (et == 0) mark(p, 8);
-                    finish_chunks(p_blk, q_blk, item.part - tile * p.splits, item.nseg, true);
+                    if (BN == 16) finish_quarters(p_blk, q_blk, item.part - tile * p.splits, item.nseg);
+                    else finish_chunks(p_blk, q_blk, item.part - tile * p.splits, item.nseg, true);
                     if (et == 0) mark(p, 12);
                 }
                 // the last CTA to leave the tile makes its counters ready for the next launch
@@ -1091,7 +1130,7 @@ FR_EXPORT int gemm_tc_fused(const void* x, const void* w, void* out, int out_dty
         FR_CHECK_LAUNCH("gemm_tc (pairs)");
         return FR_OK;
     }
-    p.shared_finish = swap && splits > 1 && bn >= 32 && bn <= 64 && grid == tiles * splits && grid <= sm_count &&
+    p.shared_finish = swap && splits > 1 && bn <= 64 && grid == tiles * splits && grid <= sm_count && n % TILE_P == 0 &&
                       2 * tiles <= n_counters && use_shared_finish();
     CUtensorMap mp, mq;
     int rc = swap ? make_map(&mp, w, n, k, ldw, TILE_P) : make_map(&mp, x, m, k, lda, TILE_P);
