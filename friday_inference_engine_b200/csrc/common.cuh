@@ -46,6 +46,18 @@ static thread_local char fr_error_text[512] = "";
 
 #define FR_EXPORT extern "C" __attribute__((visibility("default")))
 
+// SMs of the current device (asked once per device); 0 if the query fails.
+static inline int fr_sm_count() {
+    static int counts[64] = {0};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 0;
+    if (counts[device] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) == cudaSuccess) counts[device] = n;
+    }
+    return counts[device];
+}
+
 __device__ __forceinline__ float fr_load(const float* p) { return *p; }
 __device__ __forceinline__ float fr_load(const __nv_bfloat16* p) { return __bfloat162float(*p); }
 __device__ __forceinline__ void fr_store(float* p, float v) { *p = v; }

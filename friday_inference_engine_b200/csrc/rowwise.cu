@@ -193,7 +193,8 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
 FR_EXPORT int rowwise_swiglu(const void* gu, void* out, int n_rows, int inner, int dtype, cudaStream_t stream) {
     if (n_rows <= 0) return FR_OK;
     const size_t total = (size_t)n_rows * inner;
-    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    const long long cap = (long long)(fr_sm_count() > 0 ? fr_sm_count() : 128) * 16;       // a few waves of the device
+    const int blocks = (int)((long long)((total + 255) / 256) < cap ? (total + 255) / 256 : cap);
     if (dtype == FR_F32)
         swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, inner, total);
     else if (dtype == FR_BF16)
@@ -442,7 +443,8 @@ __global__ void random_normal_kernel(T* out, long long n, unsigned long long key
 FR_EXPORT int rowwise_random_normal(void* out, long long n, int dtype, unsigned long long key, float mean, float std,
                                     cudaStream_t stream) {
     if (n <= 0) return FR_OK;
-    const int blocks = (int)((n + 255) / 256 < 148 * 32 ? (n + 255) / 256 : 148 * 32);
+    const long long cap = (long long)(fr_sm_count() > 0 ? fr_sm_count() : 128) * 32;
+    const int blocks = (int)((n + 255) / 256 < cap ? (n + 255) / 256 : cap);
     if (dtype == FR_F32)
         random_normal_kernel<float><<<blocks, 256, 0, stream>>>((float*)out, n, key, mean, std);
     else if (dtype == FR_BF16)

@@ -1,6 +1,6 @@
 // Device-side building blocks of the tensor-core kernels: mbarrier, TMA, tcgen05 and descriptor helpers,
 // bounded waits, and the epilogue that turns 16 accumulator columns into stored outputs.  Shared by the matrix
-// product (gemm_tc.cu) and the fused decode kernel (decode_layer.cu).
+// product (gemm_tc.cu, gemm_tc_pair.cuh) and the attention kernels that use tcgen05 and TMA.
 #pragma once
 #include <cuda.h>
 
