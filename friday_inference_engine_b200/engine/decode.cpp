@@ -132,6 +132,14 @@ public:
     int bound() const override { return bound_; }
 
     void step(const int* tokens) override {
+        if (!e_.options.profile) return step_now(tokens);
+        const auto t0 = std::chrono::steady_clock::now();       // profile: a decode step counts like a call of the step function
+        step_now(tokens);
+        e_.prof.host_ms += std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+        e_.prof.steps += 1;
+    }
+
+    void step_now(const int* tokens) {
         cuda_check(cudaSetDevice(e_.device), "cudaSetDevice");
         sync_tables();
         int longest = 0;

@@ -108,53 +108,53 @@ float* Ops::scratch_floats(int64_t n) {
 
 // ------------------------------------------------------------------ row-wise
 Tensor Ops::embedding(const int* tokens, int64_t n, const Tensor& table, Tensor* out) {
-    Timed t(*this, Other);
     Tensor o = out ? *out : alloc(table.dtype, n, table.cols());
     const auto& k = kernels::rowwise();
+    Timed t(*this, Other);
     call(launches_, k, k.embedding(tokens, table.data, o.data, (int)n, (int)table.cols(), (int)table.rows(), code(table.dtype), stream_),
          "embedding");
     return o;
 }
 
 Tensor Ops::gather_rows(const int* rows, int64_t n, const Tensor& src) {
-    Timed t(*this, Other);
     if (!src.contiguous()) throw KernelError("gather_rows: the source must be contiguous");
     Tensor o = alloc(src.dtype, n, src.cols());
     const auto& k = kernels::rowwise();
+    Timed t(*this, Other);
     call(launches_, k, k.gather_rows(rows, src.data, o.data, (int)n, (int)src.cols(), code(src.dtype), stream_), "gather_rows");
     return o;
 }
 
 Tensor Ops::rmsnorm(const Tensor& x, const Tensor& weight, float eps, Tensor* out) {
-    Timed t(*this, Other);
     if (!x.contiguous() || weight.numel() != x.cols())
         throw KernelError(format("rmsnorm: rows of %lld columns (contiguous: %d), weight of %lld", (long long)x.cols(),
                                  (int)x.contiguous(), (long long)weight.numel()));
     Tensor o = out ? *out : alloc(x.dtype, x.rows(), x.cols());
     const auto& k = kernels::rowwise();
+    Timed t(*this, Other);
     call(launches_, k, k.rmsnorm(x.data, weight.data, code(weight.dtype), o.data, (int)x.rows(), (int)x.cols(), eps,
                                  code(x.dtype), stream_), "rmsnorm");
     return o;
 }
 
 Tensor Ops::swiglu(const Tensor& gate_up) {
-    Timed t(*this, Other);
     if (!gate_up.contiguous() || gate_up.cols() % 2) throw KernelError("swiglu: rows must be contiguous pairs (gate, up)");
     const int64_t inner = gate_up.cols() / 2;
     Tensor o = alloc(gate_up.dtype, gate_up.rows(), inner);
     const auto& k = kernels::rowwise();
+    Timed t(*this, Other);
     call(launches_, k, k.swiglu(gate_up.data, o.data, (int)gate_up.rows(), (int)inner, code(gate_up.dtype), stream_), "swiglu");
     return o;
 }
 
 void Ops::rope_kv_write(Tensor& qkv, const int* row_seq, const int* row_pos, const float* denominators, int rotary_dim,
                         int n_heads, int n_kv_heads, int head_dim, const CacheView* view) {
-    Timed t(*this, Other);
     if (!qkv.contiguous() || qkv.cols() != (int64_t)(n_heads + 2 * n_kv_heads) * head_dim)
         throw KernelError("rope_kv_write: qkv must be contiguous rows of (heads + 2 kv heads) * head_dim");
     const bool write = view && view->write && view->k_pool;
     if (write && view->dtype != qkv.dtype) throw KernelError("rope_kv_write: the cache's dtype differs from the rows'");
     const auto& k = kernels::rowwise();
+    Timed t(*this, Other);
     call(launches_, k,
          k.rope_kv_write(qkv.data, row_seq, row_pos, denominators, denominators ? rotary_dim : 0, n_heads, n_kv_heads,
                          head_dim, write ? view->k_pool : nullptr, write ? view->v_pool : nullptr,
@@ -164,25 +164,25 @@ void Ops::rope_kv_write(Tensor& qkv, const int* row_seq, const int* row_pos, con
 }
 
 void Ops::advance(int* tokens, const int* sampled, int* row_pos, int* kv_len, const int* row_seq, int* draws, int n) {
-    Timed t(*this, Other);
     const auto& k = kernels::rowwise();
+    Timed t(*this, Other);
     call(launches_, k, k.advance(tokens, sampled, row_pos, kv_len, row_seq, draws, n, stream_), "advance");
 }
 
 void Ops::scale_rows(Tensor& x, float scale) {
     if (scale == 1.0f) return;
-    Timed t(*this, Other);
     if (!x.contiguous()) throw KernelError("scale_rows: rows must be contiguous");
     const auto& k = kernels::rowwise();
+    Timed t(*this, Other);
     call(launches_, k, k.scale_rows(x.data, (long long)x.numel(), scale, code(x.dtype), stream_), "scale_rows");
 }
 
 void Ops::finish_logits(Tensor& logits, const Tensor* bias, float scale, float softcap) {
     if (!bias && scale == 1.0f && softcap <= 0.f) return;
-    Timed t(*this, Other);
     if (logits.dtype != DType::F32) throw KernelError("finish_logits: logits are float32");
     if (bias && bias->numel() != logits.cols()) throw KernelError("finish_logits: the bias does not match the vocabulary");
     const auto& k = kernels::rowwise();
+    Timed t(*this, Other);
     call(launches_, k, k.finish_logits((float*)logits.data, (int)logits.rows(), (int)logits.cols(), (int)logits.ld,
                                        bias ? bias->data : nullptr, bias ? code(bias->dtype) : 0, scale, softcap, stream_),
          "finish_logits");
@@ -234,8 +234,8 @@ static void check_residual(const Tensor* residual, const Tensor& out) {
 
 Tensor Ops::linear_tc(const Tensor& x, const Tensor& weight, const Tensor* bias, const Tensor* residual, Tensor& out,
                       int swap, int bn, int splits, int act, GemmFusion* fusion) {
-    Timed t(*this, Product);
     const auto& g = kernels::gemm_tc();
+    Timed t(*this, Product);
     GemmFusion traced;
     if (trace_ && trace_next_ < trace_left_) {
         if (fusion) traced = *fusion;
@@ -254,8 +254,8 @@ Tensor Ops::linear_tc(const Tensor& x, const Tensor& weight, const Tensor* bias,
 }
 
 Tensor Ops::linear_simt(const Tensor& x, const Tensor& weight, const Tensor* bias, const Tensor* residual, Tensor& out) {
-    Timed t(*this, Product);
     const auto& g = kernels::gemm_simt();
+    Timed t(*this, Product);
     call(launches_, g,
          g.gemm(x.data, code(x.dtype), weight.data, code(weight.dtype), out.data, code(out.dtype),
                 bias ? bias->data : nullptr, bias ? code(bias->dtype) : 0, residual ? residual->data : nullptr,
@@ -423,7 +423,6 @@ int Ops::decode_splits(int n_seqs, int n_heads, int n_kv_heads, int head_dim, in
 
 void Ops::attention(const Tensor& q, int64_t q_stride, Tensor& out, const CacheView& view, const StepContext& ctx,
                     int n_heads, int n_kv_heads, int head_dim, int window, float scale) {
-    Timed t(*this, Attention);
     if (view.kind != CacheRequest::KV || !view.k_pool) throw KernelError("attention needs a view of keys and values");
     const bool geometry = ctx.seq_start != nullptr;
     const bool hd_ok = head_dim % 16 == 0 && head_dim >= 16 && head_dim <= 128 && view.page_size == 64;
@@ -431,6 +430,7 @@ void Ops::attention(const Tensor& q, int64_t q_stride, Tensor& out, const CacheV
     if (out.dtype == DType::BF16 && geometry && !ctx.decode && attn_tc_ && hd_ok && n_kv_heads > 0 &&
         n_heads % n_kv_heads == 0 && n_heads / n_kv_heads <= 128 && q_stride % 8 == 0) {
         const auto& k = kernels::attention_tc();
+        Timed t(*this, Attention);
         call(launches_, k,
              k.run(q.data, (int)q_stride, (int)q.rows(), out.data, view.k_pool, view.v_pool, view.pool_pages,
                    view.block_table, view.table_width, ctx.seq_start, ctx.seq_qlen, ctx.seq_pos0, ctx.row_seq, ctx.n_seqs,
@@ -443,6 +443,7 @@ void Ops::attention(const Tensor& q, int64_t q_stride, Tensor& out, const CacheV
         const int splits = keys_mode ? decode_splits(ctx.n_seqs, n_heads, n_kv_heads, head_dim, ctx.max_kv_len) : 1;
         float* scratch = splits > 1 ? scratch_floats((int64_t)rows * n_heads * splits * (head_dim + 2)) : nullptr;
         const auto& k = kernels::attention_mma();
+        Timed t(*this, Attention);
         call(launches_, k,
              k.run(q.data, (int)q_stride, out.data, view.k_pool, view.v_pool, view.pool_pages, view.block_table,
                    view.table_width, 64, ctx.seq_start, ctx.seq_qlen, ctx.seq_pos0, ctx.row_seq, ctx.n_seqs, rows,
@@ -454,6 +455,7 @@ void Ops::attention(const Tensor& q, int64_t q_stride, Tensor& out, const CacheV
     const int splits = attention_splits(rows, n_heads, ctx.max_kv_len);
     float* scratch = splits > 1 ? scratch_floats((int64_t)rows * n_heads * splits * (head_dim + 2)) : nullptr;
     const auto& k = kernels::attention_simt();
+    Timed t(*this, Attention);
     call(launches_, k,
          k.run(q.data, (int)q_stride, out.data, view.k_pool, view.v_pool, view.block_table, view.table_width,
                view.page_size, ctx.row_seq, ctx.row_pos, rows, n_heads, n_kv_heads, head_dim, window, scale, splits,
@@ -464,9 +466,9 @@ void Ops::attention(const Tensor& q, int64_t q_stride, Tensor& out, const CacheV
 // ------------------------------------------------------------------ sampling
 void Ops::sample(const Tensor& logits, const float* temperature, const int* streams, const int* steps,
                  unsigned long long seed, const int* row_live, int* out) {
-    Timed t(*this, Other);
     if (logits.dtype != DType::F32) throw KernelError("sample: logits are float32");
     const auto& k = kernels::sampling();
+    Timed t(*this, Other);
     call(launches_, k,
          k.sample((const float*)logits.data, (int)logits.rows(), (int)logits.cols(), (int)logits.ld, temperature, streams,
                   steps, seed, row_live, out, stream_),
