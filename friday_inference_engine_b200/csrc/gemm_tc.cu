@@ -878,6 +878,16 @@ bool use_stream_k() {
     return v != 0;
 }
 
+// FRIDAY_GEMM_EVEN_RUNS=0: products of few rows always run whole tiles times an equal split of k.
+bool use_even_runs() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("FRIDAY_GEMM_EVEN_RUNS");
+        v = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return v != 0;
+}
+
 // FRIDAY_GEMM_PAIR=0: products of many rows run on single SMs (128 x bn tiles) instead of pairs (256 x bn).
 bool use_pair() {
     static int v = -1;
@@ -1042,9 +1052,27 @@ FR_EXPORT int gemm_tc_fused(const void* x, const void* w, void* out, int out_dty
     if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) FR_REFUSE("gemm_tc: operands must be 16-byte aligned");
     if (status == nullptr) FR_REFUSE("gemm_tc: a status word is needed");
     long long plan[5];
+    const bool splits_free = splits < 0;
     gemm_tc_plan(m, n, k, sm_count, swap, bn, splits, plan);
     swap = (int)plan[0]; bn = (int)plan[1]; splits = (int)plan[2];
     if (bn != 16 && bn != 32 && bn != 64 && !(bn >= 128 && bn <= 256 && bn % 16 == 0)) FR_REFUSE("gemm_tc: tile width %d", bn);
+    // Few rows stream the weights once, and an SM draws only so much (about 45 GB/s on a B200): the product is as fast as
+    // its share of busy SMs.  Several waves of whole tiles can leave most SMs idle in the last one (the head's 1,188 tiles
+    // on 148 SMs: a ninth wave of four); where that costs more than a tenth, the k blocks of all tiles are laid end to end
+    // and cut into equal runs, one per SM, whatever tiles a run touches (its first and last tile are partial tiles that
+    // the last CTA to arrive sums).  Measured at 7B and 14B sizes: the head 247 -> 236 us; products of one wave gain
+    // nothing from it (the shared finish of their equal splits is worth as much as the idle SMs), so they keep those.
+    bool even_runs = false;
+    if (splits_free && swap && use_even_runs()) {
+        const long long tiles_now = (long long)((n + TILE_P - 1) / TILE_P) * ((m + bn - 1) / bn);
+        const long long items = tiles_now * splits, waves = (items + sm_count - 1) / sm_count;
+        const long long kb_all = tiles_now * ((k + TILE_K - 1) / TILE_K);
+        if (waves > 1 && items * 10 < waves * sm_count * 9 && kb_all >= 4LL * sm_count && 2LL * sm_count * TILE_P * bn <= scratch_floats &&
+            tiles_now <= n_counters) {
+            even_runs = true;
+            splits = 1;
+        }
+    }
     if (plan[3] > scratch_floats || plan[4] > n_counters)
         FR_REFUSE("gemm_tc: split-k needs %lld scratch floats and %lld counters, given %lld and %d", plan[3], plan[4],
                   scratch_floats, n_counters);
@@ -1097,7 +1125,12 @@ FR_EXPORT int gemm_tc_fused(const void* x, const void* w, void* out, int out_dty
     const int tiles = p.tiles_p * p.tiles_q;
     p.dp_tiles = tiles; p.sk_tiles = 0; p.sk_units = 1;
     int grid = tiles * splits < sm_count ? tiles * splits : sm_count;
-    if (!swap && splits == 1 && tiles > sm_count && use_stream_k()) {
+    if (even_runs) {
+        p.dp_tiles = 0;
+        p.sk_tiles = tiles;
+        p.sk_units = (int)(((long long)tiles * p.kb_total + sm_count - 1) / sm_count);
+        grid = (int)(((long long)tiles * p.kb_total + p.sk_units - 1) / p.sk_units);
+    } else if (!swap && splits == 1 && tiles > sm_count && use_stream_k()) {
         const int rem = tiles % sm_count;
         if (rem != 0 && rem * 100 < sm_count * 85 && p.kb_total >= 4 && 2LL * sm_count * TILE_P * bn <= scratch_floats &&
             tiles <= n_counters) {
