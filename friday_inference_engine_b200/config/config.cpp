@@ -112,7 +112,7 @@ std::vector<std::string> registered_architectures() {
     return names;
 }
 
-const Architecture& architecture(const std::string& name) {
+Architecture architecture(const std::string& name) {
     std::lock_guard<std::mutex> lock(registry_mutex());
     auto it = registry().find(name);
     if (it == registry().end()) {

@@ -203,7 +203,7 @@ FR_API const char* friday_loaded_libraries(void) { return hand_back(kernels::loa
 FR_API int friday_read_config(const char* config_json, const char** typed_json) {
     GUARD({
         const Json cfg = parse_arg(config_json, "config.json");
-        const Architecture& arch = architecture(architecture_name_of(cfg));
+        const Architecture arch = architecture(architecture_name_of(cfg));
         *typed_json = hand_back(arch.read_config(cfg).dump());
     })
 }
@@ -220,7 +220,7 @@ FR_API int friday_registered(const char* what, const char** json_list) {
 FR_API int friday_describe_model(const char* config_json, const char** json) {
     GUARD({
         const Json cfg = parse_arg(config_json, "config.json");
-        const Architecture& arch = architecture(architecture_name_of(cfg));
+        const Architecture arch = architecture(architecture_name_of(cfg));
         const Json typed = arch.read_config(cfg);
         ModelSpec spec = arch.build_spec(typed);
         DecoderModel model(spec, DType::BF16);
@@ -270,7 +270,7 @@ FR_API int friday_write_random_model(const char* dir, const char* config_json, u
 FR_API int friday_check_weights(const char* model_dir) {
     GUARD({
         const Json cfg = read_config_file(model_dir);
-        const Architecture& arch = architecture(architecture_name_of(cfg));
+        const Architecture arch = architecture(architecture_name_of(cfg));
         ModelSpec spec = arch.build_spec(arch.read_config(cfg));
         DecoderModel model(spec, DType::BF16);
         std::unique_ptr<WeightSource> src = open_model_weights(model_dir);
@@ -285,7 +285,7 @@ FR_API int friday_check_weights(const char* model_dir) {
 FR_API int friday_storage_plan(const char* model_dir, const char* dtype, const char** json) {
     GUARD({
         const Json cfg = read_config_file(model_dir);
-        const Architecture& arch = architecture(architecture_name_of(cfg));
+        const Architecture arch = architecture(architecture_name_of(cfg));
         DecoderModel model(arch.build_spec(arch.read_config(cfg)), parse_dtype(dtype));
         std::unique_ptr<WeightSource> src = open_model_weights(model_dir);
         Json out = Json::array();

@@ -4,6 +4,7 @@
 
 #include <algorithm>
 #include <numeric>
+#include <set>
 
 #include "engine/engine_impl.h"
 #include "friday/sampling.h"
@@ -233,7 +234,7 @@ Engine::Engine(const EngineOptions& opt) : impl_(new Impl) {
             throw ConfigError(std::string("config_json: not JSON: ") + x.what());
         }
     }
-    const Architecture& arch = friday::architecture(architecture_name_of(cfg));
+    const Architecture arch = friday::architecture(architecture_name_of(cfg));
     e.arch_name = arch.name;
     e.typed_config = arch.read_config(cfg);
     ModelSpec spec = arch.build_spec(e.typed_config);

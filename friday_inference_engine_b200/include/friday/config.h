@@ -52,7 +52,7 @@ struct Architecture {
 };
 
 void register_architecture(const Architecture& arch);
-const Architecture& architecture(const std::string& name);           // ConfigError listing the known names
+Architecture architecture(const std::string& name);                  // ConfigError listing the known names
 std::vector<std::string> registered_architectures();
 std::string architecture_name_of(const Json& config_json);           // architectures[0]
 

@@ -133,7 +133,7 @@ std::unique_ptr<WeightSource> random_weights(const std::vector<Part::Named>& exp
 
 void write_random_model(const std::string& dir, const Json& config_json, uint64_t seed, const std::string& dtype, int shards) {
     if (dtype != "BF16" && dtype != "F32") throw WeightsError("model folders are written as BF16 or F32, not " + dtype);
-    const Architecture& arch = architecture(architecture_name_of(config_json));
+    const Architecture arch = architecture(architecture_name_of(config_json));
     const Json typed = arch.read_config(config_json);
     DecoderModel model(arch.build_spec(typed), DType::BF16);
     if (mkdir(dir.c_str(), 0777) != 0 && errno != EEXIST) throw WeightsError(dir + ": cannot create: " + strerror(errno));
