@@ -201,6 +201,37 @@ def test_generation_through_the_entry_point(root, where, name, temperature):
             seq.append(tok)
 
 
+@pytest.mark.parametrize("name", ["C", "B"])
+def test_many_batches_of_random_shape(root, name):
+    """Generation calls of random numbers of requests, lengths and budgets, one after another on one engine: batches of
+    every size up to the engine's, kept decoders armed again and again, slots and pages used again, stop tokens.  In
+    32-bit every chosen token must be the plain implementation's choice."""
+    import random
+    eng, pm = engine(root, name, ("cuda:0", "float32"), max_batch=3, max_ctx=200)
+    rnd = random.Random(5)
+    for call in range(10):
+        lens = [rnd.choice([1, 2, 5, 31, 63, 64, 65, 100, 140]) for _ in range(rnd.randint(1, 7))]
+        prompts = tiny_configs.random_prompts(lens, eng.vocab_size, 100 + call)
+        budget = rnd.randint(1, 24)
+        free = eng.generate(prompts, max_new_tokens=budget)
+        stop = rnd.choice(free[0].tokens)
+        out = eng.generate(prompts, max_new_tokens=budget, stop_token_ids=[stop]) if call % 2 else free
+        for i, (p, g) in enumerate(zip(prompts, out)):
+            seq = list(p)
+            ref = plain_model.logits(pm, p + g.tokens + [0], at=list(range(len(p) - 1, len(p) + len(g.tokens))))
+            for k, tok in enumerate(g.tokens):
+                assert tok == plain_model.greedy(ref[k]), "call %d request %d token %d" % (call, i, k)
+                seq.append(tok)
+            if g.finish_reason == "stop":
+                assert plain_model.greedy(ref[len(g.tokens)]) == stop and stop not in g.tokens
+            elif g.finish_reason == "length":
+                assert len(g.tokens) == budget
+            else:
+                assert g.finish_reason == "context" and len(p) + len(g.tokens) - 1 >= 200
+        assert nothing_held(eng)
+    eng.check()
+
+
 def test_stop_tokens_end_sequences_early(root, where):
     eng, pm = engine(root, "A", where, max_batch=3, max_ctx=128)
     prompts = tiny_configs.random_prompts([5, 11, 17], eng.vocab_size, 17)
