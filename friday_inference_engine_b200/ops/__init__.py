@@ -101,7 +101,7 @@ class CudaOps:
         native.call("friday_ops_new", int(device), None, byref(self._h))
 
     def __del__(self):
-        if getattr(self, "_h", None) and native._lib is not None:
+        if getattr(self, "_h", None) and native is not None and native._lib is not None:      # None at interpreter exit
             native._lib.friday_ops_free(self._h)
             self._h = None
 
