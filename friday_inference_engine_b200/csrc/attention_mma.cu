@@ -570,6 +570,7 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
         } else if (p.splits > 1 && p.counters != nullptr) {
             // Whoever writes a tile's last partial merges them: no second kernel, the partials are still in L2.
             __shared__ int s_last;
+            mark(p, 5);
             __threadfence();
             __syncthreads();
             if (tid == 0) {
@@ -579,45 +580,115 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
             }
             __syncthreads();
             if (s_last) {
+                mark(p, 6);
                 __threadfence();
-                const bool valid = rr < n_rows;
-                const int t = valid ? rr / G : 0, h = kvh * G + (valid ? rr - t * G : 0);
-                const size_t item = (size_t)(q_start + t) * p.nq + h;
-                const float* base = p.part + item * p.splits * (HD + 2);
-                float* weight = c_o;                  // [16][splits]: exp(m_s - M), free again after the syncs above
-                float big = -INFINITY;
-                if (valid)
-                    for (int sp = tid & 7; sp < p.splits; sp += 8) big = fmaxf(big, __ldcg(base + (size_t)sp * (HD + 2) + HD));
-#pragma unroll
-                for (int o2 = 1; o2 < 8; o2 <<= 1) big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, o2));
-                float l = 0.f;
-                if (valid)
-                    for (int sp = tid & 7; sp < p.splits; sp += 8) {
-                        const float ls = __ldcg(base + (size_t)sp * (HD + 2) + HD + 1);
-                        const float f = ls > 0.f ? expf(__ldcg(base + (size_t)sp * (HD + 2) + HD) - big) : 0.f;
-                        weight[r * p.splits + sp] = f;
-                        l += ls * f;
-                    }
-#pragma unroll
-                for (int o2 = 1; o2 < 8; o2 <<= 1) l += __shfl_xor_sync(0xffffffffu, l, o2);
-                __syncwarp();                         // a row's eight threads sit in one warp
-                if (valid) {
-                    constexpr int PER = HD / 8;           // consecutive dims per thread
-                    const int d0 = (tid & 7) * PER;
-                    float acc[PER];
-#pragma unroll
-                    for (int i = 0; i < PER; ++i) acc[i] = 0.f;
-#pragma unroll 4
-                    for (int sp = 0; sp < p.splits; ++sp) {
-                        const float* ps = base + (size_t)sp * (HD + 2) + d0;
-                        const float f = weight[r * p.splits + sp];
-#pragma unroll
-                        for (int i = 0; i < PER; ++i) acc[i] += __ldcg(ps + i) * f;
-                    }
-                    const float inv = l > 0.f ? 1.f / l : 0.f;
-#pragma unroll
-                    for (int i = 0; i < PER; ++i) p.out[item * HD + d0 + i] = __float2bfloat16_rn(acc[i] * inv);
+                // All splits' partial rows are in L2.  A trip there takes as long for one load as for dozens, so each
+                // phase asks for everything it needs at once: first every split's maximum and sum, then the rows
+                // themselves, the splits dealt out over the warps and a row's dimensions over a warp's lanes.
+                const int S = p.splits;                             // at most 64 on this path
+                const int n_here = min(16, n_rows - r0);
+                float* red = c_o;                                   // [WARPS][16][HD]: each warp's share of the sums
+                float* s_w = red + WARPS * 16 * HD;                 // [16][64]: a split's maximum, then its weight exp(m - M)
+                float* s_ls = s_w + 16 * 64;                        // [16][64]: a split's sum
+                float* s_inv = s_ls + 16 * 64;                      // [16]: one over a row's sum
+                auto part_of = [&](int r2) -> const float* {
+                    const int rr2 = r0 + r2, t2 = rr2 / G, h2 = kvh * G + (rr2 - t2 * G);
+                    return p.part + ((size_t)(q_start + t2) * p.nq + h2) * S * (HD + 2);
+                };
+                for (int idx = tid; idx < n_here * S; idx += blockDim.x) {
+                    const int r2 = idx / S, sp = idx - r2 * S;
+                    const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_of(r2) + (size_t)sp * (HD + 2) + HD));
+                    s_w[r2 * 64 + sp] = ml.x;
+                    s_ls[r2 * 64 + sp] = ml.y;
                 }
+                __syncthreads();
+                {
+                    const bool valid = r < n_here;                  // 8 threads per row; the copying warp has none
+                    float big = -INFINITY;
+                    if (valid)
+                        for (int sp = tid & 7; sp < S; sp += 8) big = fmaxf(big, s_w[r * 64 + sp]);
+#pragma unroll
+                    for (int o2 = 1; o2 < 8; o2 <<= 1) big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, o2));
+                    float l = 0.f;
+                    if (valid)
+                        for (int sp = tid & 7; sp < S; sp += 8) {
+                            const float ls = s_ls[r * 64 + sp];
+                            const float f = ls > 0.f ? expf(s_w[r * 64 + sp] - big) : 0.f;
+                            s_w[r * 64 + sp] = f;
+                            l += ls * f;
+                        }
+#pragma unroll
+                    for (int o2 = 1; o2 < 8; o2 <<= 1) l += __shfl_xor_sync(0xffffffffu, l, o2);
+                    if (valid && (tid & 7) == 0) s_inv[r] = l > 0.f ? 1.f / l : 0.f;
+                }
+                __syncthreads();
+                constexpr int MPIECES = HD / 2;                      // float2 pieces of a row
+                constexpr int PP = (MPIECES + 31) / 32;              // pieces per lane
+                if (warp < WARPS) {
+#pragma unroll 1
+                    for (int half = 0; half < 16; half += 8) {
+                        float2 acc[8][PP];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+#pragma unroll
+                            for (int j = 0; j < PP; ++j) acc[i][j] = make_float2(0.f, 0.f);
+                        if (half < n_here) {
+                            // Straight-line code, so that all loads of a pass are on their way before the first is
+                            // used: rows beyond the tile's last read that row again and count for nothing.
+                            const float* bases[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const bool in = half + i < n_here;
+                                bases[i] = part_of(in ? half + i : n_here - 1);
+                            }
+#pragma unroll 2
+                            for (int sp = warp; sp < S; sp += WARPS) {
+                                float2 v[8][PP];
+#pragma unroll
+                                for (int i = 0; i < 8; ++i)
+#pragma unroll
+                                    for (int j = 0; j < PP; ++j) {
+                                        const int piece = lane + 32 * j;
+                                        v[i][j] = piece < MPIECES
+                                                      ? __ldcg(reinterpret_cast<const float2*>(bases[i] + (size_t)sp * (HD + 2)) + piece)
+                                                      : make_float2(0.f, 0.f);
+                                    }
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) {
+                                    const float f = half + i < n_here ? s_w[(half + i) * 64 + sp] : 0.f;
+#pragma unroll
+                                    for (int j = 0; j < PP; ++j) {
+                                        acc[i][j].x += v[i][j].x * f;
+                                        acc[i][j].y += v[i][j].y * f;
+                                    }
+                                }
+                            }
+                        }
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+#pragma unroll
+                            for (int j = 0; j < PP; ++j) {
+                                const int piece = lane + 32 * j;
+                                if (piece < MPIECES) *reinterpret_cast<float2*>(red + (warp * 16 + half + i) * HD + 2 * piece) = acc[i][j];
+                            }
+                    }
+                }
+                __syncthreads();
+                for (int idx = tid; idx < n_here * MPIECES; idx += blockDim.x) {
+                    const int r2 = idx / MPIECES, piece = idx - r2 * MPIECES;
+                    float2 a = make_float2(0.f, 0.f);
+#pragma unroll
+                    for (int w = 0; w < WARPS; ++w) {
+                        const float2 v = *reinterpret_cast<const float2*>(red + (w * 16 + r2) * HD + 2 * piece);
+                        a.x += v.x;
+                        a.y += v.y;
+                    }
+                    const float inv = s_inv[r2];
+                    const int rr2 = r0 + r2, t2 = rr2 / G, h2 = kvh * G + (rr2 - t2 * G);
+                    *reinterpret_cast<uint32_t*>(p.out + ((size_t)(q_start + t2) * p.nq + h2) * HD + 2 * piece) =
+                        pack_bf16(a.x * inv, a.y * inv);
+                }
+                mark(p, 7);
             }
         }
     }

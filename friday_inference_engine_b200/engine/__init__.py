@@ -124,7 +124,7 @@ class Engine:
         self._stream = info["stream"]
 
     def __del__(self):
-        if getattr(self, "_h", None) and native._lib is not None:
+        if getattr(self, "_h", None) and native is not None and native._lib is not None:
             native._lib.friday_engine_free(self._h)
             self._h = None
 

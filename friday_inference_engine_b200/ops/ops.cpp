@@ -401,24 +401,72 @@ int Ops::attention_splits(int64_t rows, int n_heads, int max_kv_len) const {
     return (int)(s < 1 ? 1 : s);
 }
 
+// FRIDAY_ATTN_WIDE=0: the CTAs that share a sequence's keys in a one-token step always form one thread-block cluster.
+static bool wide_splits() {
+    const char* e = getenv("FRIDAY_ATTN_WIDE");
+    return e == nullptr || e[0] != '0';
+}
+
 int Ops::decode_splits(int n_seqs, int n_heads, int n_kv_heads, int head_dim, int max_kv_len) {
-    // CTAs that share one sequence's keys in a one-token step: as many as leave every CTA at least two blocks of
-    // keys, up to the 8 of a thread-block cluster, as long as all clusters run at once (a second wave would cost a
-    // whole CTA's set-up and merge again).  The device says how many clusters of a size it holds when it is empty;
-    // SMs that the kernel before frees one by one are packed less well (measured on a B200: 32 clusters of 8 ran in
-    // two waves although 33 fit), hence the margin of one half.
+    // How many CTAs share one sequence's keys in a one-token step: the number with the shortest estimated time.
+    // Up to 8 they form a thread-block cluster and merge through each other's shared memory; 9 to 64 leave partial
+    // rows in memory and the last to finish merges them.  The estimate, in us, fitted to one-token steps of 1 to 32
+    // sequences with 2,000 to 32,000 keys on a B200 (28 query heads on 4 kv heads of 128):
+    //  - a CTA streams a block of 64 keys in 0.84 us while it has its SM to itself; the more SMs hold two CTAs, the
+    //    slower each gets (1.13 us when 108 of 148 SMs hold two);
+    //  - the device says how many clusters of a size it holds when empty; SMs that the kernel before frees one by
+    //    one are packed less well, the worse the larger the cluster (32 clusters of 8 ran in two waves although 33
+    //    fit, 32 of 7 were slower than 32 of 6 although 37 fit), so 2 % less per CTA of a cluster count as one wave,
+    //    and every wave costs its CTAs' set-up and the merge again (2.5 us and 0.15 us per CTA of a cluster; through
+    //    memory 5 us and 0.2 us per CTA).
     const int group = n_heads / n_kv_heads;
     const long long base = (long long)n_seqs * n_kv_heads * ((group + 15) / 16);
+    if (base < 1) return 1;
+    if (const char* e = getenv("FRIDAY_ATTN_SPLITS")) {              // for measurements: this many, whatever the shape
+        const int v = atoi(e);
+        if (v >= 1 && v <= 64) return v;
+    }
     const int blocks = (max_kv_len + 63) / 64;
-    int top = blocks / 2 < 1 ? 1 : blocks / 2;
+    int top = blocks / 2 < 1 ? 1 : blocks / 2;                      // every CTA keeps at least two blocks
     if (top > 8) top = 8;
-    for (int size = top; size > 1; --size) {
+    auto fit_of = [&](int size) {
         auto key = std::make_pair(head_dim, size);
         auto it = cluster_fit_.find(key);
         if (it == cluster_fit_.end()) it = cluster_fit_.emplace(key, kernels::attention_mma().clusters_at_once(head_dim, size)).first;
-        if (2LL * it->second >= 3LL * base) return size;
+        return (long long)((1.0 - 0.02 * size) * it->second);
+    };
+    auto per_block = [&](double resident) {
+        const double second = resident > sms_ ? resident - sms_ : 0.0;
+        return 0.84 * (1.0 + 0.47 * second / sms_);
+    };
+    double best = 1e30;
+    int pick = 1;
+    for (int size = 1; size <= top; ++size) {
+        const long long fit = fit_of(size);
+        if (fit < 1) continue;
+        const int per = (blocks + size - 1) / size;
+        double t = 0.0;
+        for (long long left = base; left > 0;) {
+            const long long now = left < fit ? left : fit;
+            t += per * per_block((double)now * size) + 2.5 + 0.15 * size;
+            left -= now;
+        }
+        if (t < best) {
+            best = t;
+            pick = size;
+        }
     }
-    return 1;
+    if (wide_splits()) {
+        const long long at_once = fit_of(1);
+        for (int wide = 9; wide <= 64 && wide <= blocks / 3 && base * wide <= at_once; ++wide) {
+            const double t = (blocks + wide - 1) / wide * per_block((double)base * wide) + 5.0 + 0.2 * wide;
+            if (t < best) {
+                best = t;
+                pick = wide;
+            }
+        }
+    }
+    return pick;
 }
 
 void Ops::attention(const Tensor& q, int64_t q_stride, Tensor& out, const CacheView& view, const StepContext& ctx,

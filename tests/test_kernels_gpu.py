@@ -371,7 +371,10 @@ def test_attention_tcgen05_prompts_of_unequal_lengths(nq, nkv, hd, window):
 
 @pytest.mark.parametrize("nq,nkv,hd,window,splits", [
     (4, 2, 16, None, 1), (3, 1, 32, 24, 2), (28, 4, 128, None, 5), (28, 4, 128, None, 1), (6, 2, 48, 80, 3),
-    (8, 1, 112, 64, 4), (40, 8, 128, None, 7), (32, 1, 64, None, 2), (5, 5, 80, 130, 16)])
+    (8, 1, 112, 64, 4), (40, 8, 128, None, 7), (32, 1, 64, None, 2), (5, 5, 80, 130, 16),
+    # more than 8: partial rows through memory, merged by the last CTA (12 and 16 rows per tile, head sizes whose rows do
+    # not fill a warp's lanes evenly, more splits than a short sequence has blocks)
+    (24, 2, 96, None, 37), (28, 4, 128, None, 64), (16, 1, 48, 200, 23), (6, 3, 16, None, 9)])
 def test_attention_mma_one_token_steps(nq, nkv, hd, window, splits):
     mma_case([(0, 1), (63, 1), (64, 1), (65, 1), (299, 1), (1000, 1), (127, 1)], nq, nkv, hd, window, True, splits)
 
@@ -484,6 +487,14 @@ def test_one_token_steps_over_long_contexts(nq, nkv, longest):
     """Page tables of 64 and 128 entries and as many splits as the engine picks for the longest sequence."""
     geo = long_case([(longest - 1, 1), (longest // 2 + 5, 1), (99, 1)], nq, nkv, 128, None)
     assert ops.backend().decode_splits(3, nq, nkv, 128, geo.max_kv_len) >= 4       # really split, as the engine would
+
+
+@pytest.mark.parametrize("seqs", [[(16383, 1)], [(20000, 1), (700, 1)]])
+def test_one_token_steps_of_few_sequences_over_very_long_contexts(seqs):
+    """Few sequences with many keys: more CTAs share a sequence than a cluster holds, and the last one merges their
+    partial rows through memory."""
+    geo = long_case(seqs, 28, 4, 128, None)
+    assert ops.backend().decode_splits(len(seqs), 28, 4, 128, geo.max_kv_len) > 8
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
