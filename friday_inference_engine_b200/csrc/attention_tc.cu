@@ -67,6 +67,7 @@ struct TcArgs {
     int* status;
     int table_width, nq, nkv, hd, window, pool_rows, n_seqs;
     float scale_log2;         // softmax scale times log2(e)
+    int debug;
     unsigned long long* trace;   // for measurements (may be null): [cta][8] sums of time (ns) that row 0's thread spent
                                  // waiting for S, reading it, writing P, rescaling O, waiting for the last product;
                                  // then blocks, total time, start
@@ -219,7 +220,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
     // Block i of the CTA uses stage i & 1 of K, V and S; its barriers are in their (i >> 1)-th use.
     if (warp == 0) {
-        if (lane == 0) {
+        if (elect_one()) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
@@ -255,7 +256,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
+        if (elect_one()) {
             const uint32_t idesc_qk = instr_desc(ROWS, KEYS);
             const uint32_t idesc_pv = instr_desc(ROWS, p.hd) | (1u << 16);   // B is MN-major
             const int k_steps = p.hd / 16;                                   // of the first product
@@ -345,8 +346,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             // unmasked blocks have code of their own; most blocks need no mask (the choice must be the same for a whole
             // warp: loads from and stores to tensor memory are warp-wide instructions).
             const uint32_t s_addr = tmem_s + b * KEYS + lane_addr;
+            // (Rows of the tile that stand for no token ask for no mask: what they compute stays in their own lanes of
+            // tensor memory and is never written.  With them in the condition the warp of the tile's last rows, two of
+            // which are such rows when 7 heads share a kv head, took the masked form in every block, 2.5 times as long
+            // as the others.)
             const bool need_mask = __any_sync(0xffffffffu, j0 + KEYS - 1 > pos0 + t0 ||
-                                                               (p.window > 0 && j0 < pos_hi - p.window + 1) || !valid);
+                                                               (p.window > 0 && j0 < pos_hi - p.window + 1));
             uint32_t raw[KEYS];
             {
                 uint32_t (&lo32)[32] = *reinterpret_cast<uint32_t (*)[32]>(&raw[0]);
@@ -478,6 +483,405 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     }
 }
 
+// ------------------------------------------------------------------ two row tiles per CTA
+// The same attention with one CTA per SM that owns two consecutive row tiles of a sequence and kv head, blocks of 128
+// keys (two pages), and the whole tensor memory: per tile 128 columns of S (P over the first 64) and 128 of O.  The
+// tiles take turns on the tensor core: while the rows of one tile exponentiate, the core runs the other tile's
+// O += P V and its next S = Q K^T, so neither waits for the other's softmax; a block of keys and values is loaded
+// once for both tiles, and S = Q K^T has N = 128 (the operands' traffic from shared memory per product is half that
+// of N = 64).  S has one stage per tile: a tile's next scores are issued right behind its second product, and the
+// tensor core runs its instructions in order.
+//
+//   warp 0      TMA: both tiles' queries, then K of the block after and V of this one (two stages each)
+//   warp 1      tensor memory (512 columns); one lane issues, per block, for tile 0 and then tile 1:
+//               O += P V of this block, S = Q K^T of the next
+//   warps 2-5   the rows of tile 0, warps 6-9 the rows of tile 1: one thread per row, as in the kernel above
+constexpr int THREADS2 = 320;
+constexpr int KEYS2 = 128;
+constexpr int KSLICE2 = KEYS2 * 128;      // a block's keys (or values), 64 dims of them
+constexpr int KV_STAGE2 = 2 * KSLICE2;
+constexpr int SMEM_BYTES2 = 4 * SLICE + 4 * KV_STAGE2 + 1024 + 256;
+
+__global__ void __launch_bounds__(THREADS2, 1)
+attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                         const __grid_constant__ CUtensorMap map_v, const TcArgs p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* s_q = smem;                              // [2 tiles][2 slices][128 rows][128 B]
+    uint8_t* s_k = s_q + 4 * SLICE;                   // [2 stages][2 slices][128 keys][128 B]
+    uint8_t* s_v = s_k + 2 * KV_STAGE2;               // [2 stages][2 slices of 64 dims][128 keys][128 B]
+    uint64_t* bars = (uint64_t*)(s_v + 2 * KV_STAGE2);
+    // bars: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2 tiles], p_full[2 tiles], o_done
+    uint32_t* tmem_slot = (uint32_t*)(bars + 14);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t q_full = smem_u32(bars), k_full = smem_u32(bars + 1), k_empty = smem_u32(bars + 3);
+    const uint32_t v_full = smem_u32(bars + 5), v_empty = smem_u32(bars + 7);
+    const uint32_t s_full = smem_u32(bars + 9), p_full = smem_u32(bars + 11), o_done = smem_u32(bars + 13);
+
+    // x = (pair rank * kv heads + kv head) * sequences + sequence, long pairs (late tokens) first
+    const int seq = blockIdx.x % p.n_seqs;
+    const int kvh = (blockIdx.x / p.n_seqs) % p.nkv;
+    const int n_pairs = gridDim.x / (p.n_seqs * p.nkv);
+    const int pair = n_pairs - 1 - blockIdx.x / (p.n_seqs * p.nkv);
+    const int G = p.nq / p.nkv, T = ROWS / G;
+    const int q_len = p.seq_qlen[seq], q_start = p.seq_start[seq], pos0 = p.seq_pos0[seq];
+    if (2 * pair * T >= q_len) return;
+    if (p.seq_live != nullptr && p.seq_live[q_start] < 0) return;
+    // Per tile: its tokens, the farthest key any of its rows may see, and its blocks of 128 keys (inclusive).  The
+    // second tile may not exist; its range never begins or ends before the first one's.
+    int t0[2], pos_hi[2], kb0[2], kb1[2];
+    bool active[2];
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+        t0[x] = (2 * pair + x) * T;
+        active[x] = t0[x] < q_len;
+        const int t_end = min(t0[x] + T, q_len);
+        pos_hi[x] = pos0 + t_end - 1;
+        const int lo_min = p.window > 0 ? max(0, pos0 + t0[x] - p.window + 1) : 0;
+        kb0[x] = lo_min / KEYS2;
+        kb1[x] = pos_hi[x] / KEYS2;
+    }
+    const int ub0 = kb0[0], ub1 = active[1] ? kb1[1] : kb1[0];
+    const int n_blocks = ub1 - ub0 + 1;
+    const int pos_hi_u = active[1] ? pos_hi[1] : pos_hi[0];
+    const int slices = (p.hd + 63) / 64;
+    auto part = [&](int x, int i) { return active[x] && ub0 + i >= kb0[x] && ub0 + i <= kb1[x]; };
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(k_full + 8 * b, 1);
+            mbar_init(k_empty + 8 * b, 1);
+            mbar_init(v_full + 8 * b, 1);
+            mbar_init(v_empty + 8 * b, 1);
+            mbar_init(s_full + 8 * b, 1);
+            mbar_init(p_full + 8 * b, 128);
+        }
+        mbar_init(o_done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(512u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;            // columns of tile x: S at 256 x (P over its first 64), O at 256 x + 128
+    fr_pdl_wait();
+    if (threadIdx.x == 0) fr_pdl_launch();
+
+    // Block i of the CTA uses stage i & 1 of K and V, in their (i >> 1)-th use; a tile's barriers count its own blocks.
+    if (warp == 0) {
+        if (elect_one()) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+            mbar_expect_tx(q_full, (uint32_t)((active[1] ? 2 : 1) * slices * 64 * G * T * 2));
+            for (int x = 0; x < 2; ++x)
+                if (active[x])
+                    for (int s = 0; s < slices; ++s)
+                        tma_load_4d(smem_u32(s_q + (2 * x + s) * SLICE), &map_q, s * 64, 0, kvh, q_start + t0[x], q_full);
+            const int* table = p.block_table + (size_t)seq * p.table_width;
+            auto page_row = [&](int lp) {              // lp: the page's number in the sequence
+                if (lp * PAGE <= pos_hi_u && lp < p.table_width) {
+                    const int page = table[lp];
+                    if (page >= 0) return page * PAGE;
+                }
+                return p.pool_rows;                    // beyond the pool: zeros
+            };
+            auto load = [&](int i, const CUtensorMap* map, uint8_t* ring, uint32_t full, uint32_t empty) {
+                const int b = i & 1, par = (i >> 1) & 1;
+                if (!mbar_wait(empty + 8 * b, par ^ 1, p.status, 1)) return false;
+                mbar_expect_tx(full + 8 * b, (uint32_t)(2 * slices * KSLICE));
+                for (int pg = 0; pg < 2; ++pg) {
+                    const int row = page_row(2 * (ub0 + i) + pg);
+                    for (int s = 0; s < slices; ++s)
+                        tma_load_3d(smem_u32(ring) + (uint32_t)(b * KV_STAGE2 + s * KSLICE2 + pg * KSLICE), map, s * 64, kvh, row,
+                                    full + 8 * b);
+                }
+                return true;
+            };
+            bool ok = load(0, &map_k, s_k, k_full, k_empty);
+            for (int i = 0; i < n_blocks && ok; ++i) {
+                if (i + 1 < n_blocks) ok = load(i + 1, &map_k, s_k, k_full, k_empty);
+                if (ok) ok = load(i, &map_v, s_v, v_full, v_empty);
+            }
+        }
+    } else if (warp == 1) {
+        if (elect_one()) {
+            const uint32_t idesc_qk = instr_desc(ROWS, KEYS2);
+            const uint32_t idesc_pv = instr_desc(ROWS, p.hd) | (1u << 16);   // B is MN-major
+            const int k_steps = p.hd / 16;
+            bool ok = mbar_wait(q_full, 0, p.status, 2);
+            int done[2] = {0, 0};                      // blocks whose second product a tile has issued
+            unsigned long long m_spent[5] = {0, 0, 0, 0, 0}, m_mark = p.trace != nullptr ? global_ns() : 0;
+            auto mlap = [&](int which) {
+                if (p.trace != nullptr) {
+                    const unsigned long long now = global_ns();
+                    m_spent[which] += now - m_mark;
+                    m_mark = now;
+                }
+            };
+            // One thread issues every product, and a lone thread runs one dependent instruction every four or five
+            // cycles: what an instruction costs to prepare decides whether the tensor core is kept busy (a product of
+            // N = 128 takes it 64 cycles).  So the descriptors are made once and only stepped in the loops below.  (A
+            // descriptor's low bits are the address in units of 16 bytes; offsets that stay inside the operand's buffer
+            // never carry out of them.)
+            const uint64_t dq0 = smem_desc(smem_u32(s_q)), dk0 = smem_desc(smem_u32(s_k));
+            const uint64_t dv0 = smem_desc_mn(smem_u32(s_v), KSLICE2, 1024);
+            auto scores = [&](int x, int i) {
+                const int b = i & 1, par = (i >> 1) & 1;
+                if (!mbar_wait(k_full + 8 * b, par, p.status, 3)) return false;
+                mlap(0);
+                tc_fence_after();
+                uint64_t da = dq0 + (uint64_t)(x * (2 * SLICE >> 4)), db = dk0 + (uint64_t)(b * (KV_STAGE2 >> 4));
+                const uint32_t d = tmem_base + 256 * x;
+                for (int ks = 0; ks < k_steps; ++ks) {
+                    tc_mma(d, da, db, idesc_qk, ks > 0 ? 1u : 0u);
+                    // 32 bytes on in the 128-byte row; after four of them the next slice of 64 dims
+                    da += (ks & 3) == 3 ? (uint64_t)((SLICE >> 4) - 6) : 2ull;
+                    db += (ks & 3) == 3 ? (uint64_t)((KSLICE2 >> 4) - 6) : 2ull;
+                }
+                tc_commit(s_full + 8 * x);
+                mlap(1);
+                return true;
+            };
+            auto second = [&](int x, int i) {
+                const int b = i & 1, par = (i >> 1) & 1;
+                if (!mbar_wait(v_full + 8 * b, par, p.status, 3)) return false;
+                mlap(2);
+                if (!mbar_wait(p_full + 8 * x, done[x] & 1, p.status, 4)) return false;
+                mlap(3);
+                tc_fence_after();
+                const int keys_here = min(KEYS2, pos_hi[x] - (ub0 + i) * KEYS2 + 1);
+                const int pv_steps = (keys_here + 15) / 16;
+                uint64_t db = dv0 + (uint64_t)(b * (KV_STAGE2 >> 4));
+                const uint32_t d = tmem_base + 256 * x + 128;
+                uint32_t pa = tmem_base + 256 * x;
+                uint32_t keep = done[x] > 0 ? 1u : 0u;
+                for (int ks = 0; ks < pv_steps; ++ks) {
+                    tc_mma_ta(d, pa, db, idesc_pv, keep);
+                    keep = 1u;
+                    pa += 8;                               // 16 keys of P: 8 columns
+                    db += (uint64_t)(16 * 128 >> 4);       // 16 keys of V
+                }
+                ++done[x];
+                mlap(4);
+                return true;
+            };
+            for (int x = 0; x < 2 && ok; ++x)
+                if (part(x, 0)) ok = scores(x, 0);
+            if (ok) tc_commit(k_empty);
+            for (int i = 0; i < n_blocks && ok; ++i) {
+                for (int x = 0; x < 2 && ok; ++x) {
+                    if (part(x, i)) ok = second(x, i);
+                    if (ok && i + 1 < n_blocks && part(x, i + 1)) ok = scores(x, i + 1);
+                }
+                if (!ok) break;
+                tc_commit(v_empty + 8 * (i & 1));
+                if (i + 1 < n_blocks) tc_commit(k_empty + 8 * ((i + 1) & 1));
+            }
+            if (ok) tc_commit(o_done);
+            if (p.trace != nullptr) {
+                unsigned long long* at = p.trace + (size_t)blockIdx.x * 16 + 8;
+                for (int k = 0; k < 5; ++k) at[k] = m_spent[k];
+            }
+        }
+    } else {
+        const int x = (warp - 2) >> 2;                     // this warp's tile
+        const int quarter = warp & 3;                      // TMEM lanes this warp may read: 32*quarter ..
+        const int r = quarter * 32 + lane;                 // this thread's row of the tile
+        const int t = r / G, g = r - t * G;
+        const bool valid = active[x] && r < T * G && t0[x] + t < q_len;
+        const int pos_r = valid ? pos0 + t0[x] + t : -1;   // -1: every key is masked
+        const int lo_r = (valid && p.window > 0) ? max(0, pos_r - p.window + 1) : 0;
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        const uint32_t tmem_s = tmem_base + 256 * x + lane_addr, tmem_o = tmem_s + 128;
+        float m_run = -INFINITY, l_run = 0.f;
+        bool ok = true;
+        int count = 0;                                     // blocks of this tile so far
+        unsigned long long spent[5] = {0, 0, 0, 0, 0};
+        const bool tracing = p.trace != nullptr && r == 0 && x == 0;
+        unsigned long long t_mark = tracing ? global_ns() : 0, t_begin = t_mark;
+        auto lap = [&](int which) {
+            if (tracing) {
+                const unsigned long long now = global_ns();
+                spent[which] += now - t_mark;
+                t_mark = now;
+            }
+        };
+        for (int i = 0; i < n_blocks && ok && active[x]; ++i) {
+            if (!part(x, i)) continue;
+            const int b = i & 1, par = (i >> 1) & 1;
+            const int kb = ub0 + i;
+            const int j0 = kb * KEYS2;
+            if (!(ok = mbar_wait(s_full + 8 * x, count & 1, p.status, 6))) break;
+            tc_fence_after();
+            lap(0);
+            if (p.debug & 1) {                             // measurement only: no softmax at all
+                tc_fence_before();
+                mbar_arrive(p_full + 8 * x);
+                ++count;
+                continue;
+            }
+            const bool need_mask = __any_sync(0xffffffffu, j0 + KEYS2 - 1 > pos0 + t0[x] ||
+                                                               (p.window > 0 && j0 < pos_hi[x] - p.window + 1));
+            // Two passes over the row's 128 scores, 64 at a time (the code of 128 unrolled scores, twice for the masked
+            // and the unmasked form, does not fit the instruction cache beside the other roles'): the maximum first;
+            // then, read again from tensor memory, the exponentials.
+            const int hi = pos_r - j0, lo = lo_r - j0;     // columns hi < j or j < lo are masked
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll 1
+            for (int h = 0; h < 2; ++h) {
+                uint32_t raw[64];
+                {
+                    uint32_t (&lo32)[32] = *reinterpret_cast<uint32_t (*)[32]>(&raw[0]);
+                    uint32_t (&hi32)[32] = *reinterpret_cast<uint32_t (*)[32]>(&raw[32]);
+                    tc_ld32(tmem_s + 64 * h, lo32);
+                    tc_ld32(tmem_s + 64 * h + 32, hi32);
+                    tc_ld_wait();
+                }
+                if (need_mask) {
+#pragma unroll
+                    for (int j = 0; j < 64; ++j) {
+                        const int jj = 64 * h + j;
+                        mx4[j & 3] = fmaxf(mx4[j & 3], (jj > hi || jj < lo) ? -INFINITY : __uint_as_float(raw[j]));
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 64; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(raw[j]));
+                }
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+            lap(1);
+            // The reference maximum moves only when the true one has grown by more than 8; O is rescaled then.  The
+            // tile's second product of the block before is done: this block's scores were issued behind it.
+            const bool grow = mx > m_run + 8.f;
+            if (__any_sync(0xffffffffu, grow)) {
+                const float alpha = grow ? exp2f(m_run - mx) : 1.f;
+                if (grow) {
+                    m_run = mx;
+                    l_run *= alpha;
+                }
+                if (count > 0) {
+#pragma unroll 1
+                    for (int c = 0; c < 8; ++c) {
+                        if (c * 16 < p.hd) {
+                            uint32_t o16[16];
+                            tc_ld16(tmem_o + c * 16, o16);
+                            tc_ld_wait();
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) o16[j] = __float_as_uint(__uint_as_float(o16[j]) * alpha);
+                            tc_st16(tmem_o + c * 16, o16);
+                        }
+                    }
+                    tc_st_wait();
+                }
+            }
+            lap(3);
+            const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            // P (bf16, two to a column) goes over the first 64 columns of S: the 32 columns that the keys of a pass take
+            // held scores that this pass or the one before has read.
+#pragma unroll 1
+            for (int h = 0; h < 2; ++h) {
+                uint32_t raw[64];
+                {
+                    uint32_t (&lo32)[32] = *reinterpret_cast<uint32_t (*)[32]>(&raw[0]);
+                    uint32_t (&hi32)[32] = *reinterpret_cast<uint32_t (*)[32]>(&raw[32]);
+                    tc_ld32(tmem_s + 64 * h, lo32);
+                    tc_ld32(tmem_s + 64 * h + 32, hi32);
+                    tc_ld_wait();
+                }
+                if (need_mask) {
+#pragma unroll
+                    for (int j = 0; j < 64; ++j) {
+                        const int jj = 64 * h + j;
+                        if (jj > hi || jj < lo) raw[j] = 0xff800000u;      // -inf
+                    }
+                }
+                uint32_t packed[32];
+#pragma unroll
+                for (int j = 0; j < 64; j += 2) {
+                    const float e0 = exp2_fast(fmaf(__uint_as_float(raw[j]), p.scale_log2, neg_m));
+                    const float e1 = exp2_fast(fmaf(__uint_as_float(raw[j + 1]), p.scale_log2, neg_m));
+                    sum4[j & 2] += e0;
+                    sum4[(j & 2) + 1] += e1;
+                    packed[j >> 1] = pack2(e0, e1);
+                }
+                tc_st32(tmem_s + 32 * h, packed);
+            }
+            tc_st_wait();
+            l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+            if (kb == ub1) {
+                // keys past the last one that any row of the CTA may see: their V rows may hold anything; zero them
+                // (both tiles do, each before it hands over its P of this block)
+                const int key = j0 + r;
+                if (key > pos_hi_u) {
+                    if (!(ok = mbar_wait(v_full + 8 * b, par, p.status, 7))) break;
+                    for (int s = 0; s < slices; ++s) {
+                        uint4* line = (uint4*)(s_v + b * KV_STAGE2 + s * KSLICE2 + r * 128);
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) line[q] = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            }
+            tc_fence_before();
+            mbar_arrive(p_full + 8 * x);
+            ++count;
+            lap(2);
+        }
+        if (active[x]) {
+            if (ok) ok = mbar_wait(o_done, 0, p.status, 8);
+            tc_fence_after();
+            lap(4);
+            if (ok) {
+                const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+                bf16* dst = p.out + ((size_t)(q_start + t0[x] + t) * p.nq + (size_t)kvh * G + g) * p.hd;
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    if (c * 32 < p.hd) {                               // uniform: the load is warp-wide
+                        uint32_t o32[32];
+                        tc_ld32(tmem_o + c * 32, o32);
+                        tc_ld_wait();
+                        if (valid) {
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                if (c * 32 + q * 8 < p.hd) {
+                                    float v[8];
+#pragma unroll
+                                    for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(o32[q * 8 + j]) * inv;
+                                    *(uint4*)(dst + c * 32 + q * 8) =
+                                        make_uint4(pack2(v[0], v[1]), pack2(v[2], v[3]), pack2(v[4], v[5]), pack2(v[6], v[7]));
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+            if (tracing) {
+                unsigned long long* at = p.trace + (size_t)blockIdx.x * 16;
+                for (int k = 0; k < 5; ++k) at[k] = spent[k];
+                at[5] = (unsigned long long)count;
+                at[6] = global_ns() - t_begin;
+                at[7] = t_begin;
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -508,6 +912,12 @@ int encode(CUtensorMap* map, const void* base, int rank, const cuuint64_t* dims,
 }
 
 constexpr int SMEM_BYTES = 6 * SLICE + 1024 + 256;      // Q, K, V: two 64-dim slices each; two CTAs share an SM
+
+// FRIDAY_ATTN_PAIR=0: prompts always run the kernel with one row tile per CTA.
+bool use_pairs() {
+    const char* e = getenv("FRIDAY_ATTN_PAIR");
+    return e == nullptr || e[0] != '0';
+}
 
 }  // namespace
 
@@ -562,14 +972,27 @@ FR_EXPORT int attention_tc(const void* q, int q_stride, int total_rows, void* ou
     p.seq_pos0 = seq_pos0; p.seq_live = seq_live; p.status = status; p.table_width = table_width; p.nq = nq;
     p.nkv = nkv; p.hd = hd; p.window = window; p.pool_rows = pool_pages * PAGE; p.scale_log2 = scale * LOG2E;
     p.trace = attention_tc_trace;
+    p.debug = getenv("FRIDAY_ATTN_DEBUG") ? atoi(getenv("FRIDAY_ATTN_DEBUG")) : 0;
     static bool configured = false;
     if (!configured) {
         FR_CUDA(cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         configured = true;
     }
-    const long long tiles = (long long)((max_q_len + T - 1) / T) * nkv * n_seqs;
+    const long long tiles_seq = (max_q_len + T - 1) / T;
+    const long long tiles = tiles_seq * nkv * n_seqs;
     if (tiles > 0x7fffffffLL) FR_REFUSE("attention_tc: %lld tiles exceed the grid", tiles);
     p.n_seqs = n_seqs;
+    if (tiles_seq >= 2 && use_pairs()) {
+        static bool configured2 = false;
+        if (!configured2) {
+            FR_CUDA(cudaFuncSetAttribute(attention_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES2));
+            configured2 = true;
+        }
+        const dim3 grid((unsigned)(((tiles_seq + 1) / 2) * nkv * n_seqs));
+        FR_CUDA(fr_launch(attention_tc_pair_kernel, grid, dim3(THREADS2), SMEM_BYTES2, stream, mq, mk, mv, p));
+        FR_CHECK_LAUNCH("attention_tc (two tiles per CTA)");
+        return FR_OK;
+    }
     const dim3 grid((unsigned)tiles);
     FR_CUDA(fr_launch(attention_tc_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, mq, mk, mv, p));
     FR_CHECK_LAUNCH("attention_tc");

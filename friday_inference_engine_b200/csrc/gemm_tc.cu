@@ -256,7 +256,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     }
 
     if (warp == 0) {
-        if (lane == 0) {
+        if (elect_one()) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_p) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
             // The k-slices this CTA will load, in order: (work item, k block).
@@ -313,7 +313,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
+        if (elect_one()) {
             fr_pdl_wait();
             const uint32_t idesc = instr_desc(TILE_P, bn);
             int stage = 0;

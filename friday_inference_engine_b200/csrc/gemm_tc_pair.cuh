@@ -97,7 +97,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     if (threadIdx.x == 0) fr_pdl_launch();
 
     if (warp == 0) {
-        if (lane == 0) {
+        if (elect_one()) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_p) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
             struct Walk {                                  // the k blocks this pair will load, in order
@@ -147,7 +147,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             }
         }
     } else if (warp == 1) {
-        if (lane == 0 && rank == 0) {
+        if (rank == 0 && elect_one()) {
             fr_pdl_wait();
             const uint32_t idesc = instr_desc(2 * TILE_P, bn);
             int stage = 0;
