@@ -232,7 +232,7 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
             }
             if (!(ok = tc::mbar_wait(empty0 + 8 * b, ((j / NS) & 1) ^ 1, p.status, 21))) break;
             const int page = kb < WARPS * 32 ? s_pages[kb] : table[kb];
-            if (lane == 0) {
+            if (tc::elect_one()) {
                 // a page that the table does not name is loaded from beyond the pool's last row: zeros
                 const int row = page >= 0 ? page * BLOCK_N : p.pool_rows;
                 tc::mbar_expect_tx(full0 + 8 * b, (uint32_t)(2 * SL * BLOCK_N * 128));

@@ -67,7 +67,6 @@ struct TcArgs {
     int* status;
     int table_width, nq, nkv, hd, window, pool_rows, n_seqs;
     float scale_log2;         // softmax scale times log2(e)
-    int debug;
     unsigned long long* trace;   // for measurements (may be null): [cta][8] sums of time (ns) that row 0's thread spent
                                  // waiting for S, reading it, writing P, rescaling O, waiting for the last product;
                                  // then blocks, total time, start
@@ -723,40 +722,26 @@ attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             if (!(ok = mbar_wait(s_full + 8 * x, count & 1, p.status, 6))) break;
             tc_fence_after();
             lap(0);
-            if (p.debug & 1) {                             // measurement only: no softmax at all
-                tc_fence_before();
-                mbar_arrive(p_full + 8 * x);
-                ++count;
-                continue;
-            }
             const bool need_mask = __any_sync(0xffffffffu, j0 + KEYS2 - 1 > pos0 + t0[x] ||
                                                                (p.window > 0 && j0 < pos_hi[x] - p.window + 1));
-            // Two passes over the row's 128 scores, 64 at a time (the code of 128 unrolled scores, twice for the masked
-            // and the unmasked form, does not fit the instruction cache beside the other roles'): the maximum first;
-            // then, read again from tensor memory, the exponentials.
+            // The row's 128 scores are read from tensor memory once (a load and its wait cost some 400 cycles, whatever
+            // the number of columns) and stay in registers for both passes.
             const int hi = pos_r - j0, lo = lo_r - j0;     // columns hi < j or j < lo are masked
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll 1
-            for (int h = 0; h < 2; ++h) {
-                uint32_t raw[64];
-                {
-                    uint32_t (&lo32)[32] = *reinterpret_cast<uint32_t (*)[32]>(&raw[0]);
-                    uint32_t (&hi32)[32] = *reinterpret_cast<uint32_t (*)[32]>(&raw[32]);
-                    tc_ld32(tmem_s + 64 * h, lo32);
-                    tc_ld32(tmem_s + 64 * h + 32, hi32);
-                    tc_ld_wait();
-                }
-                if (need_mask) {
+            uint32_t raw[KEYS2];
 #pragma unroll
-                    for (int j = 0; j < 64; ++j) {
-                        const int jj = 64 * h + j;
-                        mx4[j & 3] = fmaxf(mx4[j & 3], (jj > hi || jj < lo) ? -INFINITY : __uint_as_float(raw[j]));
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 64; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(raw[j]));
-                }
+            for (int c = 0; c < 4; ++c) {
+                uint32_t (&part32)[32] = *reinterpret_cast<uint32_t (*)[32]>(&raw[32 * c]);
+                tc_ld32(tmem_s + 32 * c, part32);
             }
+            tc_ld_wait();
+            if (need_mask) {
+#pragma unroll
+                for (int j = 0; j < KEYS2; ++j)
+                    if (j > hi || j < lo) raw[j] = 0xff800000u;          // -inf
+            }
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int j = 0; j < KEYS2; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(raw[j]));
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
             lap(1);
             // The reference maximum moves only when the true one has grown by more than 8; O is rescaled then.  The
@@ -786,30 +771,14 @@ attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             lap(3);
             const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-            // P (bf16, two to a column) goes over the first 64 columns of S: the 32 columns that the keys of a pass take
-            // held scores that this pass or the one before has read.
-#pragma unroll 1
-            for (int h = 0; h < 2; ++h) {
-                uint32_t raw[64];
-                {
-                    uint32_t (&lo32)[32] = *reinterpret_cast<uint32_t (*)[32]>(&raw[0]);
-                    uint32_t (&hi32)[32] = *reinterpret_cast<uint32_t (*)[32]>(&raw[32]);
-                    tc_ld32(tmem_s + 64 * h, lo32);
-                    tc_ld32(tmem_s + 64 * h + 32, hi32);
-                    tc_ld_wait();
-                }
-                if (need_mask) {
+            // P (bf16, two to a column) goes over the first 64 columns of S.
 #pragma unroll
-                    for (int j = 0; j < 64; ++j) {
-                        const int jj = 64 * h + j;
-                        if (jj > hi || jj < lo) raw[j] = 0xff800000u;      // -inf
-                    }
-                }
+            for (int h = 0; h < 2; ++h) {
                 uint32_t packed[32];
 #pragma unroll
                 for (int j = 0; j < 64; j += 2) {
-                    const float e0 = exp2_fast(fmaf(__uint_as_float(raw[j]), p.scale_log2, neg_m));
-                    const float e1 = exp2_fast(fmaf(__uint_as_float(raw[j + 1]), p.scale_log2, neg_m));
+                    const float e0 = exp2_fast(fmaf(__uint_as_float(raw[64 * h + j]), p.scale_log2, neg_m));
+                    const float e1 = exp2_fast(fmaf(__uint_as_float(raw[64 * h + j + 1]), p.scale_log2, neg_m));
                     sum4[j & 2] += e0;
                     sum4[(j & 2) + 1] += e1;
                     packed[j >> 1] = pack2(e0, e1);
@@ -972,7 +941,6 @@ FR_EXPORT int attention_tc(const void* q, int q_stride, int total_rows, void* ou
     p.seq_pos0 = seq_pos0; p.seq_live = seq_live; p.status = status; p.table_width = table_width; p.nq = nq;
     p.nkv = nkv; p.hd = hd; p.window = window; p.pool_rows = pool_pages * PAGE; p.scale_log2 = scale * LOG2E;
     p.trace = attention_tc_trace;
-    p.debug = getenv("FRIDAY_ATTN_DEBUG") ? atoi(getenv("FRIDAY_ATTN_DEBUG")) : 0;
     static bool configured = false;
     if (!configured) {
         FR_CUDA(cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
