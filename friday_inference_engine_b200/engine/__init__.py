@@ -31,7 +31,7 @@ class EngineOptions:
     max_batch: int = 8                     # sequences alive at once
     max_tokens: Optional[int] = None       # cache capacity in tokens; default max_batch * max_ctx (in pages)
     device: str = "cuda:0"
-    prefill_chunk: int = 2048              # tokens of one sequence per pass
+    prefill_chunk: int = 2560              # most tokens of one sequence per pass
     cuda_graphs: bool = True               # decode steps of generate() are captured once and replayed
     random_on_device: bool = True          # random weights are drawn on the device (fast); False: on the host
     profile: bool = False                  # per-step host time and event-bracketed kernel time (Engine.profile())

@@ -45,7 +45,7 @@ void PinnedRing::sent(cudaStream_t stream) {
 
 // ------------------------------------------------------------------ the step function
 Stepper::Stepper(DecoderModel& model, Cache& cache, Ops& ops, int chunk)
-    : model_(model), cache_(cache), ops_(ops), chunk_(chunk > 0 ? chunk : 2048), pass_(ops.stream()),
+    : model_(model), cache_(cache), ops_(ops), chunk_(chunk > 0 ? chunk : 2560), pass_(ops.stream()),
       layer_a_(ops.stream()), layer_b_(ops.stream()), keep_(ops.stream()) {}
 
 void Stepper::check(const StepBatch& b) const {
@@ -99,7 +99,12 @@ size_t Stepper::step(const StepBatch& b, float* out, bool out_on_device) {
         std::vector<int> slots, q_lens, start;
         int rows = 0;
         for (int i : live) {
-            const int q = std::min(chunk_, (int)b.tokens[i].size() - done[i]);
+            // what is left of the sequence in passes of equal size (whole pages), none longer than the chunk: a last
+            // pass of a few hundred tokens would fill the device badly
+            const int left = (int)b.tokens[i].size() - done[i];
+            const int passes = (left + chunk_ - 1) / chunk_;
+            const int even = ((left + passes - 1) / passes + PAGE - 1) / PAGE * PAGE;
+            const int q = std::min(left, std::min(chunk_, even));
             slots.push_back(b.slots[i]);
             q_lens.push_back(q);
             start.push_back(cache_.lens[b.slots[i]]);

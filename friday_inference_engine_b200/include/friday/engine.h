@@ -39,7 +39,7 @@ struct EngineOptions {
     int max_batch = 8;               // sequences alive at once
     int64_t max_tokens = 0;          // cache capacity in tokens; 0: max_batch * max_ctx (in pages)
     int device = 0;
-    int prefill_chunk = 2048;        // tokens of one sequence per pass
+    int prefill_chunk = 2560;        // most tokens of one sequence per pass (ten 256-row tiles of a prompt's products)
     bool cuda_graphs = true;         // decode steps of generate() are captured once and replayed
     bool random_on_device = true;    // random weights are drawn on the device (fast); false: on the host
     bool profile = false;            // event-bracketed time per kind of kernel and host time per step (see profile())
