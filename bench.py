@@ -329,7 +329,7 @@ def cta_trace(eng, batch):
         eng.free_slot(s)
 
     # the prompt attention of the last layer: where the thread of a CTA's first row and the thread that issues the
-    # products spend the time of a block of 64 keys
+    # products spend the time of a block of keys
     (p,) = random_prompts(1, PREFILL_TOKENS, eng.vocab_size, 99)
     for _ in range(2):
         s = eng.alloc_slot()
@@ -346,7 +346,8 @@ def cta_trace(eng, batch):
     t = tc.cpu().numpy().astype(np.float64)
     t = t[t[:, 5] > 0]
     blocks = t[:, 5].sum()
-    print("prompt attention, %d tokens: %d CTAs, %d blocks of 64 keys; us per block: " % (PREFILL_TOKENS, len(t), blocks)
+    # (with two row tiles per CTA a block is 128 keys, the rows' figures are the first tile's, the issuer's both tiles')
+    print("prompt attention, %d tokens: %d CTAs, %d blocks; us per block: " % (PREFILL_TOKENS, len(t), blocks)
           + ", ".join("%s %.2f" % (what, t[:, k].sum() / blocks / 1000.0) for k, what in
                       ((0, "row waits for S"), (1, "reads S, maximum"), (2, "exponentials and P"), (3, "rescales O"),
                        (4, "waits for the last product"), (8, "issuer waits for K"), (9, "issues Q K^T"),
