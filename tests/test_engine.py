@@ -110,6 +110,21 @@ def test_cut_into_passes_and_continued(root, where, name):
     eng.free_slot(s)
 
 
+def test_passes_of_equal_size(root, where):
+    """Passes are cut as equal as whole pages allow, none longer than the limit: 200 tokens with a limit of 144 run as
+    128 + 72 (two passes of 100, rounded up to pages of 64), 150 tokens with a limit of 80 as 80 + 70 (the rounded share
+    would exceed the limit)."""
+    for limit, n in ((80, 150), (144, 200)):
+        eng, pm = engine(root, "B", where, prefill_chunk=limit)
+        (p,) = tiny_configs.random_prompts([n], eng.vocab_size, 14)
+        ref = plain_model.logits(pm, p)
+        want = [n - 1, 0, 63, 64, 79, 80, 127, min(128, n - 1)]
+        s = eng.alloc_slot()
+        got = eng.step([s], [p], [want])
+        harness.check_logits(harness.to_np(got), ref[want], where[1], "%d tokens in passes of at most %d" % (n, limit))
+        eng.free_slot(s)
+
+
 @pytest.mark.parametrize("name", ["B", "C"])
 def test_several_sequences_over_several_passes(root, where, name):
     """Three sequences of unequal lengths cut into passes of 48 tokens: the later passes hold fewer sequences, and
