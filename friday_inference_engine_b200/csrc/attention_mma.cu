@@ -499,13 +499,38 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
             const int t = rr / G, h = kvh * G + (rr - t * G);
             const size_t item = (size_t)(q_start + t) * p.nq + h;
             const float inv = l > 0.f ? 1.f / l : 0.f;
-            for (int d = (tid & 7); d < HD; d += 8) {
-                float acc = 0.f;
+            // A row's eight threads take HD / 8 consecutive dimensions each, in pieces of four (two for head sizes
+            // that are no multiple of 32): all loads of a piece's four warps are issued before the first is used (one
+            // dimension at a time, this loop took 1.6 us of a 9 us kernel).
+            constexpr int PER = HD / 8;                  // 2, 4, ... 16
+            constexpr int V = PER % 4 == 0 ? 4 : 2;      // floats per piece
+            const int d0 = (tid & 7) * PER;
 #pragma unroll
-                for (int w = 0; w < WARPS; ++w) acc += c_o[(w * 16 + r) * HDP + d] * f[w];
-                if (p.splits == 1) p.out[item * HD + d] = __float2bfloat16_rn(acc * inv);
-                else if (p.cluster) r_o[r * HD + d] = acc;
-                else p.part[(item * p.splits + split) * (HD + 2) + d] = acc;
+            for (int c = 0; c < PER / V; ++c) {
+                float acc[V];
+#pragma unroll
+                for (int j = 0; j < V; ++j) acc[j] = 0.f;
+#pragma unroll
+                for (int w = 0; w < WARPS; ++w) {
+                    const float* src = c_o + (w * 16 + r) * HDP + d0 + c * V;
+                    if (V == 4) {
+                        const float4 x = *reinterpret_cast<const float4*>(src);
+                        acc[0] += x.x * f[w]; acc[1] += x.y * f[w]; acc[2 % V] += x.z * f[w]; acc[3 % V] += x.w * f[w];
+                    } else {
+                        const float2 x = *reinterpret_cast<const float2*>(src);
+                        acc[0] += x.x * f[w]; acc[1] += x.y * f[w];
+                    }
+                }
+                const int d = d0 + c * V;
+                if (p.splits == 1) {
+#pragma unroll
+                    for (int j = 0; j < V; j += 2)
+                        *reinterpret_cast<uint32_t*>(p.out + item * HD + d + j) = pack_bf16(acc[j] * inv, acc[j + 1] * inv);
+                } else {
+                    float* dst = p.cluster ? r_o + r * HD + d : p.part + (item * p.splits + split) * (HD + 2) + d;
+#pragma unroll
+                    for (int j = 0; j < V; j += 2) *reinterpret_cast<float2*>(dst + j) = make_float2(acc[j], acc[j + 1]);
+                }
             }
             if (p.cluster && p.splits > 1 && (tid & 7) == 0) {
                 r_m[r] = big;
