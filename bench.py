@@ -512,6 +512,37 @@ def run_32b(eng, args, cfg, layers, full_layers, nums, pk):
     return 0 if same else 1
 
 
+def sweeps(Engine, args):
+    """Decode steps and prompts away from the headline's sizes (same timing functions), one line of text each."""
+    cfg = dict(SHAPES[args.model_size])
+    layers = args.layers or cfg["num_hidden_layers"]
+    cfg["num_hidden_layers"] = layers
+    cases = [tuple(int(v) for v in c.split("x")) for c in args.decode_sweep.split(",") if c]
+    lengths = [int(v) for v in args.prompt_sweep.split(",") if v]
+    longest = max([c + 64 + SETTLE_STEPS for _, c in cases] + lengths + [1024])
+    context = (longest + 1023) // 1024 * 1024
+    tokens = max([b * (c + 128) for b, c in cases] + lengths + [1024]) + 4096
+    batch = max([b for b, _ in cases] + [1])
+    options = {"prefill_chunk": args.prefill_chunk} if args.prefill_chunk else {}
+    eng = Engine(config=cfg, seed=0, dtype="bfloat16", max_ctx=context, max_batch=batch, max_tokens=tokens, **options)
+    print("[bench] %s" % eng.summary(), file=sys.stderr, flush=True)
+    pk = peaks()
+    nums = model_numbers(cfg, layers)
+    for length in lengths:
+        ms = time_prefill(eng, length, 1, 3)
+        rec = prefill_record(cfg, layers, nums, length, ms, pk)
+        print("prompt of %6d tokens: %8.1f ms, %8.1f tok/s, %.3f of the %s bf16 peak" % (length, ms, rec["value"], rec["frac"], pk["source"]),
+              flush=True)
+    for b, c in cases:
+        prompts = random_prompts(b, c, eng.vocab_size, 3)
+        ms, _, mean_len, _ = time_decode(eng, prompts, min(args.steps, 32), args.warmup)
+        step_bytes = nums["step_weight_bytes"] + nums["kv_bytes_per_token"] * mean_len * b
+        print("decode, %2d sequences of %5d tokens: %.3f ms per step, %8.1f tok/s, %.3f of the %s HBM roofline" % (
+            b, c, ms, b * 1000.0 / ms, step_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], pk["source"]), flush=True)
+    eng.check()
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -527,6 +558,12 @@ def main():
     ap.add_argument("--slots", type=int, default=0, help="sequences the cache is sized for (smaller for profiling)")
     ap.add_argument("--cta-trace", action="store_true",
                     help="print when the CTAs of a decode step's products and attention reach the points they stamp")
+    ap.add_argument("--decode-sweep", default="", dest="decode_sweep",
+                    help="decode steps at other batch sizes and context lengths, e.g. 1x32000,8x8000,32x4000: one line each")
+    ap.add_argument("--prompt-sweep", default="", dest="prompt_sweep",
+                    help="one prompt of each of these lengths, e.g. 2048,8192,32000: one line each")
+    ap.add_argument("--prefill-chunk", type=int, default=0, dest="prefill_chunk",
+                    help="most tokens of a sequence per pass in the sweeps (0: the engine's own)")
     ap.add_argument("--timeline", action="store_true",
                     help="print the kernels of one decode step as they run inside the captured graph (torch profiler)")
     args = ap.parse_args()
@@ -542,6 +579,8 @@ def main():
 
     from friday_inference_engine_b200 import Engine
 
+    if args.decode_sweep or args.prompt_sweep:
+        return sweeps(Engine, args)
     cfg = dict(SHAPES[args.model_size])
     full_layers = cfg["num_hidden_layers"]
     layers = args.layers or full_layers
