@@ -988,6 +988,10 @@ FR_EXPORT int gemm_tc_plan(int m, int n, int k, int sm_count, int swap, int bn, 
             splits = sm_count / tiles;
             if (splits > kb_total / 4) splits = kb_total / 4;      // at least four k-slices per split
             if (skinny && splits > 4) splits = 4;                  // wide partial tiles are costly to merge
+            // ... and with rows on the M side every partial tile is 128 or 256 rows high: a split pays only if it still
+            // has 64 k blocks to itself (256 x 4608 x 3584: 19.7 us whole on 36 of 74 SM pairs, 23.2 us in two splits on
+            // 72; 256 x 3584 x 18944: 72.5 us whole, 53.5 us in two)
+            if (!swap && splits > kb_total / 64) splits = kb_total / 64;
             if (splits < 1) splits = 1;
         } else if (swap && bn <= 16 && tiles > sm_count) {
             // More tiles than SMs and a last wave that is partly empty (216 tiles on 148 SMs: the second wave costs as
