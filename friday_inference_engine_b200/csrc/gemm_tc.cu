@@ -972,12 +972,16 @@ FR_EXPORT int gemm_tc_plan(int m, int n, int k, int sm_count, int swap, int bn, 
             const long long tiles_p = pair ? (p_rows + 2 * TILE_P - 1) / (2 * TILE_P) : (p_rows + TILE_P - 1) / TILE_P;
             const long long units = pair ? sm_count / 2 : sm_count;
             long long best = -1;
-            for (int cand = 256; cand >= 128; cand -= 16) {
+            // (pairs of SMs also take narrower tiles; they pay where k is short and the wider tiles leave pairs idle:
+            // 256 x 4608 x 3584 runs 36 tiles of 128 in 19.7 us and 72 of 64 in 17.6 us; long k is split instead)
+            const int narrowest = pair && kb_total < 128 ? 64 : 128;
+            for (int cand = 256; cand >= narrowest; cand -= 16) {
                 const long long tiles = tiles_p * ((q_rows + cand - 1) / cand);
                 const long long cost = ((tiles + units - 1) / units) * (cand + 16);
                 if (best < 0 || cost < best) { best = cost; bn = cand; }
             }
         } else if (!skinny) bn = q_rows > 64 ? 128 : 64;
+        else if (kb_total >= 128 && q_rows < 8192 && 2 * ((q_rows + 63) / 64) <= sm_count) bn = 64;   // long k, cut in two (96 x 3584 x 18944: 42.7 us; 128-wide tiles in four splits: 47.1 us)
         else if (q_rows >= 8192 || kb_total >= 128) bn = 128;
         else bn = (q_rows + 31) / 32 <= sm_count ? 32 : 64;
     }
@@ -1059,7 +1063,8 @@ FR_EXPORT int gemm_tc_fused(const void* x, const void* w, void* out, int out_dty
     const bool splits_free = splits < 0;
     gemm_tc_plan(m, n, k, sm_count, swap, bn, splits, plan);
     swap = (int)plan[0]; bn = (int)plan[1]; splits = (int)plan[2];
-    if (bn != 16 && bn != 32 && bn != 64 && !(bn >= 128 && bn <= 256 && bn % 16 == 0)) FR_REFUSE("gemm_tc: tile width %d", bn);
+    const bool narrow_pair = pair_shape(m, n, swap, sm_count) && splits == 1 && bn >= 64 && bn < 128 && bn % 16 == 0;
+    if (bn != 16 && bn != 32 && bn != 64 && !(bn >= 128 && bn <= 256 && bn % 16 == 0) && !narrow_pair) FR_REFUSE("gemm_tc: tile width %d", bn);
     // Few rows stream the weights once, and an SM draws only so much (about 45 GB/s on a B200): the product is as fast as
     // its share of busy SMs.  Several waves of whole tiles can leave most SMs idle in the last one (the head's 1,188 tiles
     // on 148 SMs: a ninth wave of four); where that costs more than a tenth, the k blocks of all tiles are laid end to end
@@ -1144,7 +1149,7 @@ FR_EXPORT int gemm_tc_fused(const void* x, const void* w, void* out, int out_dty
             grid = sm_count;
         }
     }
-    if (pair_shape(m, n, swap, sm_count) && splits == 1 && bn >= 128 && p.sk_tiles == 0) {
+    if (pair_shape(m, n, swap, sm_count) && splits == 1 && (bn >= 128 || narrow_pair) && p.sk_tiles == 0) {
         // 256 x bn tiles on pairs of SMs; each CTA loads half of a tile's weight rows
         p.tiles_p = (m + 2 * TILE_P - 1) / (2 * TILE_P);
         const int pair_tiles = p.tiles_p * p.tiles_q;

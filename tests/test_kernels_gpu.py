@@ -273,7 +273,9 @@ def test_gemm_tensor_core(m, n, k):
     (8, 512, 1024, 1, 16, 1), (8, 512, 1024, 1, 16, 4), (8, 512, 1024, 1, 64, 16), (40, 300, 2048, 1, 64, 3),
     (40, 300, 2048, 0, 64, 1), (300, 300, 2048, 0, 128, 2), (300, 700, 2048, 0, 256, 5), (128, 256, 4096, 0, 256, 64),
     (100, 100, 64, 0, 128, 1), (5, 130, 72, 0, 256, 1), (300, 40, 2048, 1, 32, 1),
-    (300, 1000, 256, 0, 208, 1), (2048, 3584, 512, 0, 208, 1), (256, 700, 128, 0, 144, 3), (130, 1001, 328, 0, 240, 1)])
+    (300, 1000, 256, 0, 208, 1), (2048, 3584, 512, 0, 208, 1), (256, 700, 128, 0, 144, 3), (130, 1001, 328, 0, 240, 1),
+    # tiles narrower than 128 on pairs of SMs (more than 128 rows, k not split)
+    (256, 1000, 512, 0, 64, 1), (300, 700, 328, 0, 112, 1), (513, 333, 256, 0, 80, 1), (200, 4608, 192, 0, 96, 1)])
 def test_gemm_tensor_core_every_tiling(m, n, k, swap, bn, splits):
     """Orientation, tile width and split-k are choices of the launcher; each must give the same product."""
     dt = torch.bfloat16
@@ -388,6 +390,19 @@ def sampled_columns(n, count, seed):
     g = torch.Generator().manual_seed(seed)
     cols = torch.randperm(n, generator=g)[:count].sort().values
     return torch.cat([torch.tensor([0, 127, 128, n - 129, n - 128, n - 1]), cols]).unique()
+
+
+@pytest.mark.parametrize("m", [129, 256, 300, 512, 640])
+@pytest.mark.parametrize("n,k", [(4608, 3584), (3584, 3584), (7168, 5120)])
+def test_products_of_prompts_of_a_few_hundred_rows(m, n, k):
+    """The tilings the planner picks between one and a few row tiles (narrow tiles on pairs of SMs among them), with
+    bias and residual, against float64."""
+    dt = torch.bfloat16
+    a, w = rnd((m, k), dt, 210 + m), rnd((n, k), dt, 211, 0.02)
+    bias, res = rnd((n,), dt, 212), rnd((m, n), dt, 213)
+    ref = pm.linear(f64(a), f64(w), f64(bias)) + f64(res)
+    close(ops.linear(a, w, bias, res), ref, dt, "%d x %d x %d as planned" % (m, n, k), bf16_rel=0.01)
+    ops.backend().check_status()
 
 
 @pytest.mark.parametrize("m", [1, 8, 64, 130])
