@@ -71,7 +71,7 @@ constexpr int SIDE_BYTES = 3 * TILE_P * 4 + 3 * 64 * 4 + 64 * 8;      // row fac
 template <int BN, int STAGES>
 constexpr int smem_bytes() {
     return STAGES * (P_BYTES + BN * TILE_K * 2) + 1024 + (2 * STAGES + 4) * 8 + 64 + SIDE_BYTES +
-           (BN <= 64 ? BN * TILE_P * 4 : BN * 4) + (BN <= 64 ? 16 * 64 * 8 : 0);
+           (BN <= 64 ? BN * TILE_P * 4 : BN == 128 ? 16 * TILE_P * 4 : BN * 4) + (BN <= 64 ? 16 * 64 * 8 : 0);
 }
 
 struct GemmParams {
@@ -219,7 +219,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     long long* s_crow = (long long*)(s_pos + 64);                            // [64]
     // Narrow tiles (the swapped orientation) write their output transposed: the sums of [BN rows][128 columns]
     // go through this buffer so that global memory sees 16-byte pieces of whole rows.
-    constexpr int T_BYTES = BN <= 64 ? BN * TILE_P * 4 : 0;
+    // (a 128-wide tile of the swapped orientation goes through a window of 16 of its rows at a time)
+    constexpr int W_ROWS = BN <= 64 ? BN : 16;
+    constexpr int T_BYTES = BN <= 64 || BN == 128 ? W_ROWS * TILE_P * 4 : 0;
     uint8_t* s_tile = (uint8_t*)s_scale + SIDE_BYTES;
     float2* s_cs = (float2*)(s_tile + T_BYTES);                              // [16][64]: the rotation's (cos, sin) of the 16 rows being finished
     float* s_gw = (float*)s_tile;                                            // [BN] norm weights of the columns of a tile with rows on M
@@ -413,11 +415,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         // 16 rows of the step for this thread's column: into the transposed tile.
         auto put16 = [&](int c, const float (&v)[16]) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) s_sum[(c * 16 + j) * TILE_P + i_local] = v[j];
+            for (int j = 0; j < 16; ++j) s_sum[((c * 16 + j) & (W_ROWS - 1)) * TILE_P + i_local] = v[j];
         };
         // bias and residual added to 8 sums of one row; the values as they will be stored (bf16: rounded)
         auto load_piece = [&](int token, int f0, float (&x)[8]) {
-            const float4 a0 = *(const float4*)(s_sum + token * TILE_P + f0), a1 = *(const float4*)(s_sum + token * TILE_P + f0 + 4);
+            const float* at = s_sum + (token & (W_ROWS - 1)) * TILE_P + f0;
+            const float4 a0 = *(const float4*)at, a1 = *(const float4*)(at + 4);
             const float4 b0 = *(const float4*)(s_bias + f0), b1 = *(const float4*)(s_bias + f0 + 4);
             x[0] = a0.x + b0.x; x[1] = a0.y + b0.y; x[2] = a0.z + b0.z; x[3] = a0.w + b0.w;
             x[4] = a1.x + b1.x; x[5] = a1.y + b1.y; x[6] = a1.z + b1.z; x[7] = a1.w + b1.w;
@@ -432,7 +435,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         auto finish_rows_gated = [&](int p_blk, int q_blk, int t_lo, int t_cnt) {
             if (et >= t_cnt * 8) return;
             const int token = t_lo + (et >> 3), f0 = (et & 7) * 16;
-            const float* src = s_sum + token * TILE_P + f0;
+            const float* src = s_sum + (token & (W_ROWS - 1)) * TILE_P + f0;
             float x[8];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -697,7 +700,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
                 if (part == nullptr) {
                     scale16(c, v);
-                    if (staged) put16(c, v);
+                    if (staged) {
+                        put16(c, v);
+                        if (BN == 128) {                   // the window holds these 16 rows only: finish them now
+                            asm volatile("bar.sync 1, 128;" ::: "memory");
+                            finish_chunks(p_blk, q_blk, c, BN, false);
+                        }
+                    }
                     else if (norm_rows) finish16_norm(q_blk, gi, q_blk * bn + c * 16, v, ss_row);
                     else finish16(p, gi, q_blk * bn + c * 16, v);
                 } else {
@@ -709,7 +718,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acce0 + 8 * a);     // the accumulator may be overwritten
-            if (part == nullptr && staged) {
+            if (part == nullptr && staged && BN != 128) {
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 finish_chunks(p_blk, q_blk, 0, 1, false);
             }
@@ -878,12 +887,16 @@ bool use_stream_k() {
     return v != 0;
 }
 
-// FRIDAY_GEMM_EVEN_RUNS=0: products of few rows always run whole tiles times an equal split of k.
+// FRIDAY_GEMM_EVEN_RUNS=1: products of few rows whose tiles fill several waves with a nearly empty last one run as
+// equal runs of k blocks over all SMs.  Off by default: since the instructions of the copying and issuing threads
+// became cheap (elect.sync), whole tiles are as fast or faster at every size measured (the head of 152,064 columns:
+// 165.5 us against 168.2 us at 8 rows, 182.6 against 187.0 at 64, 203.3 against 213.0 at 128; the 14B shape's gate/up
+// product: 48.9 against 50.2 us at 8 rows, 55.8 against 63.1 at 64).
 bool use_even_runs() {
     static int v = -1;
     if (v < 0) {
         const char* e = getenv("FRIDAY_GEMM_EVEN_RUNS");
-        v = (e != nullptr && e[0] == '0') ? 0 : 1;
+        v = (e != nullptr && e[0] == '1') ? 1 : 0;
     }
     return v != 0;
 }
@@ -951,18 +964,18 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmParams& p, in
 // and plan[4] = counters needed.  bn / splits / swap < 0 let the heuristics decide.
 FR_EXPORT int gemm_tc_plan(int m, int n, int k, int sm_count, int swap, int bn, int splits, long long* plan) {
     // Measured on B200 at the sizes of a 7B model (k = 3584 or 18944, n from 3584 to 152064):
-    //  * up to 64 rows: weights on the M side, the rows as an N tile of 16, 32 or 64; k split until the SMs are
+    //  * up to 128 rows: weights on the M side, the rows as an N tile of 16, 32, 64 or 128; k split until the SMs are
     //    busy (at 64 rows: 16 / 15 / 35 us for the qkv, output and down products against 21 / 20 / 40 us the other
-    //    way round; at 32 rows 13 / 12 / 31 against 21 / 20 / 39);
-    //  * 65 to 128 rows: rows on the M side (one tile, partly empty) and narrow weight tiles, so that about a
-    //    hundred CTAs stream weights without splitting k; very long k is split four ways over wide tiles instead;
+    //    way round; at 32 rows 13 / 12 / 31 against 21 / 20 / 39).  With the rows on the M side a CTA moves 16 KB of
+    //    activations per k block whatever the number of rows, beside 4 KB of a narrow weight tile: at 96 rows the same
+    //    three products took 15.4 / 14.9 / 42.7 us that way;
     //  * more rows: 128 x bn tiles, or 256 x bn tiles on pairs of SMs (wide outputs).
     const int kb_total = (k + TILE_K - 1) / TILE_K;
-    if (swap < 0) swap = m <= 64 ? 1 : 0;
+    if (swap < 0) swap = m <= 128 ? 1 : 0;
     const int q_rows = swap ? m : n, p_rows = swap ? n : m;
     const bool skinny = !swap && m <= TILE_P;
     if (bn <= 0) {
-        if (swap) bn = q_rows <= 16 ? 16 : q_rows <= 32 ? 32 : 64;
+        if (swap) bn = q_rows <= 16 ? 16 : q_rows <= 32 ? 32 : q_rows <= 64 ? 64 : 128;
         else if (!skinny && q_rows >= 256) {
             // Many rows: 128 x bn tiles, bn a multiple of 16 from 128 to 256, chosen so that the tiles fill whole
             // waves of the SMs.  A tile costs about bn + 16 (its products, and an epilogue that is mostly hidden);
@@ -1067,10 +1080,9 @@ FR_EXPORT int gemm_tc_fused(const void* x, const void* w, void* out, int out_dty
     if (bn != 16 && bn != 32 && bn != 64 && !(bn >= 128 && bn <= 256 && bn % 16 == 0) && !narrow_pair) FR_REFUSE("gemm_tc: tile width %d", bn);
     // Few rows stream the weights once, and an SM draws only so much (about 45 GB/s on a B200): the product is as fast as
     // its share of busy SMs.  Several waves of whole tiles can leave most SMs idle in the last one (the head's 1,188 tiles
-    // on 148 SMs: a ninth wave of four); where that costs more than a tenth, the k blocks of all tiles are laid end to end
+    // on 148 SMs: a ninth wave of four); with FRIDAY_GEMM_EVEN_RUNS=1 the k blocks of all tiles are then laid end to end
     // and cut into equal runs, one per SM, whatever tiles a run touches (its first and last tile are partial tiles that
-    // the last CTA to arrive sums).  Measured at 7B and 14B sizes: the head 247 -> 236 us; products of one wave gain
-    // nothing from it (the shared finish of their equal splits is worth as much as the idle SMs), so they keep those.
+    // the last CTA to arrive sums).
     bool even_runs = false;
     if (splits_free && swap && use_even_runs()) {
         const long long tiles_now = (long long)((n + TILE_P - 1) / TILE_P) * ((m + bn - 1) / bn);
@@ -1095,10 +1107,10 @@ FR_EXPORT int gemm_tc_fused(const void* x, const void* w, void* out, int out_dty
             FR_REFUSE("gemm_tc: a deferred norm of the input needs its partial sums, the width, and tiles of at most %d rows", TILE_P);
         if (rope || (f.norm_out != nullptr && swap)) {
             // both work on the staged tile of the swapped orientation: whole tiles of 128 columns, rows of 16-byte pieces
-            if (!swap || act || out_dtype != FR_BF16 || bn > 64 || n % TILE_P || ldo % 8 ||
+            if (!swap || act || out_dtype != FR_BF16 || bn > (rope ? 64 : 128) || n % TILE_P || ldo % 8 ||
                 (((uintptr_t)out | (uintptr_t)residual | (uintptr_t)f.norm_out) & 15))
-                FR_REFUSE("gemm_tc: a fused norm or rotation needs few rows (swapped tiles up to 64 wide), bf16 output "
-                          "without activation, n a multiple of %d and 16-byte aligned rows", TILE_P);
+                FR_REFUSE("gemm_tc: a fused norm or rotation needs few rows (swapped tiles up to 128 wide, 64 with a rotation), "
+                          "bf16 output without activation, n a multiple of %d and 16-byte aligned rows", TILE_P);
         }
         if (f.norm_out != nullptr && !swap) {
             // rows on the M side: every thread finishes whole groups of 16 columns of its row
@@ -1172,7 +1184,7 @@ FR_EXPORT int gemm_tc_fused(const void* x, const void* w, void* out, int out_dty
         FR_CHECK_LAUNCH("gemm_tc (pairs)");
         return FR_OK;
     }
-    p.shared_finish = swap && splits > 1 && bn <= 64 && grid == tiles * splits && grid <= sm_count && n % TILE_P == 0 &&
+    p.shared_finish = swap && splits > 1 && bn <= 128 && grid == tiles * splits && grid <= sm_count && n % TILE_P == 0 &&
                       2 * tiles <= n_counters && use_shared_finish();
     CUtensorMap mp, mq;
     int rc = swap ? make_map(&mp, w, n, k, ldw, TILE_P) : make_map(&mp, x, m, k, lda, TILE_P);

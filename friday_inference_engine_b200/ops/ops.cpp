@@ -300,14 +300,25 @@ std::pair<Tensor, Rows> Ops::linear_norm(const Rows& x, const Tensor& weight, co
     const int64_t rows = xt.rows(), n = weight.rows();
     if (norm_weight.numel() == n) {
         Tensor probe = Tensor::make((void*)16, xt.dtype, {rows, n});      // shape and alignment of a fresh result
-        const bool few = few_rows_tile_ok(xt, weight, probe, residual, 64);
-        bool many = false;
-        int bn = 0;
-        if (!few && rows > 64 && n % 16 == 0 && few_rows_tile_ok(xt, weight, probe, residual, rows, 16)) {
-            // many rows: the rows lie on the tiles' M side and every column tile adds one partial sum per row
+        // few rows: the weights lie on the tiles' M side (the planner's choice up to 128 rows) and every tile of 128
+        // columns adds one partial sum per row; many rows: the rows lie on the M side and every column tile adds one
+        bool few = false, many = false;
+        int bn = 0, swap = -1;
+        if (tensor_core_ok(xt, weight, probe, residual)) {
             bool swapped = false;
             plan(rows, n, xt.cols(), &swapped, &bn);
-            many = !swapped;
+            few = swapped && few_rows_tile_ok(xt, weight, probe, residual, 128);
+            many = !few && n % 16 == 0 && few_rows_tile_ok(xt, weight, probe, residual, rows, 16);
+            if (many && swapped) {
+                // few rows whose width is no multiple of 128: the fused norm wants whole tiles that way round, so the
+                // product runs the other way round
+                long long p[8] = {0};
+                const auto& g = kernels::gemm_tc();
+                if (g.plan((int)rows, (int)n, (int)xt.cols(), sms_, 0, -1, -1, p) != 0)
+                    throw KernelError(std::string("gemm_tc_plan: ") + g.last_error());
+                bn = (int)p[1];
+                swap = 0;
+            }
         }
         if (few || many) {
             Tensor out = alloc(xt.dtype, rows, n);
@@ -322,7 +333,7 @@ std::pair<Tensor, Rows> Ops::linear_norm(const Rows& x, const Tensor& weight, co
             f.norm_w_dtype = code(norm_weight.dtype);
             f.norm_out = scaled.data;
             f.out_ssq = (float*)ssq.data;
-            linear_tc(xt, weight, bias, residual, out, -1, -1, -1, 0, &f);
+            linear_tc(xt, weight, bias, residual, out, swap, -1, -1, 0, &f);
             Rows r;
             r.t = scaled;
             r.deferred = true;

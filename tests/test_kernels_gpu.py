@@ -275,7 +275,9 @@ def test_gemm_tensor_core(m, n, k):
     (100, 100, 64, 0, 128, 1), (5, 130, 72, 0, 256, 1), (300, 40, 2048, 1, 32, 1),
     (300, 1000, 256, 0, 208, 1), (2048, 3584, 512, 0, 208, 1), (256, 700, 128, 0, 144, 3), (130, 1001, 328, 0, 240, 1),
     # tiles narrower than 128 on pairs of SMs (more than 128 rows, k not split)
-    (256, 1000, 512, 0, 64, 1), (300, 700, 328, 0, 112, 1), (513, 333, 256, 0, 80, 1), (200, 4608, 192, 0, 96, 1)])
+    (256, 1000, 512, 0, 64, 1), (300, 700, 328, 0, 112, 1), (513, 333, 256, 0, 80, 1), (200, 4608, 192, 0, 96, 1),
+    # weights on the M side with the rows as a 128-wide tile that is finished through a window of 16 rows
+    (128, 512, 1024, 1, 128, 1), (100, 384, 2048, 1, 128, 3), (65, 300, 512, 1, 128, 2), (128, 1024, 4096, 1, 128, 16)])
 def test_gemm_tensor_core_every_tiling(m, n, k, swap, bn, splits):
     """Orientation, tile width and split-k are choices of the launcher; each must give the same product."""
     dt = torch.bfloat16
@@ -392,7 +394,7 @@ def sampled_columns(n, count, seed):
     return torch.cat([torch.tensor([0, 127, 128, n - 129, n - 128, n - 1]), cols]).unique()
 
 
-@pytest.mark.parametrize("m", [129, 256, 300, 512, 640])
+@pytest.mark.parametrize("m", [65, 100, 128, 129, 256, 300, 512, 640])
 @pytest.mark.parametrize("n,k", [(4608, 3584), (3584, 3584), (7168, 5120)])
 def test_products_of_prompts_of_a_few_hundred_rows(m, n, k):
     """The tilings the planner picks between one and a few row tiles (narrow tiles on pairs of SMs among them), with
@@ -540,6 +542,7 @@ def test_attention_mma_dead_rows_give_zero():
 
 
 @pytest.mark.parametrize("m,inner,k", [(1, 64, 64), (8, 18944, 3584), (8, 13824, 5120), (40, 177, 512), (64, 200, 96), (100, 177, 512),
+                                       (100, 18944, 3584), (128, 1024, 512),
                                        (300, 1000, 1024), (2048, 2368, 512)])
 def test_gemm_tensor_core_gated_epilogue(m, inner, k):
     dt = torch.bfloat16
@@ -680,8 +683,9 @@ def test_gemm_begins_a_norm_that_the_next_gemm_finishes(m, n, k, k2, monkeypatch
 @pytest.mark.parametrize("m,n,k,k2", [(80, 3584, 512, 96), (128, 640, 4096, 64), (65, 48, 64, 24), (300, 3584, 1024, 128),
                                       (2048, 3584, 256, 104), (257, 208, 72, 512), (130, 272, 18944, 40)])
 def test_gemm_of_many_rows_begins_a_norm(m, n, k, k2):
-    """More than 64 rows lie on the tiles' M side: every column tile, whatever its width, adds one share of each
-    row's sum of squares; the next product, the same way round, finishes the norm."""
+    """More than 128 rows (and fewer whose width is no multiple of 128) lie on the tiles' M side: every column tile,
+    whatever its width, adds one share of each row's sum of squares; up to 128 rows with the weights on the M side add
+    one share per 128 columns.  The next product, either way round, finishes the norm."""
     x, w = rnd((m, k), torch.bfloat16, 180, 0.5), rnd((n, k), torch.bfloat16, 181, 0.05)
     res, b = rnd((m, n), torch.bfloat16, 182, 2.0), rnd((n,), torch.bfloat16, 183)
     g = rnd((n,), torch.bfloat16, 184) + 1.0
@@ -691,8 +695,13 @@ def test_gemm_of_many_rows_begins_a_norm(m, n, k, k2):
     assert torch.equal(out, ops.linear(x, w, bias=b, residual=res)), "the product itself is unchanged"
     plan = np.zeros(5, dtype=np.int64)
     ops.lib.family("gemm_tc").call("gemm_tc_plan", m, n, k, ops.backend().info()["sm_count"], -1, -1, -1, plan.ctypes.data)
-    bn = int(plan[1])
-    assert plan[0] == 0 and h.ssq.shape == (-(-n // bn), m)
+    assert plan[0] == (1 if m <= 128 else 0)
+    if plan[0] == 1 and n % 128 == 0:
+        bn = 128
+    else:
+        ops.lib.family("gemm_tc").call("gemm_tc_plan", m, n, k, ops.backend().info()["sm_count"], 0, -1, -1, plan.ctypes.data)
+        bn = int(plan[1])
+    assert h.ssq.shape == (-(-n // bn), m)
     sq = f64(out) ** 2
     ssq = np.stack([sq[:, c:c + bn].sum(-1) for c in range(0, n, bn)])
     close(h.ssq, ssq, torch.float32, "partial sums of squares", fp32_tol=1e-5)
