@@ -44,10 +44,13 @@ def test_few_rows_put_the_weights_on_the_m_side(m):
 
 
 def test_tile_width_follows_the_rows():
-    assert [plan(m, 3584, 3584)["bn"] for m in (16, 17, 32, 33, 64)] == [16, 32, 32, 64, 64]
-    assert all(plan(m, 3584, 3584)["swap"] == 1 for m in (1, 64)) and plan(65, 3584, 3584)["swap"] == 0
-    # wide partial tiles are costly to merge: rows on the M side are cut at most four ways
-    assert plan(100, 3584, 18944)["splits"] <= 4
+    assert [plan(m, 3584, 3584)["bn"] for m in (16, 17, 32, 33, 64, 65, 128)] == [16, 32, 32, 64, 64, 128, 128]
+    assert all(plan(m, 3584, 3584)["swap"] == 1 for m in (1, 64, 65, 128)) and plan(129, 3584, 3584)["swap"] == 0
+    # wide partial tiles are costly to merge: rows on the M side are cut at most four ways, and only where a split keeps
+    # 64 k blocks
+    assert plan(130, 3584, 18944)["splits"] <= 4 and plan(256, 4608, 3584)["splits"] == 1
+    # pairs of SMs take narrower tiles where k is short and wider ones leave pairs idle
+    assert plan(256, 4608, 3584)["bn"] == 64 and plan(512, 3584, 3584)["bn"] == 112 and plan(512, 3584, 18944)["bn"] == 128
 
 
 def test_many_rows_fill_whole_waves_of_pairs():
