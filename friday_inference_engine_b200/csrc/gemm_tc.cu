@@ -71,7 +71,7 @@ constexpr int SIDE_BYTES = 3 * TILE_P * 4 + 3 * 64 * 4 + 64 * 8;      // row fac
 template <int BN, int STAGES>
 constexpr int smem_bytes() {
     return STAGES * (P_BYTES + BN * TILE_K * 2) + 1024 + (2 * STAGES + 4) * 8 + 64 + SIDE_BYTES +
-           (BN <= 64 ? BN * TILE_P * 4 : BN == 128 ? 16 * TILE_P * 4 : BN * 4) + (BN <= 64 ? 16 * 64 * 8 : 0);
+           (BN <= 32 ? BN * TILE_P * 4 : BN == 64 || BN == 128 ? 16 * TILE_P * 4 : BN * 4) + (BN <= 64 ? 16 * 64 * 8 : 0);
 }
 
 struct GemmParams {
@@ -219,8 +219,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     long long* s_crow = (long long*)(s_pos + 64);                            // [64]
     // Narrow tiles (the swapped orientation) write their output transposed: the sums of [BN rows][128 columns]
     // go through this buffer so that global memory sees 16-byte pieces of whole rows.
-    // (a 128-wide tile of the swapped orientation goes through a window of 16 of its rows at a time)
-    constexpr int W_ROWS = BN <= 64 ? BN : 16;
+    // (64- and 128-wide tiles of the swapped orientation go through a window of 16 of their rows at a time: 24 KB less
+    // than a whole 64-wide tile, one more stage of the ring)
+    constexpr int W_ROWS = BN <= 32 ? BN : 16;
     constexpr int T_BYTES = BN <= 64 || BN == 128 ? W_ROWS * TILE_P * 4 : 0;
     uint8_t* s_tile = (uint8_t*)s_scale + SIDE_BYTES;
     float2* s_cs = (float2*)(s_tile + T_BYTES);                              // [16][64]: the rotation's (cos, sin) of the 16 rows being finished
@@ -702,7 +703,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                     scale16(c, v);
                     if (staged) {
                         put16(c, v);
-                        if (BN == 128) {                   // the window holds these 16 rows only: finish them now
+                        if (BN >= 64) {                    // the window holds these 16 rows only: finish them now
                             asm volatile("bar.sync 1, 128;" ::: "memory");
                             finish_chunks(p_blk, q_blk, c, BN, false);
                         }
@@ -718,7 +719,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acce0 + 8 * a);     // the accumulator may be overwritten
-            if (part == nullptr && staged && BN != 128) {
+            if (part == nullptr && staged && BN < 64) {
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 finish_chunks(p_blk, q_blk, 0, 1, false);
             }
@@ -1194,7 +1195,7 @@ FR_EXPORT int gemm_tc_fused(const void* x, const void* w, void* out, int out_dty
     switch (bn) {
         case 16: return launch<16, 10>(mp, mq, p, grid, stream);
         case 32: return launch<32, 9>(mp, mq, p, grid, stream);
-        case 64: return launch<64, 7>(mp, mq, p, grid, stream);
+        case 64: return launch<64, 8>(mp, mq, p, grid, stream);
         case 128: return launch<128, 6>(mp, mq, p, grid, stream);
         default: return launch<256, 4>(mp, mq, p, grid, stream);       // any width from 144 to 256
     }
@@ -1231,7 +1232,7 @@ int noalloc_setup(int device) {
     FR_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, device));
     FR_CUDA((allow_smem<16, 10>()));
     FR_CUDA((allow_smem<32, 9>()));
-    FR_CUDA((allow_smem<64, 7>()));
+    FR_CUDA((allow_smem<64, 8>()));
     FR_CUDA((allow_smem<128, 6>()));
     FR_CUDA((allow_smem<256, 4>()));
     d.base = (unsigned char*)ptr;
