@@ -54,9 +54,9 @@ def test_device_decoder_follows_the_plain_model(root, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
-@pytest.mark.parametrize("rows", [17, 32, 64])
+@pytest.mark.parametrize("rows", [17, 32, 64, 100])
 def test_decoder_of_many_rows(root, rows, dtype):
-    """17 to 64 rows: the products put the weights on the tiles' M side with 32- and 64-wide row tiles, the norms
+    """17 to 100 rows: the products put the weights on the tiles' M side with 32- and 64-wide row tiles, the norms
     ride in the epilogues but the rotation has its own kernel, and attention runs one CTA per (sequence, kv head).
     Unequal lengths, and every third row retires midway."""
     d, pm = harness.model_dir(root, "D")

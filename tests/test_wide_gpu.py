@@ -115,10 +115,11 @@ def test_wide_layers_device_decoder(wide):
     eng.check()
 
 
-@pytest.mark.parametrize("rows", [17, 64])
+@pytest.mark.parametrize("rows", [17, 64, 100])
 def test_wide_layers_decoder_of_many_rows(tmp_path, rows):
     """The benchmark's batch-64 step at its layer sizes (one layer): 32- and 64-row tiles with split k where all CTAs
-    of a tile finish 16 rows each, the norm in the epilogues beside the rotary kernel, attention over 64 x 4 CTAs."""
+    of a tile finish 16 rows each, the norm in the epilogues beside the rotary kernel, attention over 64 x 4 CTAs; and
+    100 rows, whose 128-wide tiles go through the 16-row window."""
     cfg = dict(WIDE, num_hidden_layers=1, vocab_size=3000)
     d = tiny_configs.make_model_dir(str(tmp_path / "model"), cfg, 12)
     harness.sharpen(d, 2.0)
